@@ -1,0 +1,191 @@
+"""Generate the golden fixtures in this directory by running the REFERENCE's own goldens.
+
+Run once, in a container that has the reference tree (it is not needed at test time):
+
+    python tests/golden/make_golden.py /path/to/ops-rec
+
+Two reference goldens are executed on small seeded inputs and their outputs stored as .npz:
+
+  * `get_golden_jagged` (numpy, fp32, per-sequence loop; no alpha) from
+    ascendc/attention/hstu_v1/hstu_forward_v1/test/pytest/common.py:189-252 -- imported as a module with a
+    stand-in for the `torch.npu` attribute it touches at import time (common.py:28);
+  * `PytorchNative.kernel(...)._forward_impl` (torch, pads to dense; has alpha and rab) from
+    ascendc/attention/hstu_v2/test/pytest/backend/pytorch_native_backend.py:48-86 -- loaded by file path under a
+    synthetic package so the NPU-only sibling backends are never imported; its mask input is built with
+    `create_causal_mask` of the same reference file set (common.py:128-137).
+
+Every fixture stores the inputs too, so the tests need nothing but numpy/torch.  bf16 arrays are stored as
+their uint16 bit patterns (key suffix `__bf16`).
+"""
+from __future__ import annotations
+
+import importlib.util
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _load_reference(ref_root):
+    v1 = os.path.join(ref_root, "ascendc/attention/hstu_v1/hstu_forward_v1/test/pytest")
+    v2 = os.path.join(ref_root, "ascendc/attention/hstu_v2/test/pytest/backend")
+    if not hasattr(torch, "npu"):
+        torch.npu = types.SimpleNamespace(config=types.SimpleNamespace())
+    spec = importlib.util.spec_from_file_location("ref_v1_common", os.path.join(v1, "common.py"))
+    v1c = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(v1c)
+    pkg = types.ModuleType("ref_v2_backend")
+    pkg.__path__ = [v2]
+    sys.modules["ref_v2_backend"] = pkg
+    for name in ("common", "pytorch_native_backend"):
+        spec = importlib.util.spec_from_file_location(f"ref_v2_backend.{name}", os.path.join(v2, f"{name}.py"))
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[f"ref_v2_backend.{name}"] = mod
+        spec.loader.exec_module(mod)
+    return v1c, sys.modules["ref_v2_backend.pytorch_native_backend"]
+
+
+def _store(path, arrays):
+    out = {}
+    for key, val in arrays.items():
+        if val is None:
+            continue
+        if isinstance(val, torch.Tensor):
+            if val.dtype == torch.bfloat16:
+                out[key + "__bf16"] = val.view(torch.int16).numpy().view(np.uint16)
+                continue
+            val = val.numpy()
+        out[key] = np.asarray(val)
+    np.savez_compressed(path, **out)
+
+
+# name, B, Hq, Hk, Dqk, Dv, maxL, len range, dtype, alpha, rab, ctx, target, group, mask_type, delta
+CASES = [
+    # BASELINE config 1: B4 H2 d32 fp32, L ~ U[1,128] seed 0, alpha 1/32, causal, no rab
+    dict(name="cfg1_fp32_causal", B=4, Hq=2, Hk=2, Dqk=32, Dv=32, maxL=128, lo=1, hi=128, dtype="fp32",
+         alpha=1.0 / 32, rab=False, ctx=0, tgt=0, g=0, mask_type=0, numpy_rng_lengths=True),
+    dict(name="fp32_rab_alpha", B=3, Hq=2, Hk=2, Dqk=16, Dv=16, maxL=40, lo=1, hi=40, dtype="fp32",
+         alpha=0.37, rab=True, ctx=0, tgt=0, g=0, mask_type=0),
+    dict(name="fp32_target_g1", B=3, Hq=2, Hk=2, Dqk=16, Dv=32, maxL=70, lo=1, hi=30, dtype="fp32",
+         alpha=1.0, rab=True, ctx=0, tgt=30, g=1, mask_type=0),
+    dict(name="fp32_ctx_target_g3", B=4, Hq=4, Hk=2, Dqk=32, Dv=16, maxL=80, lo=1, hi=40, dtype="fp32",
+         alpha=0.5, rab=False, ctx=6, tgt=30, g=3, mask_type=0),
+    dict(name="fp32_ctx_only", B=2, Hq=2, Hk=1, Dqk=16, Dv=16, maxL=50, lo=1, hi=40, dtype="fp32",
+         alpha=1.0, rab=True, ctx=6, tgt=0, g=1, mask_type=0),
+    dict(name="fp32_target_g0", B=2, Hq=1, Hk=1, Dqk=16, Dv=16, maxL=50, lo=1, hi=30, dtype="fp32",
+         alpha=1.0, rab=False, ctx=0, tgt=9, g=0, mask_type=0),
+    dict(name="fp32_mask_none", B=3, Hq=2, Hk=2, Dqk=16, Dv=16, maxL=33, lo=1, hi=33, dtype="fp32",
+         alpha=0.25, rab=True, ctx=0, tgt=0, g=0, mask_type=2),
+    dict(name="fp32_mask_custom", B=2, Hq=2, Hk=2, Dqk=16, Dv=16, maxL=29, lo=1, hi=29, dtype="fp32",
+         alpha=1.0, rab=False, ctx=0, tgt=0, g=0, mask_type=3),
+    dict(name="fp32_delta", B=3, Hq=2, Hk=2, Dqk=16, Dv=16, maxL=48, lo=1, hi=48, dtype="fp32",
+         alpha=0.3, rab=True, ctx=0, tgt=0, g=0, mask_type=0, delta=True),
+    dict(name="bf16_d128_rab_target", B=3, Hq=2, Hk=2, Dqk=128, Dv=128, maxL=300, lo=100, hi=260, dtype="bf16",
+         alpha=1.0 / 128, rab=True, ctx=0, tgt=17, g=1, mask_type=0),
+    dict(name="bf16_d64_gqa", B=4, Hq=4, Hk=2, Dqk=64, Dv=64, maxL=200, lo=1, hi=200, dtype="bf16",
+         alpha=1.0 / 64, rab=False, ctx=0, tgt=0, g=0, mask_type=0),
+]
+
+
+def build_case(case, v1c, v2b):
+    torch.manual_seed(1234 + len(case["name"]))
+    rng = np.random.default_rng(0)
+    B, Hq, Hk, Dqk, Dv, maxL = (case[k] for k in ("B", "Hq", "Hk", "Dqk", "Dv", "maxL"))
+    dtype = torch.float32 if case["dtype"] == "fp32" else torch.bfloat16
+    ctx, tgt, g = case["ctx"], case["tgt"], case["g"]
+    base = rng.integers(case["lo"], case["hi"] + 1, B)
+    len_k = base + (ctx + tgt if case["mask_type"] == 0 else 0)
+    if case.get("delta"):
+        len_q = np.maximum(1, len_k - rng.integers(0, 9, B))
+    else:
+        len_q = len_k.copy()
+    assert len_k.max() <= maxL
+    offq = np.concatenate([[0], np.cumsum(len_q)]).astype(np.int64)
+    offk = np.concatenate([[0], np.cumsum(len_k)]).astype(np.int64)
+    scale_in = 1.0 if case["dtype"] == "fp32" else 0.5
+    q = (torch.randn(int(offq[-1]), Hq, Dqk) * scale_in).to(dtype)
+    k = (torch.randn(int(offk[-1]), Hk, Dqk) * scale_in).to(dtype)
+    v = (torch.randn(int(offk[-1]), Hk, Dv) * scale_in).to(dtype)
+    rab = (torch.randn(B, Hq, maxL, maxL) * (1.0 if case["dtype"] == "fp32" else 0.1)).to(dtype) \
+        if case["rab"] else None
+    num_context = np.full(B, ctx, dtype=np.int64)
+    num_target = np.full(B, tgt, dtype=np.int64)
+    mask = None
+    if case["mask_type"] == 3:
+        mask = torch.randint(0, 2, (B, Hq, maxL, maxL)).to(dtype)
+
+    # dense mask tensor the v2 golden multiplies by (reference semantics, reference code)
+    dense_mask = None
+    if case["mask_type"] == 0:
+        dense_mask = torch.zeros(B, Hq, maxL, maxL)
+        for b in range(B):
+            lq, lk = int(len_q[b]), int(len_k[b])
+            dense_mask[b, :, :lq, :lk] = v1c.create_causal_mask(lq, lk, ctx or None, tgt or None, g or None)
+    elif case["mask_type"] == 3:
+        dense_mask = mask.float()
+
+    # golden A: v2 torch golden in fp32 (alpha, rab, mask) -- the fp32-accumulated reference
+    kern = v2b.PytorchNative.kernel(case["alpha"], 0.0, rab is not None, maxL, maxL,
+                                    torch.from_numpy(offq), torch.from_numpy(offk))
+    with torch.enable_grad():
+        out_v2_fp32 = kern._forward_impl(q.float().clone(), k.float().clone(), v.float().clone(),
+                                         rab.float().clone() if rab is not None else None,
+                                         dense_mask).detach()
+    arrays = dict(q=q, k=k, v=v, rab=rab, mask=mask, seq_offset=offq, seq_offset_k=offk,
+                  num_context=num_context, num_target=num_target,
+                  meta=np.array([B, Hq, Hk, Dqk, Dv, maxL, ctx, tgt, g, case["mask_type"]], dtype=np.int64),
+                  alpha=np.float64(case["alpha"]), out_v2_fp32=out_v2_fp32)
+    # golden B: v2 torch golden in the input dtype (low-precision side of the double-reference rule)
+    if dtype != torch.float32:
+        kern2 = v2b.PytorchNative.kernel(case["alpha"], 0.0, rab is not None, maxL, maxL,
+                                         torch.from_numpy(offq), torch.from_numpy(offk))
+        with torch.enable_grad():
+            arrays["out_v2_lowp"] = kern2._forward_impl(
+                q.clone(), k.clone(), v.clone(), rab.clone() if rab is not None else None,
+                dense_mask.to(dtype) if dense_mask is not None else None).detach()
+    # golden C: v1 numpy golden (no alpha => only comparable when alpha == 1)
+    if case["alpha"] == 1.0:
+        out_v1 = v1c.get_golden_jagged(
+            q.float().numpy(), k.float().numpy(), v.float().numpy(),
+            mask=mask.float().numpy() if mask is not None else None,
+            attn_bias=rab.float().numpy() if rab is not None else None,
+            mask_type=case["mask_type"], max_seq_len=maxL, silu_scale=0.0, seq_offset=offq, seq_offset_k=offk,
+            num_context=num_context if ctx else None, num_target=num_target if tgt else None,
+            target_group_size=g)
+        arrays["out_v1_numpy"] = out_v1
+    return arrays
+
+
+def main():
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    v1c, v2b = _load_reference(ref_root)
+    for case in CASES:
+        arrays = build_case(case, v1c, v2b)
+        path = os.path.join(HERE, case["name"] + ".npz")
+        _store(path, arrays)
+        print(f"{case['name']:28s} tokens_q={arrays['q'].shape[0]:5d} {os.path.getsize(path) / 1024:8.1f} KiB")
+
+    # mask-only fixtures: the reference's create_causal_mask over a grid incl. the boundary values its tests use
+    grid = []
+    masks = {}
+    for (lq, lk) in [(1, 1), (7, 7), (33, 33), (64, 64), (65, 65), (40, 52), (129, 129)]:
+        for c in (0, 1, 6, 31):
+            for t in (0, 1, 5, 30):
+                for g in (0, 1, 3):
+                    if c + t > lq:
+                        continue
+                    m = v1c.create_causal_mask(lq, lk, c or None, t or None, g or None).numpy().astype(np.uint8)
+                    key = f"m_{lq}_{lk}_{c}_{t}_{g}"
+                    masks[key] = np.packbits(m, axis=None)
+                    grid.append((lq, lk, c, t, g))
+    masks["grid"] = np.array(grid, dtype=np.int64)
+    np.savez_compressed(os.path.join(HERE, "mask_grid.npz"), **masks)
+    print("mask_grid", len(grid), "masks")
+
+
+if __name__ == "__main__":
+    main()
