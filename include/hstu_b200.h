@@ -1,0 +1,159 @@
+/*
+ * C ABI of the B200 (sm_100a) HSTU jagged attention forward.
+ *
+ *   O = ( silu(alpha * (Q.K^T + attn_bias)) * silu_scale * M ) . V      per sequence, per head
+ *
+ * over variable-length sequences packed along the token axis by seq_offset.  The functions below are what the
+ * reference's torch adapter binds for this operator through its two-phase "aclnn" C interface:
+ *
+ *   aclnnHstuJaggedForwardGetWorkspaceSize / aclnnHstuJaggedForward
+ *     contract:  ascendc/attention/hstu_v1/hstu_forward_v1/docs/aclnn_hstu_forward.md:47-62,107-112
+ *     call site: ascendc/attention/hstu_v1/torch_extension/hstu_jagged_plugin.cpp:63-65
+ *     macro:     ascendc/common/torch_plugin/pytorch_npu_helper.hpp:625-677 (phase 1 sizes the workspace, the
+ *                caller allocates it, phase 2 enqueues the kernel on the caller's stream)
+ *
+ * Rules of the boundary
+ *   - plain C, no exceptions: every function returns 0 on success or a negative HSTU_E* code; the text of the last
+ *     error of the calling thread is available from hstu_last_error().
+ *   - the caller owns every buffer, including the workspace; the library allocates no device memory.
+ *   - hstu_jagged_fwd is asynchronous on `stream`; it never synchronises and never reads device data on the host.
+ *     The sequence offsets are device data, so per-call scheduling happens in a small device pre-pass.
+ *   - there is no CPU implementation behind these entry points.
+ */
+#ifndef HSTU_B200_H_
+#define HSTU_B200_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define HSTU_API __attribute__((visibility("default")))
+#else
+#define HSTU_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element type of q/k/v/out/attn_bias/mask */
+enum { HSTU_DTYPE_BF16 = 0, HSTU_DTYPE_FP16 = 1, HSTU_DTYPE_FP32 = 2 };
+
+/* mask_type values of the reference (ascendc/attention/hstu_v1/torch_extension/hstu_common.h:36-39);
+ * 1 (upper-triangular) is rejected there and here. */
+enum { HSTU_MASK_TRIL = 0, HSTU_MASK_TRIU = 1, HSTU_MASK_NONE = 2, HSTU_MASK_CUSTOM = 3 };
+
+/* flags */
+enum {
+  HSTU_FLAG_DETERMINISTIC = 1u << 0, /* accepted for schema compatibility; results are always deterministic */
+  HSTU_FLAG_ALPHA_BEFORE_BIAS = 1u << 1, /* silu(alpha*QK^T + bias) instead of the reference's silu(alpha*(QK^T + bias)) */
+  HSTU_FLAG_FORCE_GENERIC = 1u << 2 /* use the generic fp32-accumulate CUDA-core kernel even where the tensor-core one applies */
+};
+
+/* error codes (the reference's aclnn layer reports 161001 for null pointers and 161002 for invalid
+ * parameters, aclnn_hstu_forward.md:109-112; these are their counterparts) */
+enum {
+  HSTU_OK = 0,
+  HSTU_E_NULL = -1,      /* required pointer is null */
+  HSTU_E_PARAM = -2,     /* shape / dtype / range check failed */
+  HSTU_E_WORKSPACE = -3, /* workspace missing, misaligned or too small */
+  HSTU_E_CUDA = -4,      /* CUDA runtime or driver call failed */
+  HSTU_E_ARCH = -5       /* device is not sm_100 */
+};
+
+/* bits of the device status word written by the pre-pass (read it with hstu_jagged_fwd_status) */
+enum {
+  HSTU_ST_BAD_OFFSETS = 1u << 0,   /* offsets not monotone */
+  HSTU_ST_LEN_GT_MAX = 1u << 1,    /* a sequence is longer than max_seq_len (bias/mask rows would be overrun) */
+  HSTU_ST_BAD_CTX_TARGET = 1u << 2,/* num_context + num_target exceeds the sequence length, or negative */
+  HSTU_ST_PIPE_TIMEOUT = 1u << 8   /* a bounded wait inside the tensor-core kernel gave up */
+};
+
+typedef struct HstuJaggedArgs {
+  uint32_t struct_bytes; /* sizeof(HstuJaggedArgs), checked */
+  int32_t dtype;         /* HSTU_DTYPE_* */
+
+  /* device pointers; q [total_q, heads_q, dim_qk], k [total_k, heads_k, dim_qk], v [total_k, heads_k, dim_v],
+   * out [total_q, heads_q, dim_v]; all contiguous (hstu_jagged_plugin.cpp:35-37 makes them so) */
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  /* optional [B, heads_q, max_seq_len_q, max_seq_len_k]; bias_batch_stride == 0 broadcasts one
+   * [heads_q, max_seq_len_q, max_seq_len_k] block over the batch (extension of the reference) */
+  const void* attn_bias;
+  int64_t bias_batch_stride; /* in elements */
+  /* required iff mask_type == HSTU_MASK_CUSTOM: [B, heads_q, max_seq_len_q, max_seq_len_k], values multiply P */
+  const void* mask;
+
+  /* [batch + 1] exclusive prefix sums on the device, int32 or int64 (index_bytes = 4 or 8);
+   * seq_offset_k == NULL means "same as seq_offset_q" (the .equal overload) */
+  const void* seq_offset_q;
+  const void* seq_offset_k;
+  /* optional [batch], same integer width as the offsets; NULL means all zero */
+  const void* num_context;
+  const void* num_target;
+  int32_t index_bytes;
+
+  int32_t batch;
+  int64_t total_q;
+  int64_t total_k;
+  int32_t heads_q;
+  int32_t heads_k;
+  int32_t dim_qk;
+  int32_t dim_v;
+
+  int32_t mask_type;      /* HSTU_MASK_* */
+  int32_t max_seq_len_q;  /* [1, 20480] */
+  int32_t max_seq_len_k;
+  int32_t target_group_size;
+  float silu_scale;       /* 0 => 1 / max_seq_len_q (hstu_jagged_plugin.cpp:61) */
+  float alpha;
+  uint32_t flags;         /* HSTU_FLAG_* */
+  uint32_t reserved;
+} HstuJaggedArgs;
+
+/* Phase 1 (replaces aclnnHstuJaggedForwardGetWorkspaceSize): validates the arguments that can be checked
+ * without touching device memory and returns the number of workspace bytes phase 2 needs (never 0). */
+HSTU_API int hstu_jagged_fwd_get_workspace_size(const HstuJaggedArgs* args, uint64_t* workspace_bytes);
+
+/* Phase 2 (replaces aclnnHstuJaggedForward): enqueue the forward on `stream` (a cudaStream_t; NULL = default
+ * stream) of the current device.  `workspace` is device memory, 256-byte aligned, at least the size phase 1
+ * returned, and must stay alive until the work completes. */
+HSTU_API int hstu_jagged_fwd(const HstuJaggedArgs* args, void* workspace, uint64_t workspace_bytes, void* stream);
+
+/* Optional: wait for `stream` and fetch the device status word of the last launch that used `workspace`
+ * (0 = inputs were consistent).  The reference reads out of bounds on such inputs without noticing. */
+HSTU_API int hstu_jagged_fwd_status(const void* workspace, void* stream, uint32_t* status);
+
+/* Which kernel phase 2 would run for these arguments: 1 = tcgen05 tensor-core kernel, 0 = generic kernel,
+ * negative = error code. */
+HSTU_API int hstu_jagged_fwd_kernel_kind(const HstuJaggedArgs* args);
+
+/* Host-side run of the scheduling pre-pass on HOST copies of the offsets (the same ordering rule the device
+ * pre-pass applies), for tests and tooling.  Writes up to `capacity` work items, each {sequence, head << 16 | q_pair} as two
+ * uint32, returns the item count (or a negative error code) and the status bits. */
+HSTU_API int64_t hstu_plan_host(const HstuJaggedArgs* args, const void* host_offset_q, const void* host_offset_k,
+                       const void* host_num_context, const void* host_num_target, uint32_t* items,
+                       int64_t capacity, uint32_t* status);
+
+/* Testing hooks: the device mask predicate and K-tile classifier evaluated on the host (same source, compiled
+ * for the host).  hstu_debug_mask_host fills out[len_q * len_k] with 0/1 visibility; hstu_debug_tiles_host returns
+ * how many K tiles of width bn the q-tile rows [r0, r0+rows) visits and which of them need no per-element
+ * predicate.  No counterpart in the reference API; its kernel-side equivalent is
+ * ascendc/attention/hstu_v1/hstu_forward_v1/op_kernel/atlas950/hstu_dense_causal_mask.h:63-260. */
+HSTU_API int hstu_debug_mask_host(int32_t len_q, int32_t len_k, int32_t num_context, int32_t num_target,
+                         int32_t target_group_size, int32_t mask_type, uint8_t* out);
+HSTU_API int hstu_debug_tiles_host(int32_t len_q, int32_t len_k, int32_t num_context, int32_t num_target,
+                          int32_t target_group_size, int32_t mask_type, int32_t r0, int32_t rows, int32_t bn,
+                          uint64_t* full_bits);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+HSTU_API const char* hstu_last_error(void);
+
+/* Library version, e.g. 100 = 0.1.0 */
+HSTU_API int hstu_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HSTU_B200_H_ */

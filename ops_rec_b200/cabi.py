@@ -1,0 +1,223 @@
+"""ctypes binding of the C ABI declared in include/hstu_b200.h.
+
+This is the binding a Python caller without the torch operator registration would write; the parity tests use
+it so that every GPU result they check went through the C entry points.  torch is used only for device memory
+and the current stream.  Loading fails loudly when the shared library has not been built - there is no
+fallback of any kind.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libhstu_b200.so")
+
+DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2
+MASK_TRIL, MASK_TRIU, MASK_NONE, MASK_CUSTOM = 0, 1, 2, 3
+FLAG_DETERMINISTIC, FLAG_ALPHA_BEFORE_BIAS, FLAG_FORCE_GENERIC = 1, 2, 4
+ST_BAD_OFFSETS, ST_LEN_GT_MAX, ST_BAD_CTX_TARGET, ST_PIPE_TIMEOUT = 1, 2, 4, 256
+
+EXPORTS = (
+    "hstu_jagged_fwd_get_workspace_size", "hstu_jagged_fwd", "hstu_jagged_fwd_status",
+    "hstu_jagged_fwd_kernel_kind", "hstu_plan_host", "hstu_debug_mask_host", "hstu_debug_tiles_host",
+    "hstu_last_error", "hstu_b200_version",
+)
+
+
+class HstuJaggedArgs(C.Structure):
+    _fields_ = [
+        ("struct_bytes", C.c_uint32), ("dtype", C.c_int32),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("attn_bias", C.c_void_p), ("bias_batch_stride", C.c_int64), ("mask", C.c_void_p),
+        ("seq_offset_q", C.c_void_p), ("seq_offset_k", C.c_void_p),
+        ("num_context", C.c_void_p), ("num_target", C.c_void_p), ("index_bytes", C.c_int32),
+        ("batch", C.c_int32), ("total_q", C.c_int64), ("total_k", C.c_int64),
+        ("heads_q", C.c_int32), ("heads_k", C.c_int32), ("dim_qk", C.c_int32), ("dim_v", C.c_int32),
+        ("mask_type", C.c_int32), ("max_seq_len_q", C.c_int32), ("max_seq_len_k", C.c_int32),
+        ("target_group_size", C.c_int32), ("silu_scale", C.c_float), ("alpha", C.c_float),
+        ("flags", C.c_uint32), ("reserved", C.c_uint32),
+    ]
+
+
+class HstuError(RuntimeError):
+    """A non-zero status from the C ABI (code in .code, text from hstu_last_error())."""
+
+    def __init__(self, code, text):
+        super().__init__(f"hstu_b200 error {code}: {text}")
+        self.code = code
+
+
+_lib = None
+
+
+def load():
+    """dlopen the library (once) and declare the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m ops_rec_b200._build` "
+            "(nvcc, sm_100a). There is no fallback implementation.")
+    lib = C.CDLL(LIB_PATH)
+    A = C.POINTER(HstuJaggedArgs)
+    lib.hstu_jagged_fwd_get_workspace_size.argtypes = [A, C.POINTER(C.c_uint64)]
+    lib.hstu_jagged_fwd_get_workspace_size.restype = C.c_int
+    lib.hstu_jagged_fwd.argtypes = [A, C.c_void_p, C.c_uint64, C.c_void_p]
+    lib.hstu_jagged_fwd.restype = C.c_int
+    lib.hstu_jagged_fwd_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)]
+    lib.hstu_jagged_fwd_status.restype = C.c_int
+    lib.hstu_jagged_fwd_kernel_kind.argtypes = [A]
+    lib.hstu_jagged_fwd_kernel_kind.restype = C.c_int
+    lib.hstu_plan_host.argtypes = [A, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                   C.POINTER(C.c_uint32)]
+    lib.hstu_plan_host.restype = C.c_int64
+    lib.hstu_debug_mask_host.argtypes = [C.c_int32] * 6 + [C.c_void_p]
+    lib.hstu_debug_mask_host.restype = C.c_int
+    lib.hstu_debug_tiles_host.argtypes = [C.c_int32] * 9 + [C.POINTER(C.c_uint64)]
+    lib.hstu_debug_tiles_host.restype = C.c_int
+    lib.hstu_last_error.restype = C.c_char_p
+    lib.hstu_b200_version.restype = C.c_int
+    _lib = lib
+    return lib
+
+
+def check(rc):
+    if rc < 0:
+        raise HstuError(rc, load().hstu_last_error().decode())
+    return rc
+
+
+def _dtype_code(t):
+    import torch
+    code = {torch.bfloat16: DTYPE_BF16, torch.float16: DTYPE_FP16, torch.float32: DTYPE_FP32}.get(t)
+    if code is None:
+        raise HstuError(-2, f"dtype {t} is not supported (bf16, fp16, fp32 only; fp8 inputs are rejected)")
+    return code
+
+
+def make_args(q, k, v, out, seq_offset, *, seq_offset_k=None, mask=None, attn_bias=None, mask_type=0,
+              max_seq_len=0, max_seq_len_k=None, silu_scale=0.0, num_context=None, num_target=None,
+              target_group_size=0, alpha=1.0, flags=0, ptr=lambda t: t.data_ptr()):
+    """Fill an HstuJaggedArgs from tensors (torch tensors by default; `ptr` extracts the address).
+    Returns (args, keepalive) - keepalive holds converted temporaries that must outlive the launch."""
+    a = HstuJaggedArgs()
+    a.struct_bytes = C.sizeof(HstuJaggedArgs)
+    a.dtype = _dtype_code(q.dtype)
+    keep = []
+    a.q, a.k, a.v = ptr(q), ptr(k), ptr(v)
+    a.out = ptr(out) if out is not None else None
+    if attn_bias is not None:
+        a.attn_bias = ptr(attn_bias)
+        if attn_bias.dim() == 3 or attn_bias.shape[0] == 1:
+            a.bias_batch_stride = 0
+        else:
+            a.bias_batch_stride = attn_bias.shape[-3] * attn_bias.shape[-2] * attn_bias.shape[-1]
+    if mask is not None:
+        a.mask = ptr(mask)
+    a.seq_offset_q = ptr(seq_offset)
+    a.seq_offset_k = ptr(seq_offset_k) if seq_offset_k is not None else None
+    a.index_bytes = seq_offset.element_size()
+    for name, t in (("num_context", num_context), ("num_target", num_target)):
+        if t is not None:
+            if t.dtype != seq_offset.dtype:
+                t = t.to(seq_offset.dtype)
+                keep.append(t)
+            setattr(a, name, ptr(t))
+    a.batch = seq_offset.shape[0] - 1
+    a.total_q, a.total_k = q.shape[0], k.shape[0]
+    a.heads_q, a.heads_k, a.dim_qk, a.dim_v = q.shape[1], k.shape[1], q.shape[2], v.shape[2]
+    a.mask_type = int(mask_type)
+    a.max_seq_len_q = int(max_seq_len)
+    a.max_seq_len_k = int(max_seq_len_k if max_seq_len_k else max_seq_len)
+    a.target_group_size = int(target_group_size or 0)
+    a.silu_scale = float(silu_scale)
+    a.alpha = float(1.0 if alpha is None else alpha)
+    a.flags = int(flags)
+    return a, keep
+
+
+def workspace_size(args):
+    n = C.c_uint64(0)
+    check(load().hstu_jagged_fwd_get_workspace_size(C.byref(args), C.byref(n)))
+    return n.value
+
+
+def kernel_kind(args):
+    return check(load().hstu_jagged_fwd_kernel_kind(C.byref(args)))
+
+
+def hstu_jagged_forward(q, k, v, mask=None, attn_bias=None, mask_type=0, max_seq_len=0, silu_scale=0.0,
+                        seq_offset=None, num_context=None, num_target=None, target_group_size=0, alpha=1.0,
+                        deterministic=False, *, max_seq_len_k=None, seq_offset_k=None, flags=0,
+                        return_status=False, out=None):
+    """The operator through the C ABI on CUDA tensors (argument order of ops_rec::hstu_jagged.equal,
+    ascendc/attention/hstu_v1/torch_extension/hstu_jagged_plugin.cpp:188-201; the keyword-only extras give the
+    .delta overload).  Launches on torch's current stream; with return_status=True it also synchronises and
+    returns the device status word."""
+    import torch
+    if q.dim() != 3:
+        raise HstuError(-2, "The q should be 3D in jagged layout")
+    if not q.is_cuda:
+        raise HstuError(-2, "tensors must live on a CUDA device; there is no CPU implementation")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if out is None:
+        out = torch.empty(q.shape[0], q.shape[1], v.shape[2], dtype=q.dtype, device=q.device)
+    if deterministic:
+        flags |= FLAG_DETERMINISTIC
+    args, keep = make_args(q, k, v, out, seq_offset, seq_offset_k=seq_offset_k, mask=mask, attn_bias=attn_bias,
+                           mask_type=mask_type, max_seq_len=max_seq_len, max_seq_len_k=max_seq_len_k,
+                           silu_scale=silu_scale, num_context=num_context, num_target=num_target,
+                           target_group_size=target_group_size, alpha=alpha, flags=flags)
+    nbytes = workspace_size(args)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+        check(load().hstu_jagged_fwd(C.byref(args), ws.data_ptr(), nbytes, stream))
+        if return_status:
+            st = C.c_uint32(0)
+            check(load().hstu_jagged_fwd_status(ws.data_ptr(), stream, C.byref(st)))
+            return out, st.value
+    del keep
+    return out
+
+
+def plan_host(seq_offset, heads_q, *, num_context=None, num_target=None, max_seq_len=20480, dim=128,
+              dtype_code=DTYPE_BF16, mask_type=0):
+    """Run the scheduler's ordering rule on host arrays; returns (items[n,2] uint32, status)."""
+    off = np.ascontiguousarray(np.asarray(seq_offset, dtype=np.int64))
+    a = HstuJaggedArgs()
+    a.struct_bytes = C.sizeof(HstuJaggedArgs)
+    a.dtype = dtype_code
+    a.index_bytes = 8
+    a.batch = len(off) - 1
+    a.total_q = a.total_k = int(off[-1])
+    a.heads_q = a.heads_k = heads_q
+    a.dim_qk = a.dim_v = dim
+    a.mask_type = mask_type
+    a.max_seq_len_q = a.max_seq_len_k = max_seq_len
+    a.alpha = 1.0
+    ctx = np.ascontiguousarray(np.asarray(num_context, dtype=np.int64)) if num_context is not None else None
+    tgt = np.ascontiguousarray(np.asarray(num_target, dtype=np.int64)) if num_target is not None else None
+    cap = heads_q * (int(off[-1]) // 256 + a.batch) + 1
+    items = np.zeros((cap, 2), dtype=np.uint32)
+    st = C.c_uint32(0)
+    n = check(load().hstu_plan_host(
+        C.byref(a), off.ctypes.data, None, ctx.ctypes.data if ctx is not None else None,
+        tgt.ctypes.data if tgt is not None else None, items.ctypes.data, cap, C.byref(st)))
+    return items[:n], st.value
+
+
+def debug_mask(len_q, len_k, ctx, tgt, group, mask_type=0):
+    out = np.zeros((len_q, len_k), dtype=np.uint8)
+    check(load().hstu_debug_mask_host(len_q, len_k, ctx, tgt, group, mask_type, out.ctypes.data))
+    return out.astype(bool)
+
+
+def debug_tiles(len_q, len_k, ctx, tgt, group, mask_type, r0, rows, bn):
+    bits = C.c_uint64(0)
+    n = check(load().hstu_debug_tiles_host(len_q, len_k, ctx, tgt, group, mask_type, r0, rows, bn, C.byref(bits)))
+    return n, bits.value

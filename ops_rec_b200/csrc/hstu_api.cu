@@ -1,0 +1,272 @@
+// C ABI of the library (declared in include/hstu_b200.h): argument validation, workspace sizing, kernel choice.
+//
+// The checks restate what the reference enforces on its way to the kernel:
+//   torch adapter  ascendc/attention/hstu_v1/torch_extension/hstu_jagged_plugin.cpp:29-51, hstu_common.h:68-82
+//   host tiling    ascendc/attention/hstu_v1/hstu_forward_v1/op_host/tiling_policy.cpp:68-93,
+//                  tiling_policy_jagged.cpp:103-203 (head ratio, equal k/v token and head counts, dims)
+// with two documented relaxations (batch may exceed 2048; attn_bias may be broadcast over the batch).
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "hstu_common.cuh"
+
+namespace hstu {
+cudaError_t launch_generic(const KParams& p, int dtype, cudaStream_t stream);
+cudaError_t launch_prepass(const KParams& p, bool build_items, cudaStream_t stream);
+long long plan_host(const KParams& p, uint32_t* items, long long capacity, uint32_t* status);
+bool tc_supported(const KParams& p, int dtype);
+cudaError_t launch_tc(const KParams& p, int dtype, int num_sms, cudaStream_t stream);
+}  // namespace hstu
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+constexpr int kMaxSeqLen = 20480;  // hstu_common.h:36
+constexpr int kMaxHeads = 16;      // hstu_common.h:40
+constexpr int kMaxDim = 512;       // hstu_common.h:45
+
+int validate(const HstuJaggedArgs* a) {
+  if (!a) return fail(HSTU_E_NULL, "args is null");
+  if (a->struct_bytes != sizeof(HstuJaggedArgs))
+    return fail(HSTU_E_PARAM, "struct_bytes is %u, this library expects %zu", a->struct_bytes, sizeof(HstuJaggedArgs));
+  if (a->dtype != HSTU_DTYPE_BF16 && a->dtype != HSTU_DTYPE_FP16 && a->dtype != HSTU_DTYPE_FP32)
+    return fail(HSTU_E_PARAM, "dtype must be bf16, fp16 or fp32 (fp8 inputs are not supported)");
+  if (a->batch < 1) return fail(HSTU_E_PARAM, "seq_offset params error should have at least two element.");
+  if (a->index_bytes != 4 && a->index_bytes != 8) return fail(HSTU_E_PARAM, "seq_offset must be int32 or int64");
+  if (a->total_q < 0 || a->total_k < 0) return fail(HSTU_E_PARAM, "negative token count");
+  if (a->heads_q < 1 || a->heads_q > kMaxHeads || a->heads_k < 1)
+    return fail(HSTU_E_PARAM, "head count expect in [1, %d], but value is %d", kMaxHeads, a->heads_q);
+  if (a->heads_q % a->heads_k != 0)
+    return fail(HSTU_E_PARAM, "head_num_q (%d) must be divisible by head_num_k (%d)", a->heads_q, a->heads_k);
+  if (a->dim_qk < 1 || a->dim_qk > kMaxDim) return fail(HSTU_E_PARAM, "q/k head dim expect in [1, 512], but value is %d", a->dim_qk);
+  if (a->dim_v < 16 || a->dim_v > kMaxDim || a->dim_v % 16 != 0)
+    return fail(HSTU_E_PARAM, "v head dim expect a multiple of 16 in [16, 512], but value is %d", a->dim_v);
+  if (a->mask_type < HSTU_MASK_TRIL || a->mask_type > HSTU_MASK_CUSTOM)
+    return fail(HSTU_E_PARAM, "maskType expect in [0, 3], but value is %d", a->mask_type);
+  if (a->mask_type == HSTU_MASK_TRIU)
+    return fail(HSTU_E_PARAM, "maskType current not support triu now, pls use custome mask");
+  if (a->mask_type == HSTU_MASK_CUSTOM && !a->mask)
+    return fail(HSTU_E_PARAM, "use custome mask must have valide mask tensor");
+  if (a->max_seq_len_q < 1 || a->max_seq_len_q > kMaxSeqLen)
+    return fail(HSTU_E_PARAM, "maxSeqLen expect in [1, 20480], but value is %d", a->max_seq_len_q);
+  if (a->max_seq_len_k < 1 || a->max_seq_len_k > kMaxSeqLen)
+    return fail(HSTU_E_PARAM, "maxSeqLenK expect in [1, 20480], but value is %d", a->max_seq_len_k);
+  if (a->target_group_size < 0) return fail(HSTU_E_PARAM, "target_group_size must be >= 0");
+  if (a->bias_batch_stride < 0) return fail(HSTU_E_PARAM, "bias_batch_stride must be >= 0");
+  if (!(a->silu_scale == a->silu_scale) || !(a->alpha == a->alpha)) return fail(HSTU_E_PARAM, "silu_scale / alpha is NaN");
+  return HSTU_OK;
+}
+
+int validate_pointers(const HstuJaggedArgs* a) {
+  if (!a->seq_offset_q) return fail(HSTU_E_NULL, "seq_offset is null");
+  if (a->total_q > 0 && (!a->q || !a->out)) return fail(HSTU_E_NULL, "q / out is null");
+  if (a->total_k > 0 && (!a->k || !a->v)) return fail(HSTU_E_NULL, "k / v is null");
+  return HSTU_OK;
+}
+
+hstu::KParams to_params(const HstuJaggedArgs* a, void* workspace, uint64_t workspace_bytes) {
+  hstu::KParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = a->q;
+  p.k = a->k;
+  p.v = a->v;
+  p.out = a->out;
+  p.bias = a->attn_bias;
+  p.mask = a->mask_type == HSTU_MASK_CUSTOM ? a->mask : nullptr;
+  p.offq = a->seq_offset_q;
+  p.offk = a->seq_offset_k ? a->seq_offset_k : a->seq_offset_q;
+  p.ctx = a->num_context;
+  p.tgt = a->num_target;
+  p.total_q = a->total_q;
+  p.total_k = a->total_k;
+  p.bias_bstride = a->bias_batch_stride;
+  p.index_bytes = a->index_bytes;
+  p.batch = a->batch;
+  p.hq = a->heads_q;
+  p.hk = a->heads_k;
+  p.dqk = a->dim_qk;
+  p.dv = a->dim_v;
+  p.gqa_ratio = a->heads_q / a->heads_k;
+  p.mask_type = a->mask_type;
+  p.maxq = a->max_seq_len_q;
+  p.maxk = a->max_seq_len_k;
+  p.group = a->target_group_size;
+  p.scale = a->silu_scale == 0.0f ? 1.0f / static_cast<float>(a->max_seq_len_q) : a->silu_scale;
+  p.alpha = a->alpha;
+  p.flags = a->flags;
+  if (workspace) {
+    p.ws_header = static_cast<uint32_t*>(workspace);
+    p.items = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + hstu::kWsHeaderBytes);
+    p.item_capacity = workspace_bytes > hstu::kWsHeaderBytes
+                          ? static_cast<long long>((workspace_bytes - hstu::kWsHeaderBytes) / 8)
+                          : 0;
+  }
+  return p;
+}
+
+// Upper bound of the work-list length that needs no device data: every sequence adds at most one partial pair.
+long long item_bound(const HstuJaggedArgs* a) {
+  return static_cast<long long>(a->heads_q) * (a->total_q / hstu::kPairM + a->batch);
+}
+
+bool wants_tc(const HstuJaggedArgs* a, const hstu::KParams& p) {
+  return !(a->flags & HSTU_FLAG_FORCE_GENERIC) && hstu::tc_supported(p, a->dtype);
+}
+
+struct DeviceInfo {
+  int major = -1, sms = 0;
+};
+int device_info(DeviceInfo* out) {
+  static thread_local int cached_dev = -1;
+  static thread_local DeviceInfo cached;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(HSTU_E_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev != cached_dev) {
+    DeviceInfo d;
+    e = cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return fail(HSTU_E_CUDA, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+    cached = d;
+    cached_dev = dev;
+  }
+  *out = cached;
+  return HSTU_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int hstu_b200_version(void) { return 100; }
+
+const char* hstu_last_error(void) { return g_err; }
+
+int hstu_jagged_fwd_get_workspace_size(const HstuJaggedArgs* args, uint64_t* workspace_bytes) {
+  g_err[0] = 0;
+  if (!workspace_bytes) return fail(HSTU_E_NULL, "workspace_bytes is null");
+  int rc = validate(args);
+  if (rc) return rc;
+  const hstu::KParams p = to_params(args, nullptr, 0);
+  uint64_t bytes = hstu::kWsHeaderBytes;
+  if (wants_tc(args, p)) bytes += static_cast<uint64_t>(item_bound(args)) * 8;
+  *workspace_bytes = (bytes + 255) & ~static_cast<uint64_t>(255);
+  return HSTU_OK;
+}
+
+int hstu_jagged_fwd_kernel_kind(const HstuJaggedArgs* args) {
+  g_err[0] = 0;
+  int rc = validate(args);
+  if (rc) return rc;
+  const hstu::KParams p = to_params(args, nullptr, 0);
+  return wants_tc(args, p) ? 1 : 0;
+}
+
+int hstu_jagged_fwd(const HstuJaggedArgs* args, void* workspace, uint64_t workspace_bytes, void* stream_v) {
+  g_err[0] = 0;
+  int rc = validate(args);
+  if (rc) return rc;
+  rc = validate_pointers(args);
+  if (rc) return rc;
+  uint64_t need = 0;
+  rc = hstu_jagged_fwd_get_workspace_size(args, &need);
+  if (rc) return rc;
+  if (!workspace) return fail(HSTU_E_WORKSPACE, "workspace is null (%llu bytes needed)", (unsigned long long)need);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(HSTU_E_WORKSPACE, "workspace must be 256-byte aligned");
+  if (workspace_bytes < need)
+    return fail(HSTU_E_WORKSPACE, "workspace has %llu bytes, %llu needed", (unsigned long long)workspace_bytes,
+                (unsigned long long)need);
+  DeviceInfo dev;
+  rc = device_info(&dev);
+  if (rc) return rc;
+  if (dev.major != 10) return fail(HSTU_E_ARCH, "this library is built for sm_100a only; device has compute capability %d.x", dev.major);
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  hstu::KParams p = to_params(args, workspace, need);
+  const bool tc = wants_tc(args, p);
+  cudaError_t e = hstu::launch_prepass(p, tc, stream);
+  if (e != cudaSuccess) return fail(HSTU_E_CUDA, "pre-pass launch: %s", cudaGetErrorString(e));
+  if (args->total_q == 0) return HSTU_OK;
+  if (tc) {
+    e = hstu::launch_tc(p, args->dtype, dev.sms, stream);
+    if (e == cudaErrorNotSupported) return fail(HSTU_E_CUDA, "cuTensorMapEncodeTiled failed or is unavailable");
+  } else {
+    e = hstu::launch_generic(p, args->dtype, stream);
+  }
+  if (e != cudaSuccess) return fail(HSTU_E_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+  return HSTU_OK;
+}
+
+int hstu_jagged_fwd_status(const void* workspace, void* stream_v, uint32_t* status) {
+  g_err[0] = 0;
+  if (!workspace || !status) return fail(HSTU_E_NULL, "workspace / status is null");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  cudaError_t e = cudaMemcpyAsync(status, workspace, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return fail(HSTU_E_CUDA, "reading the status word: %s", cudaGetErrorString(e));
+  return HSTU_OK;
+}
+
+int64_t hstu_plan_host(const HstuJaggedArgs* args, const void* host_offset_q, const void* host_offset_k,
+                       const void* host_num_context, const void* host_num_target, uint32_t* items, int64_t capacity,
+                       uint32_t* status) {
+  g_err[0] = 0;
+  int rc = validate(args);
+  if (rc) return rc;
+  if (!host_offset_q) return fail(HSTU_E_NULL, "host_offset_q is null");
+  hstu::KParams p = to_params(args, nullptr, 0);
+  p.offq = host_offset_q;
+  p.offk = host_offset_k ? host_offset_k : host_offset_q;
+  p.ctx = host_num_context;
+  p.tgt = host_num_target;
+  return hstu::plan_host(p, items, items ? capacity : 0, status);
+}
+
+// Host evaluation of the device mask predicate and tile classifier (identical code, compiled for the host),
+// so that the CUDA-side mask logic can be checked against the reference's create_causal_mask without a GPU.
+int hstu_debug_mask_host(int32_t len_q, int32_t len_k, int32_t num_context, int32_t num_target,
+                         int32_t target_group_size, int32_t mask_type, uint8_t* out) {
+  if (!out || len_q < 0 || len_k < 0) return HSTU_E_PARAM;
+  hstu::SeqInfo s;
+  s.q0 = s.k0 = 0;
+  s.lq = len_q;
+  s.lk = len_k;
+  s.ctx = num_context;
+  s.tgt = num_target;
+  for (int i = 0; i < len_q; ++i) {
+    const hstu::RowBounds rb = hstu::row_bounds(s, i, mask_type, target_group_size);
+    for (int j = 0; j < len_k; ++j) out[static_cast<size_t>(i) * len_k + j] = hstu::allowed(rb, j) ? 1 : 0;
+  }
+  return HSTU_OK;
+}
+
+// For the q-tile of rows [r0, r0 + rows): number of K tiles of width bn to visit, and (bit t of full_bits,
+// t < 64) whether K tile t is classified "no predicate needed".
+int hstu_debug_tiles_host(int32_t len_q, int32_t len_k, int32_t num_context, int32_t num_target,
+                          int32_t target_group_size, int32_t mask_type, int32_t r0, int32_t rows, int32_t bn,
+                          uint64_t* full_bits) {
+  hstu::SeqInfo s;
+  s.q0 = s.k0 = 0;
+  s.lq = len_q;
+  s.lk = len_k;
+  s.ctx = num_context;
+  s.tgt = num_target;
+  const int n = hstu::kv_tiles_for_rows(s, r0, rows, mask_type, bn);
+  uint64_t bits = 0;
+  for (int t = 0; t < n && t < 64; ++t)
+    if (hstu::tile_is_full(s, r0, rows, t * bn, bn, mask_type, target_group_size)) bits |= 1ull << t;
+  if (full_bits) *full_bits = bits;
+  return n;
+}
+
+}  // extern "C"

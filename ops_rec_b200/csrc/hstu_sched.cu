@@ -1,0 +1,135 @@
+// Jagged tile scheduler: the device pre-pass that turns seq_offset into the work list of the tensor-core
+// kernel, and its host mirror.
+//
+// The reference splits work inside the kernel: every core walks all B offsets and takes an equal share of
+// the non-empty causal tiles, which can cut a q-block row between two cores and is why its output must be
+// zero-filled and accumulated atomically (…/op_kernel/atlas950/hstu_split_core_policy.h:53-214,
+// torch_extension/hstu_jagged_plugin.cpp:56-59).  Here a work item is a whole (sequence, head, 256-row q-pair):
+// nothing is ever split, so the output needs neither zero-fill nor atomics.
+//
+// Order of the list: sequences by number of q-pairs, longest first (a counting sort, stable in the sequence
+// index); inside a sequence head-major, and inside a head the q-pairs from the last (most K tiles) to the
+// first.  Persistent CTAs take items round-robin in a boustrophedon order, so each CTA gets a near-equal share
+// of the heavy head of the list, and the CTAs that run at the same time work on neighbouring q-pairs of the
+// same few (sequence, head) - their K/V stays in L2.
+#include "hstu_common.cuh"
+
+namespace hstu {
+
+constexpr int kMaxPairs = 20480 / kPairM;   // 80: max_seq_len is limited to 20480 like the reference
+constexpr int kBuckets = kMaxPairs + 1;
+constexpr int kPreThreads = 1024;
+
+__global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams p, const int build_items) {
+  __shared__ unsigned s_count[kBuckets];        // sequences per bucket
+  __shared__ unsigned s_start[kBuckets];        // first item of the bucket
+  __shared__ unsigned s_seen[kBuckets];         // sequences of the bucket placed by earlier chunks
+  __shared__ unsigned s_warp[32][kBuckets];     // per-warp counts of the current chunk, then exclusive prefix
+  __shared__ unsigned s_status;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  for (int i = tid; i < kBuckets; i += kPreThreads) {
+    s_count[i] = 0;
+    s_seen[i] = 0;
+  }
+  if (tid == 0) s_status = 0;
+  __syncthreads();
+
+  unsigned st = 0;
+  for (int b = tid; b < p.batch; b += kPreThreads) {
+    st |= check_seq(p, b);
+    if (build_items) {
+      const SeqInfo s = load_seq(p, b);
+      atomicAdd(&s_count[pairs_of(s.lq)], 1u);
+    }
+  }
+  if (st) atomicOr(&s_status, st);
+  __syncthreads();
+  if (tid == 0) {
+    p.ws_header[0] = s_status;
+    p.ws_header[2] = 0;
+    unsigned run = 0;
+    for (int key = kMaxPairs; key >= 1; --key) {
+      s_start[key] = run;
+      run += s_count[key] * static_cast<unsigned>(key) * static_cast<unsigned>(p.hq);
+    }
+    s_start[0] = run;
+    p.ws_header[1] = build_items ? run : 0u;
+  }
+  if (!build_items) return;
+  __syncthreads();
+
+  for (int base = 0; base < p.batch; base += kPreThreads) {
+    for (int i = tid; i < 32 * kBuckets; i += kPreThreads) (&s_warp[0][0])[i] = 0;
+    __syncthreads();
+    const int b = base + tid;
+    const bool live = b < p.batch;
+    int key = 0;
+    SeqInfo s;
+    if (live) {
+      s = load_seq(p, b);
+      key = pairs_of(s.lq);
+    }
+    // rank among the lanes of this warp that hold the same key (idle lanes use key -1 and are ignored)
+    const unsigned same = __match_any_sync(0xffffffffu, live ? key : -1);
+    const unsigned rank_in_warp = __popc(same & ((1u << lane) - 1u));
+    if (live && rank_in_warp == 0) s_warp[warp][key] = __popc(same);
+    __syncthreads();
+    if (tid < kBuckets) {
+      unsigned acc = s_seen[tid];
+      for (int w = 0; w < 32; ++w) {
+        const unsigned c = s_warp[w][tid];
+        s_warp[w][tid] = acc;
+        acc += c;
+      }
+      s_seen[tid] = acc;
+    }
+    __syncthreads();
+    if (live && key > 0) {
+      const unsigned rank = s_warp[warp][key] + rank_in_warp;
+      const long long first = static_cast<long long>(s_start[key]) +
+                              static_cast<long long>(rank) * key * p.hq;
+      for (int h = 0; h < p.hq; ++h) {
+        for (int pr = key - 1; pr >= 0; --pr) {
+          const long long at = first + static_cast<long long>(h) * key + (key - 1 - pr);
+          if (at < p.item_capacity) {
+            p.items[2 * at] = static_cast<uint32_t>(b);
+            p.items[2 * at + 1] = (static_cast<uint32_t>(h) << 16) | static_cast<uint32_t>(pr);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+cudaError_t launch_prepass(const KParams& p, bool build_items, cudaStream_t stream) {
+  hstu_prepass_kernel<<<1, kPreThreads, 0, stream>>>(p, build_items ? 1 : 0);
+  return cudaGetLastError();
+}
+
+// Host mirror of the ordering rule above, on host copies of the index arrays.
+long long plan_host(const KParams& p, uint32_t* items, long long capacity, uint32_t* status) {
+  unsigned st = 0;
+  long long n = 0;
+  for (int b = 0; b < p.batch; ++b) st |= check_seq(p, b);
+  for (int key = kMaxPairs; key >= 1; --key) {
+    for (int b = 0; b < p.batch; ++b) {
+      const SeqInfo s = load_seq(p, b);
+      if (pairs_of(s.lq) != key) continue;
+      for (int h = 0; h < p.hq; ++h) {
+        for (int pr = key - 1; pr >= 0; --pr) {
+          if (n < capacity && items) {
+            items[2 * n] = static_cast<uint32_t>(b);
+            items[2 * n + 1] = (static_cast<uint32_t>(h) << 16) | static_cast<uint32_t>(pr);
+          }
+          ++n;
+        }
+      }
+    }
+  }
+  if (status) *status = st;
+  return n;
+}
+
+}  // namespace hstu

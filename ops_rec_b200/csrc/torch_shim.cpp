@@ -1,0 +1,191 @@
+// torch operator registration for the HSTU jagged forward, dispatching into the C ABI (include/hstu_b200.h).
+//
+// Schema strings, argument defaults and argument normalisation are those of the reference adapter
+//   ascendc/attention/hstu_v1/torch_extension/hstu_jagged_plugin.cpp:22-67   (normalisation)
+//   …/hstu_jagged_plugin.cpp:140-161                                         (equal / delta wrappers)
+//   …/hstu_jagged_plugin.cpp:186-231                                         (schemas)
+//   …/hstu_jagged_plugin.cpp:269-282                                         (Meta implementation)
+// with the CUDA dispatch key in place of PrivateUse1.  As in the reference there is no C++ autograd key on
+// the forward.  Differences, all documented for users: the output is not zero-filled first (no atomics are
+// used, every row is written exactly once); batch may exceed 2048; attn_bias may be [H,S,S] or [1,H,S,S]
+// (shared by all sequences); fp8 inputs are rejected.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <torch/types.h>
+
+#include "hstu_b200.h"
+
+namespace {
+
+int dtype_code(at::ScalarType t) {
+  switch (t) {
+    case at::kBFloat16: return HSTU_DTYPE_BF16;
+    case at::kHalf: return HSTU_DTYPE_FP16;
+    case at::kFloat: return HSTU_DTYPE_FP32;
+    default: TORCH_CHECK(false, "hstu_jagged: dtype ", t, " is not supported (bf16, fp16, fp32)");
+  }
+}
+
+at::Tensor forward_impl(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                        const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& attn_bias,
+                        int64_t mask_type, int64_t max_seq_len_q, int64_t max_seq_len_k, double silu_scale,
+                        const at::Tensor& seq_offset, const at::Tensor& seq_offset_k,
+                        const c10::optional<at::Tensor>& num_context, const c10::optional<at::Tensor>& num_target,
+                        const c10::optional<int64_t>& target_group_size, const c10::optional<double>& alpha,
+                        bool deterministic) {
+  TORCH_CHECK(q.dim() == 3, "The q should be 3D in jagged layout");
+  TORCH_CHECK(k.dim() == 3 && v.dim() == 3, "The k and v should be 3D in jagged layout");
+  TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda() && seq_offset.is_cuda(),
+              "hstu_jagged: tensors must be CUDA tensors (there is no CPU implementation)");
+  TORCH_CHECK(seq_offset.scalar_type() == at::kInt || seq_offset.scalar_type() == at::kLong,
+              "seq_offset must be int32 or int64");
+  auto off_q = seq_offset.contiguous();
+  auto off_k = seq_offset_k.to(off_q.scalar_type()).contiguous();
+  TORCH_CHECK(off_q.size(0) >= 2, "acSeqOffset params error should have at least two element.");
+  TORCH_CHECK(off_k.size(0) >= 2, "acSeqOffsetK params error should have at least two element.");
+  TORCH_CHECK(off_k.size(0) == off_q.size(0), "seq_offset and seq_offset_k must have the same length");
+  TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type(),
+              "q, k and v must have the same dtype");
+  TORCH_CHECK(k.size(0) == v.size(0) && k.size(1) == v.size(1), "k and v must agree in tokens and heads");
+  TORCH_CHECK(k.size(2) == q.size(2), "q and k must have the same head dim");
+
+  c10::cuda::CUDAGuard guard(q.device());
+  auto dq = q.contiguous(), dk = k.contiguous(), dv = v.contiguous();
+  const int64_t batch = off_q.size(0) - 1;
+
+  HstuJaggedArgs a;
+  memset(&a, 0, sizeof(a));
+  a.struct_bytes = sizeof(a);
+  a.dtype = dtype_code(q.scalar_type());
+  a.q = dq.data_ptr();
+  a.k = dk.data_ptr();
+  a.v = dv.data_ptr();
+
+  at::Tensor bias, cmask, ctx, tgt;
+  if (attn_bias.has_value() && attn_bias->defined()) {
+    bias = attn_bias->to(q.scalar_type()).contiguous();
+    TORCH_CHECK(bias.dim() == 4 || bias.dim() == 3, "attn_bias must be [B,H,Sq,Sk] (or [H,Sq,Sk] shared by the batch)");
+    TORCH_CHECK(bias.size(-1) == max_seq_len_k && bias.size(-2) == max_seq_len_q && bias.size(-3) == q.size(1),
+                "attn_bias must be [.., heads_q, max_seq_len, max_seq_len_k]");
+    const bool shared = bias.dim() == 3 || bias.size(0) == 1;
+    TORCH_CHECK(shared || bias.size(0) >= batch, "attn_bias batch dimension is smaller than the batch");
+    a.attn_bias = bias.data_ptr();
+    a.bias_batch_stride = shared ? 0 : bias.size(1) * bias.size(2) * bias.size(3);
+  }
+  if (mask.has_value() && mask->defined() && mask_type == HSTU_MASK_CUSTOM) {
+    cmask = mask->to(q.scalar_type()).contiguous();
+    TORCH_CHECK(cmask.dim() == 4 && cmask.size(0) >= batch && cmask.size(1) == q.size(1) &&
+                    cmask.size(2) == max_seq_len_q && cmask.size(3) == max_seq_len_k,
+                "mask must be [B, heads_q, max_seq_len, max_seq_len_k]");
+    a.mask = cmask.data_ptr();
+  }
+  a.seq_offset_q = off_q.data_ptr();
+  a.seq_offset_k = off_k.data_ptr();
+  a.index_bytes = static_cast<int32_t>(off_q.element_size());
+  if (num_context.has_value() && num_context->defined()) {
+    ctx = num_context->to(off_q.device(), off_q.scalar_type()).contiguous();
+    TORCH_CHECK(ctx.numel() >= batch, "num_context is shorter than the batch");
+    a.num_context = ctx.data_ptr();
+  }
+  if (num_target.has_value() && num_target->defined()) {
+    tgt = num_target->to(off_q.device(), off_q.scalar_type()).contiguous();
+    TORCH_CHECK(tgt.numel() >= batch, "num_target is shorter than the batch");
+    a.num_target = tgt.data_ptr();
+  }
+  a.batch = static_cast<int32_t>(batch);
+  a.total_q = dq.size(0);
+  a.total_k = dk.size(0);
+  a.heads_q = static_cast<int32_t>(dq.size(1));
+  a.heads_k = static_cast<int32_t>(dk.size(1));
+  a.dim_qk = static_cast<int32_t>(dq.size(2));
+  a.dim_v = static_cast<int32_t>(dv.size(2));
+  a.mask_type = static_cast<int32_t>(mask_type);
+  // range checks with the reference's messages happen inside the C ABI; keep int32 conversion safe here
+  TORCH_CHECK(max_seq_len_q >= 1 && max_seq_len_q <= 20480, "maxSeqLen expect in [1, 20480], but value is ", max_seq_len_q);
+  TORCH_CHECK(max_seq_len_k >= 1 && max_seq_len_k <= 20480, "maxSeqLenK expect in [1, 20480], but value is ", max_seq_len_k);
+  a.max_seq_len_q = static_cast<int32_t>(max_seq_len_q);
+  a.max_seq_len_k = static_cast<int32_t>(max_seq_len_k);
+  a.target_group_size = static_cast<int32_t>(target_group_size.value_or(0));
+  a.silu_scale = static_cast<float>(silu_scale);
+  a.alpha = static_cast<float>(alpha.value_or(1.0));
+  a.flags = deterministic ? HSTU_FLAG_DETERMINISTIC : 0u;
+  if (mask_type == HSTU_MASK_CUSTOM && !a.mask) {
+    // let the C ABI produce the reference's message
+    a.mask = nullptr;
+  }
+
+  auto out = at::empty({dq.size(0), dq.size(1), dv.size(2)}, dq.options());
+  a.out = out.data_ptr();
+
+  uint64_t ws_bytes = 0;
+  int rc = hstu_jagged_fwd_get_workspace_size(&a, &ws_bytes);
+  TORCH_CHECK(rc == 0, "hstu_jagged: ", hstu_last_error());
+  auto ws = at::empty({static_cast<int64_t>(ws_bytes)}, dq.options().dtype(at::kByte));
+  rc = hstu_jagged_fwd(&a, ws.data_ptr(), ws_bytes, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "hstu_jagged: ", hstu_last_error());
+  return out;
+}
+
+at::Tensor hstu_jagged_equal(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                             const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& attn_bias,
+                             int64_t mask_type, int64_t max_seq_len, double silu_scale, const at::Tensor& seq_offset,
+                             const c10::optional<at::Tensor>& num_context, const c10::optional<at::Tensor>& num_target,
+                             c10::optional<int64_t> target_group_size, c10::optional<double> alpha, bool deterministic) {
+  return forward_impl(q, k, v, mask, attn_bias, mask_type, max_seq_len, max_seq_len, silu_scale, seq_offset, seq_offset,
+                      num_context, num_target, target_group_size, alpha, deterministic);
+}
+
+at::Tensor hstu_jagged_delta(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                             const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& attn_bias,
+                             int64_t mask_type, int64_t max_seq_len, int64_t max_seq_len_k, double silu_scale,
+                             const at::Tensor& seq_offset, const at::Tensor& seq_offset_k,
+                             const c10::optional<at::Tensor>& num_context, const c10::optional<at::Tensor>& num_target,
+                             c10::optional<int64_t> target_group_size, c10::optional<double> alpha, bool deterministic) {
+  return forward_impl(q, k, v, mask, attn_bias, mask_type, max_seq_len, max_seq_len_k, silu_scale, seq_offset,
+                      seq_offset_k, num_context, num_target, target_group_size, alpha, deterministic);
+}
+
+at::Tensor meta_out(const at::Tensor& q, const at::Tensor& v) {
+  TORCH_CHECK(q.dim() == 3, "The q should be 3D in jagged layout");
+  std::vector<c10::SymInt> shape = {q.sym_size(0), q.sym_size(1), v.sym_size(2)};
+  return at::empty_symint(shape, q.options().device(c10::kMeta));
+}
+
+at::Tensor hstu_jagged_equal_meta(const at::Tensor& q, const at::Tensor&, const at::Tensor& v,
+                                  const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&, int64_t, int64_t,
+                                  double, const at::Tensor&, const c10::optional<at::Tensor>&,
+                                  const c10::optional<at::Tensor>&, c10::optional<int64_t>, c10::optional<double>, bool) {
+  return meta_out(q, v);
+}
+
+at::Tensor hstu_jagged_delta_meta(const at::Tensor& q, const at::Tensor&, const at::Tensor& v,
+                                  const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&, int64_t, int64_t,
+                                  int64_t, double, const at::Tensor&, const at::Tensor&,
+                                  const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&,
+                                  c10::optional<int64_t>, c10::optional<double>, bool) {
+  return meta_out(q, v);
+}
+
+}  // namespace
+
+TORCH_LIBRARY_FRAGMENT(ops_rec, m) {
+  m.def("hstu_jagged.equal(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, "
+        "int mask_type=0, int max_seq_len=0, float silu_scale=0.0, Tensor seq_offset=None, "
+        "Tensor? num_context=None, Tensor? num_target=None, int? target_group_size=0, float? alpha=1.0, "
+        "bool deterministic=False) -> Tensor");
+  m.def("hstu_jagged.delta(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, "
+        "int mask_type=0, int max_seq_len=0, int max_seq_len_k=0, float silu_scale=0.0, Tensor seq_offset=None, "
+        "Tensor seq_offset_k=None, Tensor? num_context=None, Tensor? num_target=None, int? target_group_size=0, "
+        "float? alpha=1.0, bool deterministic=False) -> Tensor");
+}
+
+TORCH_LIBRARY_IMPL(ops_rec, CUDA, m) {
+  m.impl("hstu_jagged.equal", TORCH_FN(hstu_jagged_equal));
+  m.impl("hstu_jagged.delta", TORCH_FN(hstu_jagged_delta));
+}
+
+TORCH_LIBRARY_IMPL(ops_rec, Meta, m) {
+  m.impl("hstu_jagged.equal", TORCH_FN(hstu_jagged_equal_meta));
+  m.impl("hstu_jagged.delta", TORCH_FN(hstu_jagged_delta_meta));
+}

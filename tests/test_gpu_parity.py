@@ -1,0 +1,253 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the CPU oracle and the committed fixtures.
+
+The grid follows the reference's own forward test (hstu_forward_v1/test/pytest/test_hstu_jagged.py:227-491):
+shapes x bias on/off x dtype x mask variants, the ctx/target boundary values, GQA, padded offsets, int32/int64
+offsets, dqk != dv, delta (q shorter than k).
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import hstu_oracle as O
+from ops_rec_b200 import cabi
+from tests._parity import assert_parity, run_cabi, to_cuda
+from tests._util import fixture_call_args, fixture_names, load_fixture, make_case
+
+pytestmark = pytest.mark.gpu
+
+BF16, FP16, FP32 = torch.bfloat16, torch.float16, torch.float32
+
+
+@pytest.mark.parametrize("name", fixture_names())
+def test_fixtures_from_the_reference_goldens(name):
+    fx = load_fixture(name)
+    args = fixture_call_args(fx)
+    out, status = run_cabi(args)
+    assert status == 0
+    ref = fx["out_v2_fp32"]
+    if args["q"].dtype == FP32:
+        torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+    else:
+        torch.testing.assert_close(out.float(), ref, rtol=1e-2, atol=1e-2)
+        ok, detail = O.double_reference_ok(out, fx["out_v2_lowp"], ref, multiplier=5)
+        assert ok, detail
+    assert_parity(out, args, label=name)
+
+
+MASKS = [dict(mask_type=2), dict(custom_mask=True), dict(ctx=0, tgt=30, g=1), dict(ctx=0, tgt=30, g=3),
+         dict(ctx=6, tgt=0, g=1), dict(ctx=6, tgt=0, g=3), dict(ctx=6, tgt=30, g=1), dict(ctx=6, tgt=30, g=3),
+         dict()]
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 15, 16), (16, 4, 1024, 128), (1, 4, 1024, 16), (16, 2, 15, 128),
+                                   (8, 4, 600, 64)])
+@pytest.mark.parametrize("bias", [None, "batch"])
+@pytest.mark.parametrize("dtype", [FP32, FP16, BF16])
+def test_reference_grid_causal(shape, bias, dtype):
+    B, H, maxL, D = shape
+    if dtype == FP32 and maxL * B > 4096:
+        B = 4
+    args = make_case(B, H, H, D, D, 1, maxL, dtype, seed=B + maxL, rab=bias)
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label=f"{shape} {bias} {dtype}")
+
+
+@pytest.mark.parametrize("mask", MASKS)
+@pytest.mark.parametrize("D,dtype", [(128, BF16), (64, FP16), (32, FP32)])
+def test_mask_variants(mask, D, dtype):
+    mask = dict(mask)
+    args = make_case(4, 2, 2, D, D, 1, 330, dtype, seed=7, rab="batch", **mask)
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label=f"{mask} d{D} {dtype}")
+
+
+@pytest.mark.parametrize("ctx", [255, 256, 257])
+@pytest.mark.parametrize("tgt", [511, 512])
+def test_ctx_target_boundaries(ctx, tgt):
+    args = make_case(2, 2, 2, 128, 128, 1, 200, BF16, seed=ctx + tgt, ctx=ctx, tgt=tgt, g=1)
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label=f"ctx{ctx} tgt{tgt}")
+
+
+@pytest.mark.parametrize("L", [1, 15, 127, 128, 129, 255, 256, 257, 383, 384, 385, 512, 513])
+@pytest.mark.parametrize("D", [64, 128])
+def test_ragged_tails_single_sequence(L, D):
+    # make_case adds ctx + tgt to the base length
+    args = make_case(1, 2, 2, D, D, L - min(3, L - 1), L - min(3, L - 1), BF16, seed=L, rab="batch",
+                     tgt=min(3, L - 1), g=1)
+    assert int(args["seq_offset"][-1]) == L
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label=f"L{L} d{D}")
+
+
+@pytest.mark.parametrize("Hq,Hk", [(8, 8), (8, 4), (8, 2), (8, 1)])
+@pytest.mark.parametrize("dtype,D", [(BF16, 128), (FP32, 16)])
+def test_gqa(Hq, Hk, dtype, D):
+    args = make_case(3, Hq, Hk, D, D, 1, 300, dtype, seed=Hk, rab="batch")
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label=f"gqa {Hq}:{Hk}")
+
+
+@pytest.mark.parametrize("dtype", [BF16, FP32])
+def test_dqk_differs_from_dv(dtype):
+    args = make_case(3, 2, 2, 64, 128, 1, 200, dtype, seed=5, rab="batch", tgt=5, g=1)
+    out, status = run_cabi(args)
+    assert status == 0 and out.shape[-1] == 128
+    assert_parity(out, args, label="dqk64 dv128")
+
+
+@pytest.mark.parametrize("dtype,D", [(BF16, 128), (BF16, 64), (FP32, 32)])
+def test_delta_q_shorter_than_k(dtype, D):
+    args = make_case(5, 2, 2, D, D, 1, 400, dtype, seed=11, rab="batch", delta=True)
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label=f"delta d{D}")
+    args = make_case(5, 2, 2, D, D, 20, 400, dtype, seed=12, delta=True, tgt=9, g=2, ctx=3)
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label=f"delta ctx/target d{D}")
+
+
+@pytest.mark.parametrize("index_dtype", [torch.int32, torch.int64])
+def test_padded_and_empty_offsets(index_dtype):
+    args = make_case(6, 4, 4, 128, 128, 1, 500, BF16, seed=21, rab="batch", index_dtype=index_dtype)
+    base, status = run_cabi(args)
+    assert status == 0
+    assert_parity(base, args, label="base")
+    off = args["seq_offset"]
+    # repeated last offset (the reference pads like this, test_hstu_jagged.py:58-61) and an empty sequence
+    padded = torch.cat([off, off[-1:], off[-1:]])
+    bias = torch.cat([args["attn_bias"], args["attn_bias"][:2]])
+    out, status = run_cabi(dict(args, seq_offset=padded, seq_offset_k=padded, attn_bias=bias))
+    assert status == 0 and torch.equal(out, base)
+    mid = torch.cat([off[:3], off[2:]])
+    bias = torch.cat([args["attn_bias"][:2], args["attn_bias"][:1], args["attn_bias"][2:]])
+    out, status = run_cabi(dict(args, seq_offset=mid, seq_offset_k=mid, attn_bias=bias))
+    assert status == 0 and torch.equal(out, base)
+
+
+@pytest.mark.parametrize("form", ["shared3", "shared4"])
+def test_bias_shared_by_the_batch(form):
+    args = make_case(5, 4, 4, 64, 64, 1, 300, BF16, seed=3, rab=form, tgt=7, g=1)
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label=form)
+    S = args["max_seq_len"]
+    dense = args["attn_bias"].reshape(1, 4, S, S).expand(5, -1, -1, -1).contiguous()
+    out2, _ = run_cabi(dict(args, attn_bias=dense))
+    assert torch.equal(out, out2)
+
+
+def test_bias_with_odd_max_seq_len_takes_the_scalar_load_path():
+    args = make_case(3, 2, 2, 128, 128, 1, 299, BF16, seed=9, rab="batch", max_seq_len=301)
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label="maxL 301")
+
+
+def test_alpha_before_bias_flag_and_default_order():
+    args = make_case(2, 2, 2, 128, 128, 50, 300, BF16, seed=2, rab="batch")
+    args["alpha"] = 0.05
+    out, _ = run_cabi(args)
+    assert_parity(out, args, label="alpha after bias")
+    out2, _ = run_cabi(args, flags=cabi.FLAG_ALPHA_BEFORE_BIAS)
+    ref2 = O.hstu_jagged_forward(**args, round_p=False, out_dtype=torch.float32, alpha_before_bias=True)
+    torch.testing.assert_close(out2.float(), ref2, rtol=1e-2, atol=1e-2)
+    assert (out2.float() - ref2).abs().max() <= 2e-2 * ref2.abs().max()
+    assert (out.float() - ref2).abs().max() > 5e-2 * ref2.abs().max()
+
+
+def test_explicit_silu_scale_and_deterministic_flag():
+    args = make_case(3, 2, 2, 64, 64, 1, 257, BF16, seed=4)
+    args["silu_scale"] = 0.125
+    out, _ = run_cabi(args)
+    assert_parity(out, args, label="silu_scale")
+    out2, _ = run_cabi(args, deterministic=True)
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("D,dtype", [(128, BF16), (64, BF16), (128, FP16)])
+def test_tensor_core_and_generic_kernels_agree(D, dtype):
+    args = make_case(6, 4, 2, D, D, 1, 700, dtype, seed=13, rab="batch", tgt=20, g=2, ctx=4)
+    a, _ = cabi.make_args(args["q"], args["k"], args["v"], None, args["seq_offset"], max_seq_len=args["max_seq_len"])
+    assert cabi.kernel_kind(a) == 1
+    tc, st1 = run_cabi(args)
+    gen, st2 = run_cabi(args, flags=cabi.FLAG_FORCE_GENERIC)
+    assert st1 == 0 and st2 == 0
+    assert_parity(tc, args, label="tc")
+    assert_parity(gen, args, label="generic")
+    scale = gen.float().abs().max()
+    assert (tc.float() - gen.float()).abs().max() <= 2e-2 * scale
+
+
+def test_results_are_bitwise_reproducible():
+    args = make_case(8, 4, 4, 128, 128, 1, 900, BF16, seed=17, rab="batch")
+    a, _ = run_cabi(args)
+    for _ in range(3):
+        b, _ = run_cabi(args)
+        assert torch.equal(a, b)
+
+
+def test_output_rows_outside_the_call_are_untouched():
+    args = to_cuda(make_case(5, 2, 2, 128, 128, 1, 300, BF16, seed=19))
+    T = args["q"].shape[0]
+    pad = 64
+    buf = torch.full((T + 2 * pad, 2, 128), 7.0, dtype=BF16, device="cuda")
+    out = buf[pad:pad + T]
+    cabi.hstu_jagged_forward(**args, out=out)
+    torch.cuda.synchronize()
+    assert (buf[:pad] == 7.0).all() and (buf[pad + T:] == 7.0).all()
+    assert_parity(out.cpu(), {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in args.items()})
+
+
+def test_inconsistent_inputs_set_the_status_word_and_never_fault():
+    args = make_case(4, 2, 2, 128, 128, 10, 300, BF16, seed=23, rab="batch", tgt=5, g=1)
+    off = args["seq_offset"].clone()
+    bad = off.clone()
+    bad[2] = bad[1] - 3                                     # not monotone
+    _, status = run_cabi(dict(args, seq_offset=bad, seq_offset_k=bad))
+    assert status & cabi.ST_BAD_OFFSETS
+    _, status = run_cabi(dict(args, max_seq_len=8, max_seq_len_k=8, attn_bias=None))
+    assert status & cabi.ST_LEN_GT_MAX
+    big = torch.full_like(args["num_target"], 10_000)
+    _, status = run_cabi(dict(args, num_target=big))
+    assert status & cabi.ST_BAD_CTX_TARGET
+    past = off.clone()
+    past[-1] += 1000                                        # points past the end of q
+    _, status = run_cabi(dict(args, seq_offset=past, seq_offset_k=past))
+    assert status & cabi.ST_BAD_OFFSETS
+    out, status = run_cabi(args)                            # the context is still healthy
+    assert status == 0
+    assert_parity(out, args, label="after bad inputs")
+
+
+def test_device_work_list_equals_host_plan():
+    args = to_cuda(make_case(37, 4, 4, 128, 128, 1, 1500, BF16, seed=29))
+    out = torch.empty_like(args["q"])
+    a, keep = cabi.make_args(args["q"], args["k"], args["v"], out, args["seq_offset"],
+                             max_seq_len=args["max_seq_len"], alpha=args["alpha"])
+    n = cabi.workspace_size(a)
+    ws = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    cabi.check(cabi.load().hstu_jagged_fwd(C.byref(a), ws.data_ptr(), n, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    header = ws[:16].cpu().numpy().view(np.uint32)
+    items_dev = ws[256:].cpu().numpy().view(np.uint32).reshape(-1, 2)[: header[1]]
+    items_host, status = cabi.plan_host(args["seq_offset"].cpu().numpy(), 4, max_seq_len=args["max_seq_len"])
+    assert header[0] == 0 and status == 0
+    assert header[1] == len(items_host)
+    assert np.array_equal(items_dev, items_host)
+
+
+def test_large_batch_beyond_the_reference_limit():
+    # the reference caps the batch at 2048 (tiling_policy_define.h:107); here it may be larger
+    args = make_case(3000, 2, 2, 64, 64, 1, 40, BF16, seed=31)
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label="B3000")
