@@ -1,0 +1,324 @@
+#!/usr/bin/env python
+"""Benchmark of the HSTU jagged attention forward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg4] [--impl reference]
+
+A step is one call of the operator (scheduler pre-pass + attention kernel) over one synthetic jagged batch.
+The default workload is the long-sequence batch ("cfg4": B=256, H=8, d=128, lognormal lengths up to 8192, bf16);
+with N GPUs its sequences are split over the ranks by a FLOP-balanced partition, one process per GPU, no
+collective on the data path (total work fixed => "scaling": "strong").  Rank 0 prints one JSON line:
+
+  value        useful TFLOP/s over all ranks, inputs resident in HBM, CUDA events, max over ranks
+  e2e          same metric through the torch operator with HOST (pinned) inputs and a host copy of the result,
+               copies inside the timed region
+  roofline     the attention kernel against the measured dense-bf16 peak (MEASURED_PEAKS.json)
+  cpu_baseline the CPU oracle (a port of the reference's PyTorch golden) on this box's cores, bounded sample
+  clocks       SM clock and throttle reasons sampled during the timed region
+
+`--impl reference` times that CPU port alone (rank 0 only) and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "hstu_jagged_fwd_causal_tflops"
+UNIT = "TFLOP/s"
+
+WORKLOAD_DESC = {
+    "cfg2": "cfg2: B=32 H=4 d=128 bf16, L~U[256,1024], max_seq_len=1024, causal, no rab",
+    "cfg3": "cfg3: cfg2 + rab [32,4,1024,1024] bf16 + num_target~U[0,32] (group 1)",
+    "cfg4": "cfg4: B=256 H=8 d=128 bf16, L~lognormal(ln2048,0.6) in [64,8192], max_seq_len=8192, causal, no rab",
+    "cfg5": "cfg5: B=4096 H=4 d=64 bf16, L~lognormal(ln200,0.8) in [8,2048], shared rab [4,2048,2048], "
+            "num_target~U[1,64] (group 1)",
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(tflops_burst=p["bf16_tflops"], tflops_sustained=p["bf16_tflops_sustained"], hbm=p["hbm_gbs"],
+                    source="measured")
+    return dict(tflops_burst=1590.0, tflops_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and clock-event reasons of one GPU through NVML (read-only) while the timed region runs."""
+
+    REASONS = {
+        0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+        0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
+    }
+
+    def __init__(self, index, period=0.02):
+        self.samples, self.mask, self.max_mhz = [], 0, None
+        self._stop = threading.Event()
+        self._thread = None
+        self.period = period
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                ids = [v.strip() for v in visible.split(",") if v.strip()]
+                if index < len(ids) and ids[index].isdigit():
+                    phys = int(ids[index])
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.mask |= int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        reasons = [name for bit, name in self.REASONS.items() if self.mask & bit and name != "gpu_idle"]
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+def cpu_oracle_sample(w, seconds_target=15.0):
+    """Time the CPU oracle (torch, all host threads) on a length-stratified sample of the workload's sequences.
+    Returns (tflops, tokens_per_s, description, cores, seconds)."""
+    import numpy as np
+    import torch
+
+    from oracle import hstu_oracle as O
+    from ops_rec_b200 import workloads as W
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    order = np.argsort(w.lengths, kind="stable")
+    # start with ~8 sequences spread over the length distribution; grow while the sample stays cheap
+    n = min(8, len(order))
+    picks = order[np.linspace(0, len(order) - 1, n).round().astype(int)]
+    sub = w.subset(np.unique(picks), name=w.name + "-sample")
+    kw = W.materialize(sub, "cpu")
+    t0 = time.perf_counter()
+    O.hstu_jagged_forward(**kw)
+    dt = time.perf_counter() - t0
+    reps = 1
+    # repeat the same sample to fill the time budget (bounded), keep the best rate
+    while dt * (reps + 1) < seconds_target and reps < 5:
+        t1 = time.perf_counter()
+        O.hstu_jagged_forward(**kw)
+        dt = min(dt, time.perf_counter() - t1)
+        reps += 1
+    desc = (f"{sub.batch} of {w.batch} sequences of {w.name} (length-stratified, {sub.tokens} tokens, "
+            f"{sub.flops() / 1e9:.1f} GFLOP), torch fp32 CPU oracle, best of {reps}")
+    return sub.flops() / dt / 1e12, sub.tokens / dt, desc, torch.get_num_threads(), dt
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    from ops_rec_b200 import workloads as W
+
+    w = W.make_workload(args.workload)
+    vals, toks = [], []
+    desc, cores = "", 0
+    t_all = time.perf_counter()
+    for i in range(args.warmup + args.steps):
+        tf, tk, desc, cores, dt = cpu_oracle_sample(w, seconds_target=0.0)
+        if i >= args.warmup:
+            vals.append((tf, tk, dt))
+        if time.perf_counter() - t_all > 240:  # keep the whole run within minutes
+            break
+    if not vals:
+        vals = [(tf, tk, dt)]
+    tf = statistics.median(v[0] for v in vals)
+    tk = statistics.median(v[1] for v in vals)
+    ms = statistics.median(v[2] for v in vals) * 1e3
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus, "steps": len(vals),
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "tokens_per_s": tk,
+        "config": {"workload": WORKLOAD_DESC[args.workload], "step": "bounded sample: " + desc},
+        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="cfg4", choices=sorted(WORKLOAD_DESC))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import ops_rec_b200 as ops_rec
+    from ops_rec_b200 import cabi
+    from ops_rec_b200 import workloads as W
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    full = W.make_workload(args.workload)
+    parts = W.partition_lpt(full.lengths, world)
+    mine = full.subset(parts[rank])
+    flop_imb, tok_imb = W.imbalance(full.lengths, parts)
+    kw = W.materialize(mine, dev, seed=1 + rank)
+    hj = ops_rec.ascendc.attention.hstu_jagged
+
+    def step():
+        return hj(kw["q"], kw["k"], kw["v"], None, kw["attn_bias"], 0, kw["max_seq_len"], 0.0, kw["seq_offset"],
+                  None, kw["num_target"], kw["target_group_size"], kw["alpha"])
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        out = step()
+    barrier()
+
+    # ---- device-resident timing: K steps, one event pair per step on the launching stream
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        for i in range(args.steps):
+            starts[i].record()
+            out = step()
+            ends[i].record()
+        barrier()
+    total_ms = starts[0].elapsed_time(ends[-1])
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms_max = float(t.item())
+
+    # status word of a launch through the C ABI (0 = consistent inputs, no bounded wait gave up)
+    _, status = cabi.hstu_jagged_forward(
+        kw["q"], kw["k"], kw["v"], None, kw["attn_bias"], 0, kw["max_seq_len"], 0.0, kw["seq_offset"], None,
+        kw["num_target"], kw["target_group_size"], kw["alpha"], return_status=True)
+    assert status == 0, f"device status word {status:#x}"
+
+    # ---- end-to-end: pinned host inputs -> device -> operator -> pinned host result, all inside the timed region
+    host_in = {k: v.cpu().pin_memory() for k, v in kw.items() if isinstance(v, torch.Tensor)}
+    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h2d = sum(v.numel() * v.element_size() for v in host_in.values())
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step():
+        d = {k: v.to(dev, non_blocking=True) for k, v in host_in.items()}
+        o = hj(d["q"], d["k"], d["v"], None, d.get("attn_bias"), 0, kw["max_seq_len"], 0.0, d["seq_offset"], None,
+               d.get("num_target"), kw["target_group_size"], kw["alpha"])
+        host_out.copy_(o, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / args.e2e_steps
+
+    if rank == 0:
+        peaks = load_peaks()
+        ms_per_step = total_ms_max / args.steps
+        value = full.flops() / (ms_per_step * 1e-3) / 1e12
+        # roofline of the attention kernel on this rank: useful FLOPs of this rank's launch / its mean duration
+        # (event pairs enclose pre-pass + attention kernel of one call; the pre-pass is a few microseconds)
+        k_ms = statistics.mean(step_ms)
+        achieved = mine.flops() / (k_ms * 1e-3) / 1e12
+        sustained = total_ms_max > 500.0
+        peak = peaks["tflops_sustained"] if sustained else peaks["tflops_burst"]
+        hbm_gbs = mine.bytes() / (k_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": full.dtype, "data": "synthetic",
+            "config": {
+                "workload": WORKLOAD_DESC[args.workload], "tokens": full.tokens, "useful_flops": full.flops(),
+                "partition": f"LPT by L(L+1) over {world} rank(s); max/mean FLOPs {flop_imb:.4f}, tokens {tok_imb:.4f}",
+                "l2": f"inputs+output of a step are {mine.bytes() / 1e6:.0f} MB per rank "
+                      + ("(larger than the 126 MB L2; no flush)" if mine.bytes() > 2 * 126e6 else "(L2-resident: warm number)"),
+            },
+            "tokens_per_s": full.tokens / (ms_per_step * 1e-3),
+            "frac_of_bf16_peak": value / (world * peak),
+            "roofline": {
+                "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": None, "peak_kind": ("sustained" if sustained else "burst") + " of " + peaks["source"],
+                "kernel": "hstu_tc_kernel", "kernel_ms": k_ms, "algorithmic_flops_per_launch": mine.flops(),
+                "hbm_gbs_algorithmic": hbm_gbs, "hbm_frac": hbm_gbs / peaks["hbm"],
+            },
+            "e2e": {"value": full.flops() / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.e2e_steps},
+            "gpu_launches": 2 * args.steps,
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            tf, tk, desc, cores, _ = cpu_oracle_sample(full)
+            line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc,
+                                    "tokens_per_s": tk}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
