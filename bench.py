@@ -148,6 +148,9 @@ def run_reference(args, rank):
     from ops_rec_b200 import workloads as W
 
     w = W.make_workload(args.workload)
+    if args.max_batch:
+        import numpy as np
+        w = w.subset(np.arange(min(args.max_batch, w.batch)))
     vals, toks = [], []
     desc, cores = "", 0
     t_all = time.perf_counter()
@@ -183,6 +186,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--max-batch", type=int, default=0,
+                    help="keep only the first N sequences of the workload (small cases for profiler captures)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -213,6 +218,8 @@ def main():
         torch.cuda.synchronize()
 
     full = W.make_workload(args.workload)
+    if args.max_batch:
+        full = full.subset(np.arange(min(args.max_batch, full.batch)))
     parts = W.partition_lpt(full.lengths, world)
     mine = full.subset(parts[rank])
     flop_imb, tok_imb = W.imbalance(full.lengths, parts)
@@ -292,7 +299,8 @@ def main():
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": full.dtype, "data": "synthetic",
             "config": {
-                "workload": WORKLOAD_DESC[args.workload], "tokens": full.tokens, "useful_flops": full.flops(),
+                "workload": WORKLOAD_DESC[args.workload] + (f" (first {full.batch} sequences only)" if args.max_batch else ""),
+                "tokens": full.tokens, "useful_flops": full.flops(),
                 "partition": f"LPT by L(L+1) over {world} rank(s); max/mean FLOPs {flop_imb:.4f}, tokens {tok_imb:.4f}",
                 "l2": f"inputs+output of a step are {mine.bytes() / 1e6:.0f} MB per rank "
                       + ("(larger than the 126 MB L2; no flush)" if mine.bytes() > 2 * 126e6 else "(L2-resident: warm number)"),

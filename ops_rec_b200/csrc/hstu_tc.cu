@@ -68,11 +68,14 @@ struct Waiter {
   int* abort_flag;
   uint32_t* status;
   __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity) const {
-    if (*reinterpret_cast<volatile int*>(abort_flag)) return;
     if (ptx::mbar_try_wait(bar, parity)) return;
+    if (*reinterpret_cast<volatile int*>(abort_flag)) return;
     const long long t0 = clock64();
     unsigned spins = 0;
     while (!ptx::mbar_try_wait(bar, parity)) {
+#ifdef HSTU_EXP_SLEEP
+      __nanosleep(HSTU_EXP_SLEEP);
+#endif
       if ((++spins & 0x3ffu) == 0) {
         if (*reinterpret_cast<volatile int*>(abort_flag)) return;
         if (clock64() - t0 > kWaitLimitCycles) {
@@ -85,11 +88,21 @@ struct Waiter {
   }
 };
 
+#ifdef HSTU_PROF
+__device__ unsigned long long g_prof[160][24];
+#define PROF_T0(var) const long long var = clock64()
+#define PROF_ADD(slot, var) prof_acc[slot] += clock64() - (var)
+#else
+#define PROF_T0(var)
+#define PROF_ADD(slot, var)
+#endif
+
 struct Item {
   SeqInfo s;
   int b, h, hk, r0;
-  int n[2];   // K tiles each Q tile visits
+  int n0, n1;  // K tiles each of the two Q tiles visits
   int nmax;
+  __device__ __forceinline__ int n(int t) const { return t == 0 ? n0 : n1; }
 };
 
 __device__ __forceinline__ Item load_item(const KParams& p, long long idx) {
@@ -100,9 +113,9 @@ __device__ __forceinline__ Item load_item(const KParams& p, long long idx) {
   it.hk = it.h / p.gqa_ratio;
   it.r0 = static_cast<int>(hp & 0xffffu) * kPairM;
   it.s = load_seq(p, it.b);
-  it.n[0] = kv_tiles_for_rows(it.s, it.r0, kTileM, p.mask_type, kTileN);
-  it.n[1] = kv_tiles_for_rows(it.s, it.r0 + kTileM, kTileM, p.mask_type, kTileN);
-  it.nmax = it.n[0] > it.n[1] ? it.n[0] : it.n[1];
+  it.n0 = kv_tiles_for_rows(it.s, it.r0, kTileM, p.mask_type, kTileN);
+  it.n1 = kv_tiles_for_rows(it.s, it.r0 + kTileM, kTileM, p.mask_type, kTileN);
+  it.nmax = it.n0 > it.n1 ? it.n0 : it.n1;
   return it;
 }
 
@@ -134,15 +147,92 @@ template <> struct Pack<__half> {
   }
 };
 
-// silu(y) * scale with a = y / 2:  a*scale*(1 + tanh(a))  (one MUFU op per element)
-__device__ __forceinline__ float silu_scaled_tanh(float a, float scale) {
-  const float r = a * scale;
-  return fmaf(r, ptx::tanh_approx(a), r);
+struct BiasRow {
+  const void* base;     // attn_bias
+  long long row;        // element offset of (b, h, i, 0)
+  bool row_ok;          // row i exists in the sequence
+  bool vec_ok;          // 16-byte loads are aligned
+  int maxk, lk;
+};
+
+// 32 consecutive bias values of one row, starting at column jb, as fp32 (0 beyond the sequence).
+template <typename T>
+__device__ __forceinline__ void load_bias32(const BiasRow& br, int jb, float (&bv)[32]) {
+  if (br.row_ok && br.vec_ok && jb + 32 <= br.maxk) {
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(br.base) + br.row + jb);
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const uint4 u = __ldg(src + q4);
+      const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = Pack<T>::unpack(uu[e]);
+        bv[q4 * 8 + e * 2] = f.x;
+        bv[q4 * 8 + e * 2 + 1] = f.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e)
+      bv[e] = (br.row_ok && jb + e < br.lk) ? Pack<T>::one(br.base, br.row + jb + e) : 0.f;
+  }
 }
-// silu(y) * scale = y*scale / (1 + 2^(-y*log2 e))  (two MUFU ops, ~1 ulp; used for fp16 inputs)
-__device__ __forceinline__ float silu_scaled_exact(float y, float scale) {
-  const float e = ptx::ex2_approx(-1.4426950408889634f * y);
-  return y * scale * ptx::rcp_approx(1.f + e);
+
+// 32 scores of one row (fp32 bits in sr) -> 16 words of packed P.  Branch-free; the arithmetic runs on the
+// packed f32x2 pipe.  x = c_in * s + c_bias * bias covers both orders of alpha and bias (c_bias = c_in gives
+// alpha * (s + bias)).
+template <typename T, bool kBias, bool kMasked>
+__device__ __forceinline__ void silu_chunk(const uint32_t (&sr)[32], const float (&bv)[32], uint32_t (&pr)[16],
+                                           float c_in, float c_bias, float scale, const RowBounds& rb, int j0) {
+  constexpr bool kExact = Pack<T>::kFormat == 0;  // fp16: exp2 + rcp (two MUFU ops); bf16: tanh form (one)
+  const float2 cin2 = make_float2(c_in, c_in);
+  const float2 cb2 = make_float2(c_bias, c_bias);
+  const float2 sc2 = make_float2(scale, scale);
+#pragma unroll
+  for (int e = 0; e < 32; e += 2) {
+    float2 x = make_float2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1]));
+    if (kBias)
+      x = __ffma2_rn(x, cin2, __fmul2_rn(make_float2(bv[e], bv[e + 1]), cb2));
+    else
+      x = __fmul2_rn(x, cin2);
+    const float2 r = __fmul2_rn(x, sc2);
+    float2 o;
+    if (kExact) {
+      const float2 ny = __fmul2_rn(x, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+      const float2 d = __fadd2_rn(make_float2(ptx::ex2_approx(ny.x), ptx::ex2_approx(ny.y)), make_float2(1.f, 1.f));
+      o = __fmul2_rn(r, make_float2(ptx::rcp_approx(d.x), ptx::rcp_approx(d.y)));
+    } else {
+#ifdef HSTU_EXP_NOMUFU
+      o = __ffma2_rn(r, x, r);
+#else
+      o = __ffma2_rn(r, make_float2(ptx::tanh_approx(x.x), ptx::tanh_approx(x.y)), r);
+#endif
+    }
+    if (kMasked) {
+      o.x = allowed(rb, j0 + e) ? o.x : 0.f;
+      o.y = allowed(rb, j0 + e + 1) ? o.y : 0.f;
+    }
+    pr[e >> 1] = Pack<T>::pack(o.x, o.y);
+  }
+}
+
+// One 128 x 128 score tile of this thread's row: S (TMEM, fp32) -> P (TMEM, packed 16-bit, in place).
+// The TMEM load of chunk c+1 is in flight while chunk c is computed.
+template <typename T, bool kBias, bool kMasked>
+__device__ __forceinline__ void p_tile(uint32_t t_s, int c0, const BiasRow& br, const RowBounds& rb, float c_in,
+                                       float c_bias, float scale) {
+  uint32_t sbuf[2][32];
+  float bv[32];
+  uint32_t pr[16];
+  ptx::tmem_ld32(t_s, sbuf[0]);
+#pragma unroll
+  for (int ch = 0; ch < kTileN / 32; ++ch) {
+    if (kBias) load_bias32<T>(br, c0 + ch * 32, bv);
+    ptx::tmem_wait_ld_dep(sbuf[ch & 1]);
+    if (ch + 1 < kTileN / 32) ptx::tmem_ld32(t_s + (ch + 1) * 32, sbuf[(ch + 1) & 1]);
+    silu_chunk<T, kBias, kMasked>(sbuf[ch & 1], bv, pr, c_in, c_bias, scale, rb, c0 + ch * 32);
+    ptx::tmem_st16(t_s + ch * 16, pr);
+  }
 }
 
 template <int D, typename T, bool kBias>
@@ -205,7 +295,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         if (idx >= num_items) continue;
         const Item it = load_item(p, idx);
         for (int t = 0; t < 2; ++t) {
-          if (it.n[t] == 0) continue;
+          if (it.n(t) == 0) continue;
           const uint32_t full = ptx::smem_u32(&bars->q_full[t]);
           w.wait(ptx::smem_u32(&bars->q_free[t]), (q_uses[t] & 1u) ^ 1u);
           ptx::mbar_expect_tx(full, C::kTileBytes);
@@ -251,9 +341,16 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ptx::umma_idesc_f16(Pack<T>::kFormat, kTileM, kTileN, 0);
       constexpr uint32_t idesc_pv = ptx::umma_idesc_f16(Pack<T>::kFormat, kTileM, D, 1);
+      // descriptor templates (everything but the start address): K-major Q / K tiles, N-major V tiles
+      constexpr uint64_t kDescK = ptx::umma_desc_sw128_hi(16, 1024);
+      constexpr uint64_t kDescV = ptx::umma_desc_sw128_hi(C::kHalfBytes, 1024);
       uint32_t q_uses[2] = {0, 0}, p_uses[2] = {0, 0}, o_uses[2] = {0, 0};
       uint32_t ring_base = 0;
       long long round = 0;
+#ifdef HSTU_PROF
+      unsigned long long prof_acc[6] = {0, 0, 0, 0, 0, 0};
+      const long long t_all = clock64();
+#endif
       for (long long first = 0; first < num_items; first += G, ++round) {
         const long long idx = first + ((round & 1) ? (G - 1 - cta) : cta);
         if (idx >= num_items) continue;
@@ -261,8 +358,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         for (int step = 0; step <= it.nmax; ++step) {
           const uint32_t pos_k = ring_base + 2u * step;            // K(step)
           const uint32_t pos_v = ring_base + 2u * (step - 1) + 1u;  // V(step - 1)
+          PROF_T0(t_kv);
           if (step < it.nmax) w.wait(ptx::smem_u32(&bars->kv_full[pos_k % C::kStages]), (pos_k / C::kStages) & 1u);
           if (step >= 1) w.wait(ptx::smem_u32(&bars->kv_full[pos_v % C::kStages]), (pos_v / C::kStages) & 1u);
+          PROF_ADD(0, t_kv);
           ptx::tc_fence_after();
           const uint32_t sm_k = sm_ring + (pos_k % C::kStages) * C::kTileBytes;
           const uint32_t sm_v = sm_ring + (pos_v % C::kStages) * C::kTileBytes;
@@ -270,38 +369,45 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           for (int t = 0; t < 2; ++t) {
             const uint32_t col_s = tmem + (t == 0 ? kColS0 : kColS1);
             const uint32_t col_o = tmem + (t == 0 ? kColO0 : C::kColO1);
-            if (step >= 1 && step - 1 < it.n[t]) {
+            if (step >= 1 && step - 1 < it.n(t)) {
               // O_t (+)= P_t(step-1) . V(step-1)
+              PROF_T0(t_p);
               w.wait(ptx::smem_u32(&bars->p_full[t]), p_uses[t] & 1u);
+              PROF_ADD(1, t_p);
               ++p_uses[t];
+              PROF_T0(t_of);
               if (step == 1) w.wait(ptx::smem_u32(&bars->o_free[t]), (o_uses[t] & 1u) ^ 1u);
+              PROF_ADD(2, t_of);
               ptx::tc_fence_after();
+              PROF_T0(t_ipv);
+              const uint64_t vbase = kDescV | static_cast<uint64_t>(sm_v >> 4);
+              ptx::mma_ts(col_o, col_s, vbase, idesc_pv, step > 1 ? 1u : 0u);
 #pragma unroll
-              for (int ks = 0; ks < kTileN / 16; ++ks) {
-                const uint64_t bdesc = ptx::umma_desc_sw128(sm_v + ks * 2048, C::kHalfBytes, 1024);
-                ptx::mma_ts(col_o, col_s + ks * 8, bdesc, idesc_pv, (step > 1 || ks > 0) ? 1u : 0u);
-              }
-              if (step == it.n[t]) {
+              for (int ks = 1; ks < kTileN / 16; ++ks)
+                ptx::mma_ts(col_o, col_s + ks * 8, vbase + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv, 1u);
+              PROF_ADD(4, t_ipv);
+              if (step == it.n(t)) {
                 ptx::mma_commit(ptx::smem_u32(&bars->o_full[t]));
                 ++o_uses[t];
               }
             }
-            if (step < it.n[t]) {
+            if (step < it.n(t)) {
               // S_t = Q_t . K(step)^T
               if (step == 0) {
                 w.wait(ptx::smem_u32(&bars->q_full[t]), q_uses[t] & 1u);
                 ptx::tc_fence_after();
               }
-              const uint32_t sm_qt = sm_q + t * C::kTileBytes;
+              PROF_T0(t_iqk);
+              const uint64_t qbase = kDescK | static_cast<uint64_t>((sm_q + t * C::kTileBytes) >> 4);
+              const uint64_t kbase = kDescK | static_cast<uint64_t>(sm_k >> 4);
 #pragma unroll
               for (int ks = 0; ks < D / 16; ++ks) {
-                const uint32_t off = (ks >> 2) * C::kHalfBytes + (ks & 3) * 32;
-                const uint64_t adesc = ptx::umma_desc_sw128(sm_qt + off, 16, 1024);
-                const uint64_t bdesc = ptx::umma_desc_sw128(sm_k + off, 16, 1024);
-                ptx::mma_ss(col_s, adesc, bdesc, idesc_qk, ks > 0 ? 1u : 0u);
+                const uint64_t off = static_cast<uint64_t>(((ks >> 2) * C::kHalfBytes + (ks & 3) * 32) >> 4);
+                ptx::mma_ss(col_s, qbase + off, kbase + off, idesc_qk, ks > 0 ? 1u : 0u);
               }
+              PROF_ADD(5, t_iqk);
               ptx::mma_commit(ptx::smem_u32(&bars->s_full[t]));
-              if (step == it.n[t] - 1) {
+              if (step == it.n(t) - 1) {
                 ptx::mma_commit(ptx::smem_u32(&bars->q_free[t]));
                 ++q_uses[t];
               }
@@ -315,6 +421,12 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       // all MMAs (and the mbarrier arrivals of their commits) complete before the CTA tears down
       ptx::mma_commit(ptx::smem_u32(&bars->done));
       w.wait(ptx::smem_u32(&bars->done), 0);
+#ifdef HSTU_PROF
+      prof_acc[3] = clock64() - t_all;
+      for (int i = 0; i < 4; ++i) g_prof[blockIdx.x][12 + i] = prof_acc[i];
+      g_prof[blockIdx.x][20] = prof_acc[4];
+      g_prof[blockIdx.x][21] = prof_acc[5];
+#endif
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ P / O groups (thread = row)
@@ -328,15 +440,21 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     const uint32_t bar_of = ptx::smem_u32(&bars->o_full[t]);
     const uint32_t bar_oe = ptx::smem_u32(&bars->o_free[t]);
     const bool alpha_first = (p.flags & HSTU_FLAG_ALPHA_BEFORE_BIAS) != 0;
-    constexpr bool kExact = Pack<T>::kFormat == 0;  // fp16: two-MUFU sigmoid; bf16: one-MUFU tanh form
+    constexpr bool kExact = Pack<T>::kFormat == 0;
+    // bf16 works on a = y / 2 (tanh form), fp16 on y itself;  x = c_in * s + c_bias * bias
     const float c_in = kExact ? p.alpha : 0.5f * p.alpha;
     const float c_bias = alpha_first ? (kExact ? 1.f : 0.5f) : c_in;
     uint32_t s_uses = 0, o_uses = 0;
     long long round = 0;
+#ifdef HSTU_PROF
+    unsigned long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+#endif
     for (long long first = 0; first < num_items; first += G, ++round) {
       const long long idx = first + ((round & 1) ? (G - 1 - cta) : cta);
       if (idx >= num_items) continue;
+      PROF_T0(t_li);
       const Item it = load_item(p, idx);
+      PROF_ADD(4, t_li);
       const int tile_r0 = it.r0 + t * kTileM;
       if (tile_r0 >= it.s.lq) continue;
       const int i = tile_r0 + row;
@@ -345,79 +463,34 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       const long long bias_row = kBias ? static_cast<long long>(it.b) * p.bias_bstride +
                                              (static_cast<long long>(it.h) * p.maxq + i) * p.maxk
                                        : 0;
-      for (int j = 0; j < it.n[t]; ++j) {
+      for (int j = 0; j < it.n(t); ++j) {
         const int c0 = j * kTileN;
         const bool full = tile_is_full(it.s, tile_r0, kTileM, c0, kTileN, p.mask_type, p.group);
+        PROF_T0(t_ws);
         w.wait(bar_s, s_uses & 1u);
+        PROF_ADD(0, t_ws);
+        PROF_T0(t_silu);
         ++s_uses;
         ptx::tc_fence_after();
-#pragma unroll 1
-        for (int ch = 0; ch < kTileN / 32; ++ch) {
-          uint32_t sr[32];
-          ptx::tmem_ld32(t_s + ch * 32, sr);
-          float bv[32];
-          if (kBias) {
-            const int jb = c0 + ch * 32;
-            if (row_ok && bias_vec_ok && jb + 32 <= p.maxk) {
-              const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + bias_row + jb);
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4) {
-                const uint4 u = __ldg(src + q4);
-                const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float2 f = Pack<T>::unpack(uu[e]);
-                  bv[q4 * 8 + e * 2] = f.x;
-                  bv[q4 * 8 + e * 2 + 1] = f.y;
-                }
-              }
-            } else {
-#pragma unroll
-              for (int e = 0; e < 32; ++e)
-                bv[e] = (row_ok && jb + e < it.s.lk) ? Pack<T>::one(p.bias, bias_row + jb + e) : 0.f;
-            }
-          }
-          ptx::tmem_wait_ld();
-          uint32_t pr[16];
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float x0 = __uint_as_float(sr[e]), x1 = __uint_as_float(sr[e + 1]);
-            if (kBias) {
-              if (alpha_first) {
-                x0 = fmaf(x0, c_in, bv[e] * c_bias);
-                x1 = fmaf(x1, c_in, bv[e + 1] * c_bias);
-              } else {
-                x0 = (x0 + bv[e]) * c_in;
-                x1 = (x1 + bv[e + 1]) * c_in;
-              }
-            } else {
-              x0 *= c_in;
-              x1 *= c_in;
-            }
-            float p0, p1;
-            if (kExact) {
-              p0 = silu_scaled_exact(x0, p.scale);
-              p1 = silu_scaled_exact(x1, p.scale);
-            } else {
-              p0 = silu_scaled_tanh(x0, p.scale);
-              p1 = silu_scaled_tanh(x1, p.scale);
-            }
-            if (!full) {
-              const int jc = c0 + ch * 32 + e;
-              p0 = allowed(rb, jc) ? p0 : 0.f;
-              p1 = allowed(rb, jc + 1) ? p1 : 0.f;
-            }
-            pr[e >> 1] = Pack<T>::pack(p0, p1);
-          }
-          ptx::tmem_st16(t_s + ch * 16, pr);
-        }
+        const BiasRow br{p.bias, bias_row, row_ok, bias_vec_ok != 0, p.maxk, it.s.lk};
+        if (full)
+          p_tile<T, kBias, false>(t_s, c0, br, rb, c_in, c_bias, p.scale);
+        else
+          p_tile<T, kBias, true>(t_s, c0, br, rb, c_in, c_bias, p.scale);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar_p);
+        PROF_ADD(1, t_silu);
+#ifdef HSTU_PROF
+        prof_acc[5] += 1;
+#endif
       }
       T* orow = static_cast<T*>(p.out) + ((it.s.q0 + i) * p.hq + it.h) * D;
-      if (it.n[t] > 0) {
+      if (it.n(t) > 0) {
+        PROF_T0(t_wo);
         w.wait(bar_of, o_uses & 1u);
+        PROF_ADD(2, t_wo);
+        PROF_T0(t_epi);
         ++o_uses;
         ptx::tc_fence_after();
 #pragma unroll 1
@@ -440,12 +513,19 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         }
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar_oe);
+        PROF_ADD(3, t_epi);
       } else if (row_ok) {
         uint4* dst = reinterpret_cast<uint4*>(orow);
 #pragma unroll
         for (int q4 = 0; q4 < D / 8; ++q4) dst[q4] = make_uint4(0, 0, 0, 0);
       }
     }
+#ifdef HSTU_PROF
+    if (row == 0)
+      for (int i = 0; i < 6; ++i) g_prof[blockIdx.x][t * 6 + i] = prof_acc[i];
+    if (row == 0 && t == 0)
+      for (int i = 6; i < 10; ++i) g_prof[blockIdx.x][10 + i] = prof_acc[i];
+#endif
   }
 
   ptx::tc_fence_before();
@@ -498,6 +578,14 @@ cudaError_t launch_inst(const KParams& p, const CUtensorMap& mq, const CUtensorM
 }
 
 }  // namespace
+
+#ifdef HSTU_PROF
+}  // namespace hstu
+extern "C" __attribute__((visibility("default"))) int hstu_debug_read_prof(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, hstu::g_prof, sizeof(unsigned long long) * 160 * 24) == cudaSuccess ? 0 : -4;
+}
+namespace hstu {
+#endif
 
 bool tc_supported(const KParams& p, int dtype) {
   if (dtype != HSTU_DTYPE_BF16 && dtype != HSTU_DTYPE_FP16) return false;
