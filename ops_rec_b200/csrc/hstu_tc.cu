@@ -39,6 +39,8 @@ constexpr int kThreads = 384;
 constexpr int kTmemCols = 512;
 constexpr int kColS0 = 0, kColS1 = 128, kColO0 = 256;
 constexpr long long kWaitLimitCycles = 2000000000ll;  // ~1 s
+constexpr int kSchedStages = 4;                       // depth of the work-item ring between scheduler and roles
+constexpr int kSchedReaders = 2 + 2 * 128;            // producer lane + MMA lane + every thread of both P/O groups
 
 template <int D>
 struct Cfg {
@@ -59,6 +61,8 @@ struct Barriers {
   uint64_t o_full[2], o_free[2];
   uint64_t done;
   uint64_t kv_full[8], kv_free[8];
+  uint64_t sched_full[kSchedStages], sched_free[kSchedStages];
+  long long sched_item[kSchedStages];  // index into the work list, -1 = no more work
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -85,6 +89,23 @@ struct Waiter {
         }
       }
     }
+  }
+};
+
+// Consumer side of the work-item ring: every role sees the same sequence of items, in the order the scheduler
+// warp drew them from the global counter.
+struct ItemFeed {
+  Barriers* bars;
+  const Waiter* w;
+  uint32_t n;
+  __device__ __forceinline__ long long next() {
+    const uint32_t slot = n % kSchedStages;
+    w->wait(ptx::smem_u32(&bars->sched_full[slot]), (n / kSchedStages) & 1u);
+    long long idx = *reinterpret_cast<volatile long long*>(&bars->sched_item[slot]);
+    if (*reinterpret_cast<volatile int*>(w->abort_flag)) idx = -1;  // a wait gave up: stop taking work
+    ptx::mbar_arrive(ptx::smem_u32(&bars->sched_free[slot]));
+    ++n;
+    return idx;
   }
 };
 
@@ -268,6 +289,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       ptx::mbar_init(ptx::smem_u32(&bars->kv_full[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&bars->kv_free[s]), 1);
     }
+    for (int s = 0; s < kSchedStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bars->sched_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->sched_free[s]), kSchedReaders);
+    }
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
   }
@@ -281,18 +306,14 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
   const long long num_items = p.ws_header[1];
-  const long long G = gridDim.x;
-  const long long cta = blockIdx.x;
+  ItemFeed feed{bars, &w, 0};
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t q_uses[2] = {0, 0};
       uint32_t ring_pos = 0;
-      long long round = 0;
-      for (long long first = 0; first < num_items; first += G, ++round) {
-        const long long idx = first + ((round & 1) ? (G - 1 - cta) : cta);
-        if (idx >= num_items) continue;
+      for (long long idx = feed.next(); idx >= 0; idx = feed.next()) {
         const Item it = load_item(p, idx);
         for (int t = 0; t < 2; ++t) {
           if (it.n(t) == 0) continue;
@@ -346,14 +367,11 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       constexpr uint64_t kDescV = ptx::umma_desc_sw128_hi(C::kHalfBytes, 1024);
       uint32_t q_uses[2] = {0, 0}, p_uses[2] = {0, 0}, o_uses[2] = {0, 0};
       uint32_t ring_base = 0;
-      long long round = 0;
 #ifdef HSTU_PROF
       unsigned long long prof_acc[6] = {0, 0, 0, 0, 0, 0};
       const long long t_all = clock64();
 #endif
-      for (long long first = 0; first < num_items; first += G, ++round) {
-        const long long idx = first + ((round & 1) ? (G - 1 - cta) : cta);
-        if (idx >= num_items) continue;
+      for (long long idx = feed.next(); idx >= 0; idx = feed.next()) {
         const Item it = load_item(p, idx);
         for (int step = 0; step <= it.nmax; ++step) {
           const uint32_t pos_k = ring_base + 2u * step;            // K(step)
@@ -428,6 +446,21 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       g_prof[blockIdx.x][21] = prof_acc[5];
 #endif
     }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ scheduler: draws items from the global
+    // counter (the list is ordered heaviest sequences first, so this is greedy longest-first list scheduling)
+    if (lane == 0) {
+      for (uint32_t n = 0;; ++n) {
+        const uint32_t slot = n % kSchedStages;
+        w.wait(ptx::smem_u32(&bars->sched_free[slot]), ((n / kSchedStages) & 1u) ^ 1u);
+        long long idx = static_cast<long long>(atomicAdd(&p.ws_header[2], 1u));
+        if (idx >= num_items || *reinterpret_cast<volatile int*>(&bars->abort_flag)) idx = -1;
+        *reinterpret_cast<volatile long long*>(&bars->sched_item[slot]) = idx;
+        ptx::mbar_arrive(ptx::smem_u32(&bars->sched_full[slot]));
+        if (idx < 0) break;
+      }
+    }
+    __syncwarp();
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ P / O groups (thread = row)
     const int t = (warp - 4) >> 2;                 // Q tile of this group
@@ -445,13 +478,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     const float c_in = kExact ? p.alpha : 0.5f * p.alpha;
     const float c_bias = alpha_first ? (kExact ? 1.f : 0.5f) : c_in;
     uint32_t s_uses = 0, o_uses = 0;
-    long long round = 0;
 #ifdef HSTU_PROF
     unsigned long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
 #endif
-    for (long long first = 0; first < num_items; first += G, ++round) {
-      const long long idx = first + ((round & 1) ? (G - 1 - cta) : cta);
-      if (idx >= num_items) continue;
+    for (long long idx = feed.next(); idx >= 0; idx = feed.next()) {
       PROF_T0(t_li);
       const Item it = load_item(p, idx);
       PROF_ADD(4, t_li);
