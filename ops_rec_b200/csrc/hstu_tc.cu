@@ -15,7 +15,8 @@
 // (…/op_kernel/atlas950/hstu_dense_forward_kernel_patten_bsnd.h:156-176, 590-689,
 //  hstu_dense_forward_jagged_kernel.h:257-398).
 //
-// Warp roles (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warp 2 = TMEM allocator,
+// Warp roles (384 threads): warp 0 = TMA producer, warps 1 and 3 = MMA issuers (one per Q tile), warp 2 = TMEM
+// allocator and work-item scheduler,
 // warps 4-7 = P/O group of Q tile 0, warps 8-11 = P/O group of Q tile 1.
 //
 // Every wait on an mbarrier is bounded: after ~1 s without progress the waiter raises HSTU_ST_PIPE_TIMEOUT in
@@ -40,7 +41,7 @@ constexpr int kTmemCols = 512;
 constexpr int kColS0 = 0, kColS1 = 128, kColO0 = 256;
 constexpr long long kWaitLimitCycles = 2000000000ll;  // ~1 s
 constexpr int kSchedStages = 4;                       // depth of the work-item ring between scheduler and roles
-constexpr int kSchedReaders = 2 + 2 * 128;            // producer lane + MMA lane + every thread of both P/O groups
+constexpr int kSchedReaders = 3 + 2 * 128;            // producer lane + two MMA lanes + every thread of both P/O groups
 
 template <int D>
 struct Cfg {
@@ -59,7 +60,8 @@ struct Barriers {
   uint64_t q_full[2], q_free[2];
   uint64_t s_full[2], p_full[2];
   uint64_t o_full[2], o_free[2];
-  uint64_t done;
+  uint64_t done[2];
+  uint64_t turn[2];  // MMA issuers alternate: turn[t] completes a phase when issuer t may go
   uint64_t kv_full[8], kv_free[8];
   uint64_t sched_full[kSchedStages], sched_free[kSchedStages];
   long long sched_item[kSchedStages];  // index into the work list, -1 = no more work
@@ -71,6 +73,11 @@ static_assert(sizeof(Barriers) <= 512, "barrier block too large");
 struct Waiter {
   int* abort_flag;
   uint32_t* status;
+  // `polled` is the result of an earlier mbar_try_wait on the same phase (polls of several barriers are issued
+  // back to back so that their latencies overlap); only an unsuccessful poll falls into the waiting loop.
+  __device__ __forceinline__ void wait_polled(bool polled, uint32_t bar, uint32_t parity) const {
+    if (!polled) wait(bar, parity);
+  }
   __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity) const {
     if (ptx::mbar_try_wait(bar, parity)) return;
     if (*reinterpret_cast<volatile int*>(abort_flag)) return;
@@ -284,10 +291,13 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       ptx::mbar_init(ptx::smem_u32(&bars->o_full[t]), 1);
       ptx::mbar_init(ptx::smem_u32(&bars->o_free[t]), kTileM);
     }
-    ptx::mbar_init(ptx::smem_u32(&bars->done), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->done[0]), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->done[1]), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->turn[0]), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->turn[1]), 1);
     for (int s = 0; s < C::kStages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&bars->kv_full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->kv_free[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->kv_free[s]), 2);  // one arrival from each MMA issuer
     }
     for (int s = 0; s < kSchedStages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&bars->sched_full[s]), 1);
@@ -334,11 +344,15 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
             const uint32_t use = ring_pos / C::kStages;
             const uint32_t full = ptx::smem_u32(&bars->kv_full[stage]);
             w.wait(ptx::smem_u32(&bars->kv_free[stage]), (use & 1u) ^ 1u);
+#ifdef HSTU_EXP_NOTMA
+            ptx::mbar_arrive(full);
+#else
             ptx::mbar_expect_tx(full, C::kTileBytes);
 #pragma unroll
             for (int hf = 0; hf < C::kHalves; ++hf)
               ptx::tma_load_3d(sm_ring + stage * C::kTileBytes + hf * C::kHalfBytes, kv == 0 ? &tm_k : &tm_v, full,
                                hf * 64, it.hk, row);
+#endif
             ++ring_pos;
           }
         }
@@ -357,15 +371,26 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (q_uses[t] - 1) & 1u); ++spin) {}
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------------------------------------------ MMA issuers, one per Q tile.
+    // Each chain (S_t = Q_t.K^T, then O_t += P_t.V) is issued by its own thread: a barrier poll costs the
+    // issuing thread ~130 cycles and the tensor pipe queues only a few instructions, so while one issuer
+    // waits for its P tile the other keeps the pipe fed.  The chains share nothing but the read-only K/V tiles.
     if (lane == 0) {
+      const int t = warp == 1 ? 0 : 1;
       constexpr uint32_t idesc_qk = ptx::umma_idesc_f16(Pack<T>::kFormat, kTileM, kTileN, 0);
       constexpr uint32_t idesc_pv = ptx::umma_idesc_f16(Pack<T>::kFormat, kTileM, D, 1);
       // descriptor templates (everything but the start address): K-major Q / K tiles, N-major V tiles
       constexpr uint64_t kDescK = ptx::umma_desc_sw128_hi(16, 1024);
       constexpr uint64_t kDescV = ptx::umma_desc_sw128_hi(C::kHalfBytes, 1024);
-      uint32_t q_uses[2] = {0, 0}, p_uses[2] = {0, 0}, o_uses[2] = {0, 0};
+      const uint32_t col_s = tmem + (t == 0 ? kColS0 : kColS1);
+      const uint32_t col_o = tmem + (t == 0 ? kColO0 : C::kColO1);
+      const uint64_t qbase = kDescK | static_cast<uint64_t>((sm_q + t * C::kTileBytes) >> 4);
+      const uint32_t bar_q_full = ptx::smem_u32(&bars->q_full[t]), bar_q_free = ptx::smem_u32(&bars->q_free[t]);
+      const uint32_t bar_s_full = ptx::smem_u32(&bars->s_full[t]), bar_p_full = ptx::smem_u32(&bars->p_full[t]);
+      const uint32_t bar_o_full = ptx::smem_u32(&bars->o_full[t]), bar_o_free = ptx::smem_u32(&bars->o_free[t]);
+      const uint32_t bar_turn_mine = ptx::smem_u32(&bars->turn[t]), bar_turn_other = ptx::smem_u32(&bars->turn[1 - t]);
+      uint32_t q_uses = 0, p_uses = 0, o_uses = 0, turns = 0;
       uint32_t ring_base = 0;
 #ifdef HSTU_PROF
       unsigned long long prof_acc[6] = {0, 0, 0, 0, 0, 0};
@@ -373,77 +398,95 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
 #endif
       for (long long idx = feed.next(); idx >= 0; idx = feed.next()) {
         const Item it = load_item(p, idx);
+        const int n = it.n(t);
         for (int step = 0; step <= it.nmax; ++step) {
-          const uint32_t pos_k = ring_base + 2u * step;            // K(step)
+          const uint32_t pos_k = ring_base + 2u * step;             // K(step)
           const uint32_t pos_v = ring_base + 2u * (step - 1) + 1u;  // V(step - 1)
+          const uint32_t st_k = pos_k % C::kStages, st_v = pos_v % C::kStages;
+          const bool has_v = step >= 1, has_k = step < it.nmax;
+          const bool do_pv = has_v && step - 1 < n, do_qk = has_k && step < n;
+          const uint32_t bar_vf = ptx::smem_u32(&bars->kv_full[st_v]), par_vf = (pos_v / C::kStages) & 1u;
+          const uint32_t bar_kf = ptx::smem_u32(&bars->kv_full[st_k]), par_kf = (pos_k / C::kStages) & 1u;
+          // The issuers alternate step by step (tile 0 first): when both P tiles become ready together the pipe
+          // serves one chain, then the other, which keeps the two P/O groups half a period apart - one computes
+          // while the other's MMAs run.  Issuer 0 waits for issuer 1's previous step, issuer 1 for issuer 0's
+          // current one.
+          const uint32_t par_turn = t == 0 ? ((turns & 1u) ^ 1u) : (turns & 1u);
+          // poll everything this step needs at once
           PROF_T0(t_kv);
-          if (step < it.nmax) w.wait(ptx::smem_u32(&bars->kv_full[pos_k % C::kStages]), (pos_k / C::kStages) & 1u);
-          if (step >= 1) w.wait(ptx::smem_u32(&bars->kv_full[pos_v % C::kStages]), (pos_v / C::kStages) & 1u);
+          const bool ok_turn = ptx::mbar_try_wait(bar_turn_mine, par_turn);
+          const bool ok_v = has_v ? ptx::mbar_try_wait(bar_vf, par_vf) : true;
+          const bool ok_k = has_k ? ptx::mbar_try_wait(bar_kf, par_kf) : true;
+          const bool ok_p = do_pv ? ptx::mbar_try_wait(bar_p_full, p_uses & 1u) : true;
+          w.wait_polled(ok_v, bar_vf, par_vf);
+          w.wait_polled(ok_k, bar_kf, par_kf);
           PROF_ADD(0, t_kv);
+          PROF_T0(t_p);
+          w.wait_polled(ok_p, bar_p_full, p_uses & 1u);
+          PROF_ADD(1, t_p);
+          PROF_T0(t_of);
+          if (do_pv && step == 1) w.wait(bar_o_free, (o_uses & 1u) ^ 1u);
+          if (do_qk && step == 0) w.wait(bar_q_full, q_uses & 1u);
+          w.wait_polled(ok_turn, bar_turn_mine, par_turn);
+          PROF_ADD(2, t_of);
+          ++turns;
           ptx::tc_fence_after();
-          const uint32_t sm_k = sm_ring + (pos_k % C::kStages) * C::kTileBytes;
-          const uint32_t sm_v = sm_ring + (pos_v % C::kStages) * C::kTileBytes;
+          if (do_pv) {
+            // O_t (+)= P_t(step-1) . V(step-1)
+            ++p_uses;
+            PROF_T0(t_ipv);
+            const uint64_t vbase = kDescV | static_cast<uint64_t>((sm_ring + st_v * C::kTileBytes) >> 4);
+            ptx::mma_ts(col_o, col_s, vbase, idesc_pv, step > 1 ? 1u : 0u);
 #pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            const uint32_t col_s = tmem + (t == 0 ? kColS0 : kColS1);
-            const uint32_t col_o = tmem + (t == 0 ? kColO0 : C::kColO1);
-            if (step >= 1 && step - 1 < it.n(t)) {
-              // O_t (+)= P_t(step-1) . V(step-1)
-              PROF_T0(t_p);
-              w.wait(ptx::smem_u32(&bars->p_full[t]), p_uses[t] & 1u);
-              PROF_ADD(1, t_p);
-              ++p_uses[t];
-              PROF_T0(t_of);
-              if (step == 1) w.wait(ptx::smem_u32(&bars->o_free[t]), (o_uses[t] & 1u) ^ 1u);
-              PROF_ADD(2, t_of);
-              ptx::tc_fence_after();
-              PROF_T0(t_ipv);
-              const uint64_t vbase = kDescV | static_cast<uint64_t>(sm_v >> 4);
-              ptx::mma_ts(col_o, col_s, vbase, idesc_pv, step > 1 ? 1u : 0u);
-#pragma unroll
-              for (int ks = 1; ks < kTileN / 16; ++ks)
-                ptx::mma_ts(col_o, col_s + ks * 8, vbase + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv, 1u);
-              PROF_ADD(4, t_ipv);
-              if (step == it.n(t)) {
-                ptx::mma_commit(ptx::smem_u32(&bars->o_full[t]));
-                ++o_uses[t];
-              }
-            }
-            if (step < it.n(t)) {
-              // S_t = Q_t . K(step)^T
-              if (step == 0) {
-                w.wait(ptx::smem_u32(&bars->q_full[t]), q_uses[t] & 1u);
-                ptx::tc_fence_after();
-              }
-              PROF_T0(t_iqk);
-              const uint64_t qbase = kDescK | static_cast<uint64_t>((sm_q + t * C::kTileBytes) >> 4);
-              const uint64_t kbase = kDescK | static_cast<uint64_t>(sm_k >> 4);
-#pragma unroll
-              for (int ks = 0; ks < D / 16; ++ks) {
-                const uint64_t off = static_cast<uint64_t>(((ks >> 2) * C::kHalfBytes + (ks & 3) * 32) >> 4);
-                ptx::mma_ss(col_s, qbase + off, kbase + off, idesc_qk, ks > 0 ? 1u : 0u);
-              }
-              PROF_ADD(5, t_iqk);
-              ptx::mma_commit(ptx::smem_u32(&bars->s_full[t]));
-              if (step == it.n(t) - 1) {
-                ptx::mma_commit(ptx::smem_u32(&bars->q_free[t]));
-                ++q_uses[t];
-              }
+            for (int ks = 1; ks < kTileN / 16; ++ks)
+              ptx::mma_ts(col_o, col_s + ks * 8, vbase + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv, 1u);
+            PROF_ADD(4, t_ipv);
+            if (step == n) {
+              ptx::mma_commit(bar_o_full);
+              ++o_uses;
             }
           }
-          if (step < it.nmax) ptx::mma_commit(ptx::smem_u32(&bars->kv_free[pos_k % C::kStages]));
-          if (step >= 1) ptx::mma_commit(ptx::smem_u32(&bars->kv_free[pos_v % C::kStages]));
+          if (do_qk) {
+            // S_t = Q_t . K(step)^T
+            PROF_T0(t_iqk);
+            const uint64_t kbase = kDescK | static_cast<uint64_t>((sm_ring + st_k * C::kTileBytes) >> 4);
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+              const uint64_t off = static_cast<uint64_t>(((ks >> 2) * C::kHalfBytes + (ks & 3) * 32) >> 4);
+              ptx::mma_ss(col_s, qbase + off, kbase + off, idesc_qk, ks > 0 ? 1u : 0u);
+            }
+            PROF_ADD(5, t_iqk);
+            ptx::mma_commit(bar_s_full);
+            if (step == n - 1) {
+              ptx::mma_commit(bar_q_free);
+              ++q_uses;
+            }
+          }
+          ptx::mbar_arrive(bar_turn_other);
+          // release the K/V tiles of this step: after this tile's MMAs that read them, or at once when this
+          // tile does not visit them (the tile is loaded - waited above - so the arrival counts for its
+          // current use)
+          if (has_v) {
+            if (do_pv) ptx::mma_commit(ptx::smem_u32(&bars->kv_free[st_v]));
+            else ptx::mbar_arrive(ptx::smem_u32(&bars->kv_free[st_v]));
+          }
+          if (has_k) {
+            if (do_qk) ptx::mma_commit(ptx::smem_u32(&bars->kv_free[st_k]));
+            else ptx::mbar_arrive(ptx::smem_u32(&bars->kv_free[st_k]));
+          }
         }
         ring_base += 2u * it.nmax;
       }
       // all MMAs (and the mbarrier arrivals of their commits) complete before the CTA tears down
-      ptx::mma_commit(ptx::smem_u32(&bars->done));
-      w.wait(ptx::smem_u32(&bars->done), 0);
+      ptx::mma_commit(ptx::smem_u32(&bars->done[t]));
+      w.wait(ptx::smem_u32(&bars->done[t]), 0);
 #ifdef HSTU_PROF
       prof_acc[3] = clock64() - t_all;
-      for (int i = 0; i < 4; ++i) g_prof[blockIdx.x][12 + i] = prof_acc[i];
-      g_prof[blockIdx.x][20] = prof_acc[4];
-      g_prof[blockIdx.x][21] = prof_acc[5];
+      if (t == 0) {
+        for (int i = 0; i < 4; ++i) g_prof[blockIdx.x][12 + i] = prof_acc[i];
+        g_prof[blockIdx.x][20] = prof_acc[4];
+        g_prof[blockIdx.x][21] = prof_acc[5];
+      }
 #endif
     }
   } else if (warp == 2) {
@@ -503,10 +546,12 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         ++s_uses;
         ptx::tc_fence_after();
         const BiasRow br{p.bias, bias_row, row_ok, bias_vec_ok != 0, p.maxk, it.s.lk};
+#ifndef HSTU_EXP_NOWG
         if (full)
           p_tile<T, kBias, false>(t_s, c0, br, rb, c_in, c_bias, p.scale);
         else
           p_tile<T, kBias, true>(t_s, c0, br, rb, c_in, c_bias, p.scale);
+#endif
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar_p);
