@@ -118,11 +118,14 @@ struct ItemFeed {
 
 #ifdef HSTU_PROF
 __device__ unsigned long long g_prof[160][24];
+__device__ unsigned long long g_trace[4][512];   // CTA 0: roles 0,1 = P/O groups, 2,3 = MMA issuers
+#define TRACE(role, code) do { if (blockIdx.x == 0 && trace_n < 512) g_trace[role][trace_n++] = (static_cast<unsigned long long>(clock64()) << 8) | (code); } while (0)
 #define PROF_T0(var) const long long var = clock64()
 #define PROF_ADD(slot, var) prof_acc[slot] += clock64() - (var)
 #else
 #define PROF_T0(var)
 #define PROF_ADD(slot, var)
+#define TRACE(role, code)
 #endif
 
 struct Item {
@@ -211,7 +214,7 @@ __device__ __forceinline__ void load_bias32(const BiasRow& br, int jb, float (&b
 // alpha * (s + bias)).
 template <typename T, bool kBias, bool kMasked>
 __device__ __forceinline__ void silu_chunk(const uint32_t (&sr)[32], const float (&bv)[32], uint32_t (&pr)[16],
-                                           float c_in, float c_bias, float scale, const RowBounds& rb, int j0) {
+                                           float c_in, float c_bias, float scale, uint32_t visible) {
   constexpr bool kExact = Pack<T>::kFormat == 0;  // fp16: exp2 + rcp (two MUFU ops); bf16: tanh form (one)
   const float2 cin2 = make_float2(c_in, c_in);
   const float2 cb2 = make_float2(c_bias, c_bias);
@@ -236,16 +239,26 @@ __device__ __forceinline__ void silu_chunk(const uint32_t (&sr)[32], const float
       o = __ffma2_rn(r, make_float2(ptx::tanh_approx(x.x), ptx::tanh_approx(x.y)), r);
 #endif
     }
-    if (kMasked) {
-      o.x = allowed(rb, j0 + e) ? o.x : 0.f;
-      o.y = allowed(rb, j0 + e + 1) ? o.y : 0.f;
+    if (kMasked) {  // a select, not a multiply: scores of rows past the sequence end may be Inf or NaN
+      o.x = (visible & (1u << e)) ? o.x : 0.f;
+      o.y = (visible & (2u << e)) ? o.y : 0.f;
     }
     pr[e >> 1] = Pack<T>::pack(o.x, o.y);
   }
 }
 
+// Bit e set <=> column j0 + e is visible to the row described by rb (columns j0 .. j0 + 31).
+__device__ __forceinline__ uint32_t low_bits(int n) {  // n lowest bits set, n clamped to [0, 32]
+  return n <= 0 ? 0u : (n >= 32 ? 0xffffffffu : ((1u << n) - 1u));
+}
+__device__ __forceinline__ uint32_t visible_bits(const RowBounds& rb, int j0) {
+  return low_bits(rb.lim1 - j0) | (low_bits(rb.hi2 + 1 - j0) & ~low_bits(rb.lo2 - j0));
+}
+
 // One 128 x 128 score tile of this thread's row: S (TMEM, fp32) -> P (TMEM, packed 16-bit, in place).
-// The TMEM load of chunk c+1 is in flight while chunk c is computed.
+// The TMEM load of chunk c+1 is in flight while chunk c is computed.  In a tile the mask cuts through
+// (kMasked) every warp classifies each 32 x 32 chunk of its rows: all visible -> plain path, nothing visible ->
+// zeros without any arithmetic, mixed -> per-element select.
 template <typename T, bool kBias, bool kMasked>
 __device__ __forceinline__ void p_tile(uint32_t t_s, int c0, const BiasRow& br, const RowBounds& rb, float c_in,
                                        float c_bias, float scale) {
@@ -255,10 +268,24 @@ __device__ __forceinline__ void p_tile(uint32_t t_s, int c0, const BiasRow& br, 
   ptx::tmem_ld32(t_s, sbuf[0]);
 #pragma unroll
   for (int ch = 0; ch < kTileN / 32; ++ch) {
-    if (kBias) load_bias32<T>(br, c0 + ch * 32, bv);
+    uint32_t vis = 0xffffffffu;
+    bool all_on = true, all_off = false;
+    if (kMasked) {
+      vis = visible_bits(rb, c0 + ch * 32);
+      all_on = __all_sync(0xffffffffu, vis == 0xffffffffu);
+      all_off = __all_sync(0xffffffffu, vis == 0u);
+    }
+    if (kBias && !all_off) load_bias32<T>(br, c0 + ch * 32, bv);
     ptx::tmem_wait_ld_dep(sbuf[ch & 1]);
     if (ch + 1 < kTileN / 32) ptx::tmem_ld32(t_s + (ch + 1) * 32, sbuf[(ch + 1) & 1]);
-    silu_chunk<T, kBias, kMasked>(sbuf[ch & 1], bv, pr, c_in, c_bias, scale, rb, c0 + ch * 32);
+    if (all_on) {
+      silu_chunk<T, kBias, false>(sbuf[ch & 1], bv, pr, c_in, c_bias, scale, 0u);
+    } else if (all_off) {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) pr[e] = 0u;
+    } else {
+      silu_chunk<T, kBias, true>(sbuf[ch & 1], bv, pr, c_in, c_bias, scale, vis);
+    }
     ptx::tmem_st16(t_s + ch * 16, pr);
   }
 }
@@ -395,6 +422,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
 #ifdef HSTU_PROF
       unsigned long long prof_acc[6] = {0, 0, 0, 0, 0, 0};
       const long long t_all = clock64();
+      int trace_n = 0;
 #endif
       for (long long idx = feed.next(); idx >= 0; idx = feed.next()) {
         const Item it = load_item(p, idx);
@@ -431,6 +459,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           PROF_ADD(2, t_of);
           ++turns;
           ptx::tc_fence_after();
+          TRACE(2 + t, 1);
           if (do_pv) {
             // O_t (+)= P_t(step-1) . V(step-1)
             ++p_uses;
@@ -462,6 +491,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
               ++q_uses;
             }
           }
+          TRACE(2 + t, 2);
           ptx::mbar_arrive(bar_turn_other);
           // release the K/V tiles of this step: after this tile's MMAs that read them, or at once when this
           // tile does not visit them (the tile is loaded - waited above - so the arrival counts for its
@@ -523,6 +553,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     uint32_t s_uses = 0, o_uses = 0;
 #ifdef HSTU_PROF
     unsigned long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    int trace_n = 0;
 #endif
     for (long long idx = feed.next(); idx >= 0; idx = feed.next()) {
       PROF_T0(t_li);
@@ -543,6 +574,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         w.wait(bar_s, s_uses & 1u);
         PROF_ADD(0, t_ws);
         PROF_T0(t_silu);
+        if (row == 0) TRACE(t, 3);
         ++s_uses;
         ptx::tc_fence_after();
         const BiasRow br{p.bias, bias_row, row_ok, bias_vec_ok != 0, p.maxk, it.s.lk};
@@ -555,6 +587,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar_p);
+        if (row == 0) TRACE(t, 4);
         PROF_ADD(1, t_silu);
 #ifdef HSTU_PROF
         prof_acc[5] += 1;
@@ -566,6 +599,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         w.wait(bar_of, o_uses & 1u);
         PROF_ADD(2, t_wo);
         PROF_T0(t_epi);
+        if (row == 0) TRACE(t, 5);
         ++o_uses;
         ptx::tc_fence_after();
 #pragma unroll 1
@@ -588,6 +622,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         }
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar_oe);
+        if (row == 0) TRACE(t, 6);
         PROF_ADD(3, t_epi);
       } else if (row_ok) {
         uint4* dst = reinterpret_cast<uint4*>(orow);
@@ -656,6 +691,9 @@ cudaError_t launch_inst(const KParams& p, const CUtensorMap& mq, const CUtensorM
 
 #ifdef HSTU_PROF
 }  // namespace hstu
+extern "C" __attribute__((visibility("default"))) int hstu_debug_read_trace(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, hstu::g_trace, sizeof(unsigned long long) * 4 * 512) == cudaSuccess ? 0 : -4;
+}
 extern "C" __attribute__((visibility("default"))) int hstu_debug_read_prof(unsigned long long* out) {
   return cudaMemcpyFromSymbol(out, hstu::g_prof, sizeof(unsigned long long) * 160 * 24) == cudaSuccess ? 0 : -4;
 }
