@@ -35,7 +35,7 @@ def load_native():
 
     cabi.load()
     if not os.path.exists(SHIM_PATH):
-        raise ImportError(f"{SHIM_PATH} is missing: build it with `python -m ops_rec_b200._build`.")
+        raise ImportError(f"{SHIM_PATH} is missing: build it with `python ops_rec_b200/_build.py`.")
     torch.ops.load_library(SHIM_PATH)
     _loaded = True
 
