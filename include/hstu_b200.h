@@ -57,7 +57,8 @@ enum {
   HSTU_E_PARAM = -2,     /* shape / dtype / range check failed */
   HSTU_E_WORKSPACE = -3, /* workspace missing, misaligned or too small */
   HSTU_E_CUDA = -4,      /* CUDA runtime or driver call failed */
-  HSTU_E_ARCH = -5       /* device is not sm_100 */
+  HSTU_E_ARCH = -5,      /* device is not sm_100 */
+  HSTU_E_SCRATCH_LIMIT = -6 /* hstu_jagged_fwd_static: the call needs more scratch than the built-in block holds */
 };
 
 /* bits of the device status word written by the pre-pass (read it with hstu_jagged_fwd_status) */
@@ -120,6 +121,25 @@ HSTU_API int hstu_jagged_fwd_get_workspace_size(const HstuJaggedArgs* args, uint
  * stream) of the current device.  `workspace` is device memory, 256-byte aligned, at least the size phase 1
  * returned, and must stay alive until the work completes. */
 HSTU_API int hstu_jagged_fwd(const HstuJaggedArgs* args, void* workspace, uint64_t workspace_bytes, void* stream);
+
+/* Size of the scratch block built into the library for hstu_jagged_fwd_static (1 MiB per GPU that loads the
+ * library, held until the process exits).  It covers heads_q * (total_q / 256 + batch) <= 131040 work items. */
+#define HSTU_STATIC_SCRATCH_BYTES (1u << 20)
+
+/* The forward without any allocation, for callers that cannot give it a workspace: processes that froze their
+ * device-memory budget after start-up, plugins whose host forbids allocation inside the enqueue callback, code
+ * that cannot tolerate the device-wide synchronisation of cudaMalloc / cudaFree.  Same arguments, same kernels and
+ * bit-identical results as hstu_jagged_fwd; the scheduler's scratch lives in a fixed block inside the library.
+ * This entry point has no counterpart in the reference (its adapter always allocates the workspace tensor,
+ * ascendc/common/torch_plugin/pytorch_npu_helper.hpp:650-656).
+ *   - It calls no cudaMalloc, cudaFree or other allocating routine.
+ *   - A call whose work list does not fit returns HSTU_E_SCRATCH_LIMIT (use hstu_jagged_fwd with a workspace).
+ *   - The first call on each device looks up the block's device address (cudaGetSymbolAddress, that device
+ *     current); make that first call during start-up, before any stream capture begins.
+ *   - All calls on a device share the one block, which keeps what the previous call left in it.  Each call's
+ *     pre-pass re-initialises everything it reads, so calls that run one after another (same stream, or ordered by
+ *     events) are safe; two calls that overlap on the GPU race on the block and give undefined results. */
+HSTU_API int hstu_jagged_fwd_static(const HstuJaggedArgs* args, void* stream);
 
 /* Optional: wait for `stream` and fetch the device status word of the last launch that used `workspace`
  * (0 = inputs were consistent).  The reference reads out of bounds on such inputs without noticing. */

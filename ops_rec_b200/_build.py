@@ -3,7 +3,7 @@
   libhstu_b200.so   the C-ABI library: CUDA kernels for sm_100a + entry points (include/hstu_b200.h); nvcc only
   _torch_shim.so    registers ops_rec::hstu_jagged.{equal,delta} with torch and forwards to the C ABI
 
-Run `python -m ops_rec_b200._build` (or call build_all()) after changing anything under csrc/.
+Run `python ops_rec_b200/_build.py` (or call build_all()) after changing anything under csrc/.
 """
 from __future__ import annotations
 
@@ -18,7 +18,7 @@ ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libhstu_b200.so")
 SHIM = os.path.join(PKG, "_torch_shim.so")
 
-CUDA_SOURCES = ["hstu_api.cu", "hstu_sched.cu", "hstu_generic.cu", "hstu_tc.cu"]
+CUDA_SOURCES = ["hstu_api.cu", "hstu_sched.cu", "hstu_generic.cu", "hstu_tc.cu", "hstu_static.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

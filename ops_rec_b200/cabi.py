@@ -23,8 +23,10 @@ ST_BAD_OFFSETS, ST_LEN_GT_MAX, ST_BAD_CTX_TARGET, ST_PIPE_TIMEOUT = 1, 2, 4, 256
 EXPORTS = (
     "hstu_jagged_fwd_get_workspace_size", "hstu_jagged_fwd", "hstu_jagged_fwd_status",
     "hstu_jagged_fwd_kernel_kind", "hstu_plan_host", "hstu_debug_mask_host", "hstu_debug_tiles_host",
-    "hstu_last_error", "hstu_b200_version",
+    "hstu_last_error", "hstu_b200_version", "hstu_jagged_fwd_static",
 )
+STATIC_SCRATCH_BYTES = 1 << 20
+E_SCRATCH_LIMIT = -6
 
 
 class HstuJaggedArgs(C.Structure):
@@ -60,7 +62,7 @@ def load():
         return _lib
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m ops_rec_b200._build` "
+            f"{LIB_PATH} is missing: build it with `python ops_rec_b200/_build.py` "
             "(nvcc, sm_100a). There is no fallback implementation.")
     lib = C.CDLL(LIB_PATH)
     A = C.POINTER(HstuJaggedArgs)
@@ -79,6 +81,8 @@ def load():
     lib.hstu_debug_mask_host.restype = C.c_int
     lib.hstu_debug_tiles_host.argtypes = [C.c_int32] * 9 + [C.POINTER(C.c_uint64)]
     lib.hstu_debug_tiles_host.restype = C.c_int
+    lib.hstu_jagged_fwd_static.argtypes = [A, C.c_void_p]
+    lib.hstu_jagged_fwd_static.restype = C.c_int
     lib.hstu_last_error.restype = C.c_char_p
     lib.hstu_b200_version.restype = C.c_int
     _lib = lib
@@ -181,6 +185,28 @@ def hstu_jagged_forward(q, k, v, mask=None, attn_bias=None, mask_type=0, max_seq
             st = C.c_uint32(0)
             check(load().hstu_jagged_fwd_status(ws.data_ptr(), stream, C.byref(st)))
             return out, st.value
+    del keep
+    return out
+
+
+def hstu_jagged_forward_static(q, k, v, out, mask=None, attn_bias=None, mask_type=0, max_seq_len=0, silu_scale=0.0,
+                               seq_offset=None, num_context=None, num_target=None, target_group_size=0, alpha=1.0,
+                               *, max_seq_len_k=None, seq_offset_k=None, flags=0):
+    """The operator through hstu_jagged_fwd_static: no workspace, nothing allocated by the call.  `out` must be
+    preallocated by the caller ([total_q, heads_q, dim_v], q's dtype); inputs must already be contiguous.
+    Raises HstuError(E_SCRATCH_LIMIT) when the work list does not fit the library's built-in scratch block."""
+    import torch
+    args, keep = make_args(q, k, v, out, seq_offset, seq_offset_k=seq_offset_k, mask=mask, attn_bias=attn_bias,
+                           mask_type=mask_type, max_seq_len=max_seq_len, max_seq_len_k=max_seq_len_k,
+                           silu_scale=silu_scale, num_context=num_context, num_target=num_target,
+                           target_group_size=target_group_size, alpha=alpha, flags=flags)
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+        rc = load().hstu_jagged_fwd_static(C.byref(args), stream)
+    if rc == E_SCRATCH_LIMIT:
+        raise HstuError(rc, f"the call needs more than the {STATIC_SCRATCH_BYTES} bytes of built-in scratch; "
+                            "use hstu_jagged_fwd with a caller workspace")
+    check(rc)
     del keep
     return out
 
