@@ -34,6 +34,11 @@ if ROOT not in sys.path:
 METRIC = "hstu_jagged_fwd_causal_tflops"
 UNIT = "TFLOP/s"
 
+# DRAM bytes (read + write) per token of one attention-kernel launch, from the ncu capture summarised in
+# profiles/hstu_tc_kernel_cfg4.md (first 24 sequences of cfg4: 513 MB for 51 883 tokens; the traffic is compulsory
+# q/k/v/out movement and scales with the tokens a launch processes).
+TRAFFIC_BYTES_PER_TOKEN = {"cfg4": 513.08e6 / 51883}
+
 WORKLOAD_DESC = {
     "cfg2": "cfg2: B=32 H=4 d=128 bf16, L~U[256,1024], max_seq_len=1024, causal, no rab",
     "cfg3": "cfg3: cfg2 + rab [32,4,1024,1024] bf16 + num_target~U[0,32] (group 1)",
@@ -309,7 +314,9 @@ def main():
             "frac_of_bf16_peak": value / (world * peak),
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": None, "peak_kind": ("sustained" if sustained else "burst") + " of " + peaks["source"],
+                "traffic": (TRAFFIC_BYTES_PER_TOKEN[args.workload] * mine.tokens
+                            if args.workload in TRAFFIC_BYTES_PER_TOKEN else None),
+                "peak_kind": ("sustained" if sustained else "burst") + " of " + peaks["source"],
                 "kernel": "hstu_tc_kernel", "kernel_ms": k_ms, "algorithmic_flops_per_launch": mine.flops(),
                 "hbm_gbs_algorithmic": hbm_gbs, "hbm_frac": hbm_gbs / peaks["hbm"],
             },

@@ -1,0 +1,93 @@
+"""Parity at the full sizes of the benchmark workloads: whole-batch comparison where the CPU oracle is quick
+(cfg2, cfg3), and for the large ones (cfg4, cfg5) sampled sequences against the oracle plus size-independent
+properties of the operator: linearity in V, bitwise reproducibility, a clean device status word."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import hstu_oracle as O
+from ops_rec_b200 import cabi
+from ops_rec_b200 import workloads as W
+from tests._parity import assert_parity
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(kw, **extra):
+    out, status = cabi.hstu_jagged_forward(**kw, **extra, return_status=True)
+    torch.cuda.synchronize()
+    return out, status
+
+
+def _cpu(kw):
+    return {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in kw.items()}
+
+
+@pytest.mark.parametrize("name", ["cfg1", "cfg2", "cfg3"])
+def test_whole_batch_against_the_oracle(name):
+    w = W.make_workload(name)
+    kw = W.materialize(w, "cuda")
+    out, status = _run(kw)
+    assert status == 0
+    assert_parity(out.cpu(), _cpu(kw), label=name)
+
+
+def _check_sample(w, kw, out, picks, heads):
+    off = w.offsets()
+    for b in picks:
+        r0, r1 = int(off[b]), int(off[b + 1])
+        for h in heads:
+            bias = kw["attn_bias"]
+            if bias is not None:
+                bias = (bias[h:h + 1] if bias.dim() == 3 else bias[b:b + 1, h:h + 1]).cpu()
+            sub = dict(
+                q=kw["q"][r0:r1, h:h + 1].cpu(), k=kw["k"][r0:r1, h:h + 1].cpu(), v=kw["v"][r0:r1, h:h + 1].cpu(),
+                mask=None, attn_bias=bias, mask_type=0, max_seq_len=kw["max_seq_len"], silu_scale=0.0,
+                seq_offset=torch.tensor([0, r1 - r0]),
+                num_context=None, num_target=None if kw["num_target"] is None else kw["num_target"][b:b + 1].cpu(),
+                target_group_size=kw["target_group_size"], alpha=kw["alpha"])
+            assert_parity(out[r0:r1, h:h + 1].cpu(), sub, label=f"{w.name} seq {b} head {h} L={r1 - r0}")
+
+
+def test_cfg4_sampled_sequences_and_properties():
+    w = W.make_workload("cfg4")
+    kw = W.materialize(w, "cuda")
+    out, status = _run(kw)
+    assert status == 0 and torch.isfinite(out.float()).all()
+    order = np.argsort(w.lengths)
+    picks = [int(order[0]), int(order[len(order) // 2]), int(order[-8]), int(order[-1])]
+    _check_sample(w, kw, out, picks, heads=[0, 7])
+    # bitwise reproducible
+    out2, _ = _run(kw)
+    assert torch.equal(out, out2)
+    # linear in V:  f(q, k, v1 + v2) = f(q, k, v1) + f(q, k, v2)   (bf16 rounding of the three outputs aside)
+    v2 = (torch.randn_like(kw["v"], dtype=torch.float32) * 0.5).to(kw["v"].dtype)
+    vsum = (kw["v"].float() + v2.float()).to(kw["v"].dtype)
+    exact = vsum.float() == kw["v"].float() + v2.float()          # compare where v1 + v2 is exact in bf16
+    o_b, _ = _run(dict(kw, v=v2))
+    o_s, _ = _run(dict(kw, v=vsum))
+    lhs, rhs = o_s.float(), out.float() + o_b.float()
+    scale = rhs.abs().max()
+    frac_exact = exact.float().mean().item()
+    tol = 3e-2 if frac_exact < 0.999 else 1.2e-2
+    assert (lhs - rhs).abs().max() <= tol * scale
+    # the generic kernel agrees on a slice (first 6 sequences)
+    sub = w.subset(np.arange(6))
+    n = sub.tokens
+    kw6 = dict(kw, q=kw["q"][:n], k=kw["k"][:n], v=kw["v"][:n], seq_offset=kw["seq_offset"][:7])
+    a, _ = _run(kw6)
+    b, _ = _run(kw6, flags=cabi.FLAG_FORCE_GENERIC)
+    assert torch.equal(a, out[:n])
+    assert (a.float() - b.float()).abs().max() <= 2e-2 * b.float().abs().max()
+
+
+def test_cfg5_sampled_sequences_shared_bias_and_targets():
+    w = W.make_workload("cfg5")
+    kw = W.materialize(w, "cuda")
+    out, status = _run(kw)
+    assert status == 0 and torch.isfinite(out.float()).all()
+    order = np.argsort(w.lengths)
+    picks = [int(order[0]), int(order[1000]), int(order[2048]), int(order[3500]), int(order[-1])]
+    _check_sample(w, kw, out, picks, heads=[0, 3])
+    out2, _ = _run(kw)
+    assert torch.equal(out, out2)
