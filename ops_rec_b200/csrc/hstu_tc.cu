@@ -43,16 +43,19 @@ constexpr long long kWaitLimitCycles = 2000000000ll;  // ~1 s
 constexpr int kSchedStages = 4;                       // depth of the work-item ring between scheduler and roles
 constexpr int kSchedReaders = 3 + 2 * 128;            // producer lane + two MMA lanes + every thread of both P/O groups
 
-template <int D>
+// kBias: 0 = no attn_bias, 1 = bias read by plain loads (fallback when its rows are not 16-byte aligned),
+// 2 = bias tiles staged in shared memory by TMA.
+template <int D, int kBias = 0>
 struct Cfg {
   static constexpr int kHalves = D / 64;                 // 128-byte swizzle atoms along the head dim
   static constexpr int kHalfBytes = kTileM * 128;        // 128 rows x 128 B
   static constexpr int kTileBytes = kHalves * kHalfBytes;
-  static constexpr int kStages = D == 128 ? 4 : 8;       // K/V ring slots (one tile each)
+  static constexpr int kBiasBytes = kBias == 2 ? 2 * kTileM * kTileN * 2 : 0;  // one 128x128 16-bit tile per Q tile
+  static constexpr int kStages = D == 128 ? (kBias == 2 ? 3 : 4) : 8;          // K/V ring slots (one tile each)
   static constexpr int kQBytes = 2 * kTileBytes;
   static constexpr int kRingBytes = kStages * kTileBytes;
   static constexpr int kBarBytes = 512;
-  static constexpr int kSmemBytes = 1024 + kQBytes + kRingBytes + kBarBytes;
+  static constexpr int kSmemBytes = 1024 + kQBytes + kRingBytes + kBiasBytes + kBarBytes;
   static constexpr int kColO1 = kColO0 + D;
 };
 
@@ -61,6 +64,7 @@ struct Barriers {
   uint64_t s_full[2], p_full[2];
   uint64_t o_full[2], o_free[2];
   uint64_t done[2];
+  uint64_t bias_full[2], bias_free[2];
   uint64_t turn[2];  // MMA issuers alternate: turn[t] completes a phase when issuer t may go
   uint64_t kv_full[8], kv_free[8];
   uint64_t sched_full[kSchedStages], sched_free[kSchedStages];
@@ -184,7 +188,29 @@ struct BiasRow {
   bool row_ok;          // row i exists in the sequence
   bool vec_ok;          // 16-byte loads are aligned
   int maxk, lk;
+  uint32_t smem_row;    // kBias == 2: shared-memory address of this row in the staged tile (first 64-column half)
+  uint32_t swz;         // row & 7: the 16-byte-chunk XOR of the 128-byte swizzle
 };
+
+// 32 consecutive bias values of this thread's row from the TMA-staged tile (two 64-column halves of 128 rows x
+// 128 bytes, 128-byte swizzle), columns ch*32 .. ch*32+31 of the tile.
+template <typename T>
+__device__ __forceinline__ void load_bias32_smem(const BiasRow& br, int ch, float (&bv)[32]) {
+  const uint32_t half = br.smem_row + (ch >> 1) * (kTileM * 128);
+#pragma unroll
+  for (int q4 = 0; q4 < 4; ++q4) {
+    const uint32_t chunk = static_cast<uint32_t>((ch & 1) * 4 + q4) ^ br.swz;
+    uint32_t u0, u1, u2, u3;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u0), "=r"(u1), "=r"(u2), "=r"(u3) : "r"(half + chunk * 16));
+    const uint32_t uu[4] = {u0, u1, u2, u3};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = Pack<T>::unpack(uu[e]);
+      bv[q4 * 8 + e * 2] = f.x;
+      bv[q4 * 8 + e * 2 + 1] = f.y;
+    }
+  }
+}
 
 // 32 consecutive bias values of one row, starting at column jb, as fp32 (0 beyond the sequence).
 template <typename T>
@@ -212,7 +238,7 @@ __device__ __forceinline__ void load_bias32(const BiasRow& br, int jb, float (&b
 // 32 scores of one row (fp32 bits in sr) -> 16 words of packed P.  Branch-free; the arithmetic runs on the
 // packed f32x2 pipe.  x = c_in * s + c_bias * bias covers both orders of alpha and bias (c_bias = c_in gives
 // alpha * (s + bias)).
-template <typename T, bool kBias, bool kMasked>
+template <typename T, int kBias, bool kMasked>
 __device__ __forceinline__ void silu_chunk(const uint32_t (&sr)[32], const float (&bv)[32], uint32_t (&pr)[16],
                                            float c_in, float c_bias, float scale, uint32_t visible) {
   constexpr bool kExact = Pack<T>::kFormat == 0;  // fp16: exp2 + rcp (two MUFU ops); bf16: tanh form (one)
@@ -259,7 +285,7 @@ __device__ __forceinline__ uint32_t visible_bits(const RowBounds& rb, int j0) {
 // The TMEM load of chunk c+1 is in flight while chunk c is computed.  In a tile the mask cuts through
 // (kMasked) every warp classifies each 32 x 32 chunk of its rows: all visible -> plain path, nothing visible ->
 // zeros without any arithmetic, mixed -> per-element select.
-template <typename T, bool kBias, bool kMasked>
+template <typename T, int kBias, bool kMasked>
 __device__ __forceinline__ void p_tile(uint32_t t_s, int c0, const BiasRow& br, const RowBounds& rb, float c_in,
                                        float c_bias, float scale) {
   uint32_t sbuf[2][32];
@@ -275,7 +301,8 @@ __device__ __forceinline__ void p_tile(uint32_t t_s, int c0, const BiasRow& br, 
       all_on = __all_sync(0xffffffffu, vis == 0xffffffffu);
       all_off = __all_sync(0xffffffffu, vis == 0u);
     }
-    if (kBias && !all_off) load_bias32<T>(br, c0 + ch * 32, bv);
+    if (kBias == 1 && !all_off) load_bias32<T>(br, c0 + ch * 32, bv);
+    if (kBias == 2 && !all_off) load_bias32_smem<T>(br, ch, bv);
     ptx::tmem_wait_ld_dep(sbuf[ch & 1]);
     if (ch + 1 < kTileN / 32) ptx::tmem_ld32(t_s + (ch + 1) * 32, sbuf[(ch + 1) & 1]);
     if (all_on) {
@@ -290,18 +317,20 @@ __device__ __forceinline__ void p_tile(uint32_t t_s, int c0, const BiasRow& br, 
   }
 }
 
-template <int D, typename T, bool kBias>
+template <int D, typename T, int kBias>
 __global__ void __launch_bounds__(kThreads, 1)
 hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               const __grid_constant__ CUtensorMap tm_v, const int bias_vec_ok) {
-  using C = Cfg<D>;
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_bias,
+               const int bias_vec_ok) {
+  using C = Cfg<D, kBias>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
   const uint32_t sm_q = base;                    // 2 Q tiles
   const uint32_t sm_ring = base + C::kQBytes;    // K/V ring
-  Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + C::kQBytes + C::kRingBytes);
+  const uint32_t sm_bias = sm_ring + C::kRingBytes;  // kBias == 2: one staged bias tile per Q tile
+  Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + C::kQBytes + C::kRingBytes + C::kBiasBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const Waiter w{&bars->abort_flag, p.ws_header};
@@ -310,6 +339,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     ptx::prefetch_tensormap(&tm_q);
     ptx::prefetch_tensormap(&tm_k);
     ptx::prefetch_tensormap(&tm_v);
+    if (kBias == 2) ptx::prefetch_tensormap(&tm_bias);
     for (int t = 0; t < 2; ++t) {
       ptx::mbar_init(ptx::smem_u32(&bars->q_full[t]), 1);
       ptx::mbar_init(ptx::smem_u32(&bars->q_free[t]), 1);
@@ -320,6 +350,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     }
     ptx::mbar_init(ptx::smem_u32(&bars->done[0]), 1);
     ptx::mbar_init(ptx::smem_u32(&bars->done[1]), 1);
+    for (int t = 0; t < 2; ++t) {
+      ptx::mbar_init(ptx::smem_u32(&bars->bias_full[t]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->bias_free[t]), kTileM);
+    }
     ptx::mbar_init(ptx::smem_u32(&bars->turn[0]), 1);
     ptx::mbar_init(ptx::smem_u32(&bars->turn[1]), 1);
     for (int s = 0; s < C::kStages; ++s) {
@@ -349,6 +383,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t q_uses[2] = {0, 0};
+      uint32_t bias_uses[2] = {0, 0};
       uint32_t ring_pos = 0;
       for (long long idx = feed.next(); idx >= 0; idx = feed.next()) {
         const Item it = load_item(p, idx);
@@ -381,6 +416,24 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
                                hf * 64, it.hk, row);
 #endif
             ++ring_pos;
+            if (kBias == 2 && kv == 0) {
+              // bias tiles of this step, one per Q tile that visits K(j): rows of the (batch, head) block of the
+              // [*, max_seq_len_q, max_seq_len_k] bias viewed as a 2-D matrix, columns j*128 ..
+              const int rows_per_batch = p.bias_bstride ? p.hq * p.maxq : 0;
+#pragma unroll
+              for (int t = 0; t < 2; ++t) {
+                if (j >= it.n(t)) continue;
+                const uint32_t bfull = ptx::smem_u32(&bars->bias_full[t]);
+                w.wait(ptx::smem_u32(&bars->bias_free[t]), (bias_uses[t] & 1u) ^ 1u);
+                ptx::mbar_expect_tx(bfull, kTileM * kTileN * 2);
+                const int brow = it.b * rows_per_batch + it.h * p.maxq + it.r0 + t * kTileM;
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf)
+                  ptx::tma_load_2d(sm_bias + t * (kTileM * kTileN * 2) + hf * (kTileM * 128), &tm_bias, bfull,
+                                   j * kTileN + hf * 64, brow);
+                ++bias_uses[t];
+              }
+            }
           }
         }
       }
@@ -396,6 +449,11 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         if (q_uses[t] == 0) continue;
         const uint32_t bar = ptx::smem_u32(&bars->q_full[t]);
         for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (q_uses[t] - 1) & 1u); ++spin) {}
+      }
+      for (int t = 0; t < 2; ++t) {
+        if (bias_uses[t] == 0) continue;
+        const uint32_t bar = ptx::smem_u32(&bars->bias_full[t]);
+        for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (bias_uses[t] - 1) & 1u); ++spin) {}
       }
     }
   } else if (warp == 1 || warp == 3) {
@@ -550,7 +608,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     // bf16 works on a = y / 2 (tanh form), fp16 on y itself;  x = c_in * s + c_bias * bias
     const float c_in = kExact ? p.alpha : 0.5f * p.alpha;
     const float c_bias = alpha_first ? (kExact ? 1.f : 0.5f) : c_in;
-    uint32_t s_uses = 0, o_uses = 0;
+    uint32_t s_uses = 0, o_uses = 0, b_uses = 0;
 #ifdef HSTU_PROF
     unsigned long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     int trace_n = 0;
@@ -564,7 +622,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       const int i = tile_r0 + row;
       const bool row_ok = i < it.s.lq;
       const RowBounds rb = row_bounds(it.s, row_ok ? i : it.s.lq - 1, p.mask_type, p.group);
-      const long long bias_row = kBias ? static_cast<long long>(it.b) * p.bias_bstride +
+      const long long bias_row = kBias == 1 ? static_cast<long long>(it.b) * p.bias_bstride +
                                              (static_cast<long long>(it.h) * p.maxq + i) * p.maxk
                                        : 0;
       for (int j = 0; j < it.n(t); ++j) {
@@ -577,13 +635,19 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         if (row == 0) TRACE(t, 3);
         ++s_uses;
         ptx::tc_fence_after();
-        const BiasRow br{p.bias, bias_row, row_ok, bias_vec_ok != 0, p.maxk, it.s.lk};
+        const BiasRow br{p.bias, bias_row, row_ok, bias_vec_ok != 0, p.maxk, it.s.lk,
+                         sm_bias + t * (kTileM * kTileN * 2) + row * 128, static_cast<uint32_t>(row & 7)};
+        if (kBias == 2) {
+          w.wait(ptx::smem_u32(&bars->bias_full[t]), b_uses & 1u);
+          ++b_uses;
+        }
 #ifndef HSTU_EXP_NOWG
         if (full)
           p_tile<T, kBias, false>(t_s, c0, br, rb, c_in, c_bias, p.scale);
         else
           p_tile<T, kBias, true>(t_s, c0, br, rb, c_in, c_bias, p.scale);
 #endif
+        if (kBias == 2) ptx::mbar_arrive(ptx::smem_u32(&bars->bias_free[t]));  // staged tile fully read
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar_p);
@@ -677,13 +741,31 @@ bool make_map(CUtensorMap* m, const void* base, long long tokens, int heads, int
   return r == CUDA_SUCCESS;
 }
 
-template <int D, typename T, bool kBias>
+// 2-D view (max_seq_len_k, all rows) of the bias; box = 64 x 128, 128-byte swizzle.
+bool make_bias_map(CUtensorMap* m, const KParams& p, int dtype) {
+  auto fn = encode_fn();
+  if (!fn) return false;
+  const long long rows = static_cast<long long>(p.bias_bstride ? p.batch : 1) * p.hq * p.maxq;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.maxk), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.maxk) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kTileM)};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = dtype == HSTU_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(m, dt, 2, const_cast<void*>(p.bias), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D, typename T, int kBias>
 cudaError_t launch_inst(const KParams& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                        int bias_vec_ok, int grid, cudaStream_t stream) {
+                        const CUtensorMap& mb, int bias_vec_ok, int grid, cudaStream_t stream) {
   auto kern = hstu_tc_kernel<D, T, kBias>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes);
+  constexpr int smem = Cfg<D, kBias>::kSmemBytes;
+  static_assert(smem <= 232448, "shared memory budget of one CTA exceeded");
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(p, mq, mk, mv, bias_vec_ok);
+  kern<<<grid, kThreads, smem, stream>>>(p, mq, mk, mv, mb, bias_vec_ok);
   return cudaGetLastError();
 }
 
@@ -721,10 +803,17 @@ cudaError_t launch_tc(const KParams& p, int dtype, int num_sms, cudaStream_t str
   const int g = static_cast<int>(grid);
   const int vec_ok = p.bias && (p.maxk % 8 == 0) && (p.bias_bstride % 8 == 0) &&
                      (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;
-  const bool bias = p.bias != nullptr;
-#define HSTU_TC_CASE(DD, TT)                                                                 \
-  return bias ? launch_inst<DD, TT, true>(p, mq, mk, mv, vec_ok, g, stream)                 \
-              : launch_inst<DD, TT, false>(p, mq, mk, mv, vec_ok, g, stream)
+  // bias staging by TMA needs 16-byte aligned rows and batch blocks laid out back to back (or one shared block)
+  int bias_mode = p.bias ? 1 : 0;
+  CUtensorMap mb = mq;
+  if (p.bias && vec_ok &&
+      (p.bias_bstride == 0 || p.bias_bstride == static_cast<long long>(p.hq) * p.maxq * p.maxk) &&
+      make_bias_map(&mb, p, dtype))
+    bias_mode = 2;
+#define HSTU_TC_CASE(DD, TT)                                                                   \
+  return bias_mode == 2   ? launch_inst<DD, TT, 2>(p, mq, mk, mv, mb, vec_ok, g, stream)      \
+         : bias_mode == 1 ? launch_inst<DD, TT, 1>(p, mq, mk, mv, mb, vec_ok, g, stream)      \
+                          : launch_inst<DD, TT, 0>(p, mq, mk, mv, mb, vec_ok, g, stream)
   if (dtype == HSTU_DTYPE_BF16) {
     if (p.dqk == 128) { HSTU_TC_CASE(128, __nv_bfloat16); }
     HSTU_TC_CASE(64, __nv_bfloat16);
