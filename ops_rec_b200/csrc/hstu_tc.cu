@@ -40,7 +40,7 @@ constexpr int kThreads = 384;
 constexpr int kTmemCols = 512;
 constexpr int kColS0 = 0, kColS1 = 128, kColO0 = 256;
 constexpr long long kWaitLimitCycles = 2000000000ll;  // ~1 s
-constexpr int kSchedStages = 4;                       // depth of the work-item ring between scheduler and roles
+constexpr int kSchedStages = 8;                       // depth of the work-item ring between scheduler and roles
 constexpr int kSchedReaders = 3 + 2 * 128;            // producer lane + two MMA lanes + every thread of both P/O groups
 
 // kBias: 0 = no attn_bias, 1 = bias read by plain loads (fallback when its rows are not 16-byte aligned),
@@ -54,9 +54,20 @@ struct Cfg {
   static constexpr int kStages = D == 128 ? (kBias == 2 ? 3 : 4) : 8;          // K/V ring slots (one tile each)
   static constexpr int kQBytes = 2 * kTileBytes;
   static constexpr int kRingBytes = kStages * kTileBytes;
-  static constexpr int kBarBytes = 512;
+  static constexpr int kBarBytes = 1024;
   static constexpr int kSmemBytes = 1024 + kQBytes + kRingBytes + kBiasBytes + kBarBytes;
   static constexpr int kColO1 = kColO0 + D;
+};
+
+// A decoded work item: (sequence, head, 256-row q-pair) with the sequence geometry and the number of K tiles each
+// of the two Q tiles visits.  The scheduler warp decodes it once; the other roles read it from shared memory.
+struct Item {
+  SeqInfo s;
+  int b, h, hk, r0;
+  int n0, n1;
+  int nmax;
+  int valid;  // 0 = end of work
+  __device__ __forceinline__ int n(int t) const { return t == 0 ? n0 : n1; }
 };
 
 struct Barriers {
@@ -68,11 +79,11 @@ struct Barriers {
   uint64_t turn[2];  // MMA issuers alternate: turn[t] completes a phase when issuer t may go
   uint64_t kv_full[8], kv_free[8];
   uint64_t sched_full[kSchedStages], sched_free[kSchedStages];
-  long long sched_item[kSchedStages];  // index into the work list, -1 = no more work
+  Item sched_item[kSchedStages];
   uint32_t tmem_base;
   int abort_flag;
 };
-static_assert(sizeof(Barriers) <= 512, "barrier block too large");
+static_assert(sizeof(Barriers) <= 1024, "barrier block too large");
 
 struct Waiter {
   int* abort_flag;
@@ -109,14 +120,14 @@ struct ItemFeed {
   Barriers* bars;
   const Waiter* w;
   uint32_t n;
-  __device__ __forceinline__ long long next() {
+  __device__ __forceinline__ bool next(Item& it) {
     const uint32_t slot = n % kSchedStages;
     w->wait(ptx::smem_u32(&bars->sched_full[slot]), (n / kSchedStages) & 1u);
-    long long idx = *reinterpret_cast<volatile long long*>(&bars->sched_item[slot]);
-    if (*reinterpret_cast<volatile int*>(w->abort_flag)) idx = -1;  // a wait gave up: stop taking work
+    it = bars->sched_item[slot];
+    if (*reinterpret_cast<volatile int*>(w->abort_flag)) it.valid = 0;  // a wait gave up: stop taking work
     ptx::mbar_arrive(ptx::smem_u32(&bars->sched_free[slot]));
     ++n;
-    return idx;
+    return it.valid != 0;
   }
 };
 
@@ -132,14 +143,6 @@ __device__ unsigned long long g_trace[4][512];   // CTA 0: roles 0,1 = P/O group
 #define TRACE(role, code)
 #endif
 
-struct Item {
-  SeqInfo s;
-  int b, h, hk, r0;
-  int n0, n1;  // K tiles each of the two Q tiles visits
-  int nmax;
-  __device__ __forceinline__ int n(int t) const { return t == 0 ? n0 : n1; }
-};
-
 __device__ __forceinline__ Item load_item(const KParams& p, long long idx) {
   Item it;
   it.b = static_cast<int>(p.items[2 * idx]);
@@ -151,6 +154,7 @@ __device__ __forceinline__ Item load_item(const KParams& p, long long idx) {
   it.n0 = kv_tiles_for_rows(it.s, it.r0, kTileM, p.mask_type, kTileN);
   it.n1 = kv_tiles_for_rows(it.s, it.r0 + kTileM, kTileM, p.mask_type, kTileN);
   it.nmax = it.n0 > it.n1 ? it.n0 : it.n1;
+  it.valid = 1;
   return it;
 }
 
@@ -385,8 +389,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       uint32_t q_uses[2] = {0, 0};
       uint32_t bias_uses[2] = {0, 0};
       uint32_t ring_pos = 0;
-      for (long long idx = feed.next(); idx >= 0; idx = feed.next()) {
-        const Item it = load_item(p, idx);
+      for (Item it; feed.next(it);) {
         for (int t = 0; t < 2; ++t) {
           if (it.n(t) == 0) continue;
           const uint32_t full = ptx::smem_u32(&bars->q_full[t]);
@@ -482,8 +485,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       const long long t_all = clock64();
       int trace_n = 0;
 #endif
-      for (long long idx = feed.next(); idx >= 0; idx = feed.next()) {
-        const Item it = load_item(p, idx);
+      for (Item it; feed.next(it);) {
         const int n = it.n(t);
         for (int step = 0; step <= it.nmax; ++step) {
           const uint32_t pos_k = ring_base + 2u * step;             // K(step)
@@ -584,11 +586,14 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       for (uint32_t n = 0;; ++n) {
         const uint32_t slot = n % kSchedStages;
         w.wait(ptx::smem_u32(&bars->sched_free[slot]), ((n / kSchedStages) & 1u) ^ 1u);
-        long long idx = static_cast<long long>(atomicAdd(&p.ws_header[2], 1u));
-        if (idx >= num_items || *reinterpret_cast<volatile int*>(&bars->abort_flag)) idx = -1;
-        *reinterpret_cast<volatile long long*>(&bars->sched_item[slot]) = idx;
+        const long long idx = static_cast<long long>(atomicAdd(&p.ws_header[2], 1u));
+        const bool more = idx < num_items && !*reinterpret_cast<volatile int*>(&bars->abort_flag);
+        Item it;
+        if (more) it = load_item(p, idx);
+        else it.valid = 0;
+        bars->sched_item[slot] = it;
         ptx::mbar_arrive(ptx::smem_u32(&bars->sched_full[slot]));
-        if (idx < 0) break;
+        if (!more) break;
       }
     }
     __syncwarp();
@@ -613,10 +618,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     unsigned long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     int trace_n = 0;
 #endif
-    for (long long idx = feed.next(); idx >= 0; idx = feed.next()) {
-      PROF_T0(t_li);
-      const Item it = load_item(p, idx);
-      PROF_ADD(4, t_li);
+    for (Item it; feed.next(it);) {
       const int tile_r0 = it.r0 + t * kTileM;
       if (tile_r0 >= it.s.lq) continue;
       const int i = tile_r0 + row;
