@@ -28,6 +28,10 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
   __shared__ unsigned s_status;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
+  // Let the attention kernel (launched with programmatic stream serialization) begin its set-up now; it waits
+  // for this grid to complete before it reads the work list.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
   for (int i = tid; i < kBuckets; i += kPreThreads) {
     s_count[i] = 0;
     s_seen[i] = 0;

@@ -129,6 +129,13 @@ struct ItemFeed {
     ++n;
     return it.valid != 0;
   }
+  // Look at the next item without taking it; false when the scheduler has not published it yet.
+  __device__ __forceinline__ bool peek(Item& it) const {
+    const uint32_t slot = n % kSchedStages;
+    if (!ptx::mbar_try_wait(ptx::smem_u32(&bars->sched_full[slot]), (n / kSchedStages) & 1u)) return false;
+    it = bars->sched_item[slot];
+    return it.valid != 0;
+  }
 };
 
 #ifdef HSTU_PROF
@@ -198,82 +205,78 @@ struct BiasRow {
 
 // 32 consecutive bias values of this thread's row from the TMA-staged tile (two 64-column halves of 128 rows x
 // 128 bytes, 128-byte swizzle), columns ch*32 .. ch*32+31 of the tile.
-template <typename T>
-__device__ __forceinline__ void load_bias32_smem(const BiasRow& br, int ch, float (&bv)[32]) {
+// Result: 16 words, two 16-bit values each (converted to fp32 only where they are consumed).
+__device__ __forceinline__ void load_bias32_smem(const BiasRow& br, int ch, uint32_t (&bv)[16]) {
   const uint32_t half = br.smem_row + (ch >> 1) * (kTileM * 128);
 #pragma unroll
   for (int q4 = 0; q4 < 4; ++q4) {
     const uint32_t chunk = static_cast<uint32_t>((ch & 1) * 4 + q4) ^ br.swz;
-    uint32_t u0, u1, u2, u3;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u0), "=r"(u1), "=r"(u2), "=r"(u3) : "r"(half + chunk * 16));
-    const uint32_t uu[4] = {u0, u1, u2, u3};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 f = Pack<T>::unpack(uu[e]);
-      bv[q4 * 8 + e * 2] = f.x;
-      bv[q4 * 8 + e * 2 + 1] = f.y;
-    }
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(bv[q4 * 4]), "=r"(bv[q4 * 4 + 1]), "=r"(bv[q4 * 4 + 2]), "=r"(bv[q4 * 4 + 3])
+                 : "r"(half + chunk * 16));
   }
 }
 
-// 32 consecutive bias values of one row, starting at column jb, as fp32 (0 beyond the sequence).
+// 32 consecutive bias values of one row, starting at column jb, as 16 packed words (0 beyond the sequence).
 template <typename T>
-__device__ __forceinline__ void load_bias32(const BiasRow& br, int jb, float (&bv)[32]) {
+__device__ __forceinline__ void load_bias32(const BiasRow& br, int jb, uint32_t (&bv)[16]) {
   if (br.row_ok && br.vec_ok && jb + 32 <= br.maxk) {
     const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(br.base) + br.row + jb);
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) {
       const uint4 u = __ldg(src + q4);
-      const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = Pack<T>::unpack(uu[e]);
-        bv[q4 * 8 + e * 2] = f.x;
-        bv[q4 * 8 + e * 2 + 1] = f.y;
-      }
+      bv[q4 * 4] = u.x;
+      bv[q4 * 4 + 1] = u.y;
+      bv[q4 * 4 + 2] = u.z;
+      bv[q4 * 4 + 3] = u.w;
     }
   } else {
+    const unsigned short* src = static_cast<const unsigned short*>(br.base);
 #pragma unroll
-    for (int e = 0; e < 32; ++e)
-      bv[e] = (br.row_ok && jb + e < br.lk) ? Pack<T>::one(br.base, br.row + jb + e) : 0.f;
+    for (int e = 0; e < 16; ++e) {
+      const uint32_t lo = (br.row_ok && jb + 2 * e < br.lk) ? src[br.row + jb + 2 * e] : 0u;
+      const uint32_t hi = (br.row_ok && jb + 2 * e + 1 < br.lk) ? src[br.row + jb + 2 * e + 1] : 0u;
+      bv[e] = lo | (hi << 16);
+    }
   }
 }
 
 // 32 scores of one row (fp32 bits in sr) -> 16 words of packed P.  Branch-free; the arithmetic runs on the
 // packed f32x2 pipe.  x = c_in * s + c_bias * bias covers both orders of alpha and bias (c_bias = c_in gives
 // alpha * (s + bias)).
+// One tanh.approx per element is the SFU's whole budget (16 results/clk/SM = 1024 clk per 128 x 128 tile).  Moving
+// half of the columns to an FMA-pipe polynomial was tried: it is faster only without a range check, and any
+// data-dependent branch in this block costs more than it saves, so every element goes through the SFU.
 template <typename T, int kBias, bool kMasked>
-__device__ __forceinline__ void silu_chunk(const uint32_t (&sr)[32], const float (&bv)[32], uint32_t (&pr)[16],
+__device__ __forceinline__ void silu_chunk(const uint32_t (&sr)[32], const uint32_t (&bv)[16], uint32_t (&pr)[16],
                                            float c_in, float c_bias, float scale, uint32_t visible) {
   constexpr bool kExact = Pack<T>::kFormat == 0;  // fp16: exp2 + rcp (two MUFU ops); bf16: tanh form (one)
   const float2 cin2 = make_float2(c_in, c_in);
   const float2 cb2 = make_float2(c_bias, c_bias);
   const float2 sc2 = make_float2(scale, scale);
 #pragma unroll
-  for (int e = 0; e < 32; e += 2) {
-    float2 x = make_float2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1]));
+  for (int e = 0; e < 16; ++e) {
+    float2 x = make_float2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1]));
     if (kBias)
-      x = __ffma2_rn(x, cin2, __fmul2_rn(make_float2(bv[e], bv[e + 1]), cb2));
+      x = __ffma2_rn(x, cin2, __fmul2_rn(Pack<T>::unpack(bv[e]), cb2));
     else
       x = __fmul2_rn(x, cin2);
     const float2 r = __fmul2_rn(x, sc2);
     float2 o;
     if (kExact) {
+      // sigmoid form: o = y*scale / (1 + 2^(-y log2 e))
       const float2 ny = __fmul2_rn(x, make_float2(-1.4426950408889634f, -1.4426950408889634f));
       const float2 d = __fadd2_rn(make_float2(ptx::ex2_approx(ny.x), ptx::ex2_approx(ny.y)), make_float2(1.f, 1.f));
       o = __fmul2_rn(r, make_float2(ptx::rcp_approx(d.x), ptx::rcp_approx(d.y)));
     } else {
-#ifdef HSTU_EXP_NOMUFU
-      o = __ffma2_rn(r, x, r);
-#else
+      // tanh form on x = y/2: o = x*scale*(1 + tanh x)
       o = __ffma2_rn(r, make_float2(ptx::tanh_approx(x.x), ptx::tanh_approx(x.y)), r);
-#endif
     }
     if (kMasked) {  // a select, not a multiply: scores of rows past the sequence end may be Inf or NaN
-      o.x = (visible & (1u << e)) ? o.x : 0.f;
-      o.y = (visible & (2u << e)) ? o.y : 0.f;
+      o.x = (visible & (1u << (2 * e))) ? o.x : 0.f;
+      o.y = (visible & (2u << (2 * e))) ? o.y : 0.f;
     }
-    pr[e >> 1] = Pack<T>::pack(o.x, o.y);
+    pr[e] = Pack<T>::pack(o.x, o.y);
   }
 }
 
@@ -293,7 +296,7 @@ template <typename T, int kBias, bool kMasked>
 __device__ __forceinline__ void p_tile(uint32_t t_s, int c0, const BiasRow& br, const RowBounds& rb, float c_in,
                                        float c_bias, float scale) {
   uint32_t sbuf[2][32];
-  float bv[32];
+  uint32_t bv[16];
   uint32_t pr[16];
   ptx::tmem_ld32(t_s, sbuf[0]);
 #pragma unroll
@@ -306,7 +309,7 @@ __device__ __forceinline__ void p_tile(uint32_t t_s, int c0, const BiasRow& br, 
       all_off = __all_sync(0xffffffffu, vis == 0u);
     }
     if (kBias == 1 && !all_off) load_bias32<T>(br, c0 + ch * 32, bv);
-    if (kBias == 2 && !all_off) load_bias32_smem<T>(br, ch, bv);
+    if (kBias == 2 && !all_off) load_bias32_smem(br, ch, bv);
     ptx::tmem_wait_ld_dep(sbuf[ch & 1]);
     if (ch + 1 < kTileN / 32) ptx::tmem_ld32(t_s + (ch + 1) * 32, sbuf[(ch + 1) & 1]);
     if (all_on) {
@@ -380,14 +383,12 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
   ptx::tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
-  const long long num_items = p.ws_header[1];
   ItemFeed feed{bars, &w, 0};
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t q_uses[2] = {0, 0};
-      uint32_t bias_uses[2] = {0, 0};
       uint32_t ring_pos = 0;
       for (Item it; feed.next(it);) {
         for (int t = 0; t < 2; ++t) {
@@ -419,24 +420,6 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
                                hf * 64, it.hk, row);
 #endif
             ++ring_pos;
-            if (kBias == 2 && kv == 0) {
-              // bias tiles of this step, one per Q tile that visits K(j): rows of the (batch, head) block of the
-              // [*, max_seq_len_q, max_seq_len_k] bias viewed as a 2-D matrix, columns j*128 ..
-              const int rows_per_batch = p.bias_bstride ? p.hq * p.maxq : 0;
-#pragma unroll
-              for (int t = 0; t < 2; ++t) {
-                if (j >= it.n(t)) continue;
-                const uint32_t bfull = ptx::smem_u32(&bars->bias_full[t]);
-                w.wait(ptx::smem_u32(&bars->bias_free[t]), (bias_uses[t] & 1u) ^ 1u);
-                ptx::mbar_expect_tx(bfull, kTileM * kTileN * 2);
-                const int brow = it.b * rows_per_batch + it.h * p.maxq + it.r0 + t * kTileM;
-#pragma unroll
-                for (int hf = 0; hf < 2; ++hf)
-                  ptx::tma_load_2d(sm_bias + t * (kTileM * kTileN * 2) + hf * (kTileM * 128), &tm_bias, bfull,
-                                   j * kTileN + hf * 64, brow);
-                ++bias_uses[t];
-              }
-            }
           }
         }
       }
@@ -453,11 +436,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         const uint32_t bar = ptx::smem_u32(&bars->q_full[t]);
         for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (q_uses[t] - 1) & 1u); ++spin) {}
       }
-      for (int t = 0; t < 2; ++t) {
-        if (bias_uses[t] == 0) continue;
-        const uint32_t bar = ptx::smem_u32(&bars->bias_full[t]);
-        for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (bias_uses[t] - 1) & 1u); ++spin) {}
-      }
+
     }
   } else if (warp == 1 || warp == 3) {
     // ------------------------------------------------------------------ MMA issuers, one per Q tile.
@@ -583,6 +562,11 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     // ------------------------------------------------------------------ scheduler: draws items from the global
     // counter (the list is ordered heaviest sequences first, so this is greedy longest-first list scheduling)
     if (lane == 0) {
+      // The kernel is launched with programmatic stream serialization: everything above overlapped the tail of
+      // the scheduling pre-pass.  Only this thread reads what the pre-pass wrote (item count, work list, and the
+      // offsets it validated), so only it has to wait for that grid to complete.
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      const long long num_items = p.ws_header[1];
       for (uint32_t n = 0;; ++n) {
         const uint32_t slot = n % kSchedStages;
         w.wait(ptx::smem_u32(&bars->sched_free[slot]), ((n / kSchedStages) & 1u) ^ 1u);
@@ -613,7 +597,8 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     // bf16 works on a = y / 2 (tanh form), fp16 on y itself;  x = c_in * s + c_bias * bias
     const float c_in = kExact ? p.alpha : 0.5f * p.alpha;
     const float c_bias = alpha_first ? (kExact ? 1.f : 0.5f) : c_in;
-    uint32_t s_uses = 0, o_uses = 0, b_uses = 0;
+    uint32_t s_uses = 0, o_uses = 0, b_uses = 0, b_loads = 0;
+    bool bias_ahead = false;  // (first thread of the group) the next item's first bias tile is already requested
 #ifdef HSTU_PROF
     unsigned long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     int trace_n = 0;
@@ -627,6 +612,19 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       const long long bias_row = kBias == 1 ? static_cast<long long>(it.b) * p.bias_bstride +
                                              (static_cast<long long>(it.h) * p.maxq + i) * p.maxk
                                        : 0;
+      // kBias == 2: TMA of the 128 x 128 bias tile of K tile jt into this group's staging buffer, once every thread
+      // of the group has released the previous contents.  Only the group's first thread calls it.
+      auto issue_bias = [&](const Item& of, int jt) {
+        const uint32_t bfull = ptx::smem_u32(&bars->bias_full[t]);
+        w.wait(ptx::smem_u32(&bars->bias_free[t]), (b_loads & 1u) ^ 1u);
+        ++b_loads;
+        ptx::mbar_expect_tx(bfull, kTileM * kTileN * 2);
+        const int brow = of.b * (p.bias_bstride ? p.hq * p.maxq : 0) + of.h * p.maxq + of.r0 + t * kTileM;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf)
+          ptx::tma_load_2d(sm_bias + t * (kTileM * kTileN * 2) + hf * (kTileM * 128), &tm_bias, bfull,
+                           jt * kTileN + hf * 64, brow);
+      };
       for (int j = 0; j < it.n(t); ++j) {
         const int c0 = j * kTileN;
         const bool full = tile_is_full(it.s, tile_r0, kTileM, c0, kTileN, p.mask_type, p.group);
@@ -640,16 +638,41 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         const BiasRow br{p.bias, bias_row, row_ok, bias_vec_ok != 0, p.maxk, it.s.lk,
                          sm_bias + t * (kTileM * kTileN * 2) + row * 128, static_cast<uint32_t>(row & 7)};
         if (kBias == 2) {
+          // The group's first thread fetches the staged bias tiles itself: the first one of an item as soon as
+          // the item is known (its latency hides behind the wait for S), each later one as soon as all 128
+          // threads have read the previous tile.
+          if (j == 0 && row == 0 && !bias_ahead) issue_bias(it, 0);
+          bias_ahead = false;
+          __syncwarp();
+          PROF_T0(t_bw);
           w.wait(ptx::smem_u32(&bars->bias_full[t]), b_uses & 1u);
+          PROF_ADD(6, t_bw);
           ++b_uses;
         }
+        PROF_T0(t_pt);
 #ifndef HSTU_EXP_NOWG
         if (full)
           p_tile<T, kBias, false>(t_s, c0, br, rb, c_in, c_bias, p.scale);
         else
           p_tile<T, kBias, true>(t_s, c0, br, rb, c_in, c_bias, p.scale);
 #endif
-        if (kBias == 2) ptx::mbar_arrive(ptx::smem_u32(&bars->bias_free[t]));  // staged tile fully read
+        PROF_ADD(7, t_pt);
+        if (kBias == 2) {
+          ptx::mbar_arrive(ptx::smem_u32(&bars->bias_free[t]));  // this thread has read its row of the staged tile
+          if (row == 0) {
+            if (j + 1 < it.n(t)) {
+              issue_bias(it, j + 1);
+            } else {
+              // last tile of this item: start on the first bias tile of the next item if it is already known
+              Item nx;
+              if (feed.peek(nx) && nx.n(t) > 0) {
+                issue_bias(nx, 0);
+                bias_ahead = true;
+              }
+            }
+          }
+          __syncwarp();
+        }
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar_p);
@@ -695,6 +718,11 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
 #pragma unroll
         for (int q4 = 0; q4 < D / 8; ++q4) dst[q4] = make_uint4(0, 0, 0, 0);
       }
+    }
+    if (kBias == 2 && row == 0 && b_loads > 0) {
+      // the last bias tile this thread requested has landed (already true unless a wait gave up)
+      const uint32_t bar = ptx::smem_u32(&bars->bias_full[t]);
+      for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (b_loads - 1) & 1u); ++spin) {}
     }
 #ifdef HSTU_PROF
     if (row == 0)
@@ -767,8 +795,17 @@ cudaError_t launch_inst(const KParams& p, const CUtensorMap& mq, const CUtensorM
   static_assert(smem <= 232448, "shared memory budget of one CTA exceeded");
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  kern<<<grid, kThreads, smem, stream>>>(p, mq, mk, mv, mb, bias_vec_ok);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // start while the pre-pass is still running
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p, mq, mk, mv, mb, bias_vec_ok);
 }
 
 }  // namespace

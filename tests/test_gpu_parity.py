@@ -164,6 +164,18 @@ def test_alpha_before_bias_flag_and_default_order():
     assert (out.float() - ref2).abs().max() > 5e-2 * ref2.abs().max()
 
 
+@pytest.mark.parametrize("alpha", [0.02, 0.15, 0.5, 2.0])
+@pytest.mark.parametrize("D", [64, 128])
+def test_score_magnitudes_across_the_polynomial_and_sfu_paths(alpha, D):
+    # small arguments take the FMA-pipe polynomial for half of the columns, large ones fall back to tanh.approx
+    # chunk by chunk; alpha sweeps |alpha*(s+bias)| from << 2.5 to >> 2.5
+    args = make_case(4, 2, 2, D, D, 100, 500, BF16, seed=int(alpha * 100) + D, rab="batch", tgt=11, g=1)
+    args["alpha"] = alpha
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label=f"alpha {alpha} d{D}")
+
+
 def test_explicit_silu_scale_and_deterministic_flag():
     args = make_case(3, 2, 2, 64, 64, 1, 257, BF16, seed=4)
     args["silu_scale"] = 0.125
