@@ -55,7 +55,11 @@ struct Cfg {
   static constexpr int kQBytes = 2 * kTileBytes;
   static constexpr int kRingBytes = kStages * kTileBytes;
   static constexpr int kBarBytes = 1024;
-  static constexpr int kSmemBytes = 1024 + kQBytes + kRingBytes + kBiasBytes + kBarBytes;
+  // output staging for TMA stores: per P/O group two buffers of 128 rows x 32 columns (16 bit); not available
+  // when the staged bias tiles already fill the shared memory
+  static constexpr int kOutChunkBytes = kTileM * 32 * 2;
+  static constexpr int kOutBytes = kBias == 2 ? 0 : 2 * 2 * kOutChunkBytes;
+  static constexpr int kSmemBytes = 1024 + kQBytes + kRingBytes + kBiasBytes + kOutBytes + kBarBytes;
   static constexpr int kColO1 = kColO0 + D;
 };
 
@@ -72,7 +76,7 @@ struct Item {
 
 struct Barriers {
   uint64_t q_full[2], q_free[2];
-  uint64_t s_full[2], p_full[2];
+  uint64_t s_full[2], p_full[2][2];  // P is handed over in two 64-column halves
   uint64_t o_full[2], o_free[2];
   uint64_t done[2];
   uint64_t bias_full[2], bias_free[2];
@@ -294,7 +298,7 @@ __device__ __forceinline__ uint32_t visible_bits(const RowBounds& rb, int j0) {
 // zeros without any arithmetic, mixed -> per-element select.
 template <typename T, int kBias, bool kMasked>
 __device__ __forceinline__ void p_tile(uint32_t t_s, int c0, const BiasRow& br, const RowBounds& rb, float c_in,
-                                       float c_bias, float scale) {
+                                       float c_bias, float scale, uint32_t bar_p_half0) {
   uint32_t sbuf[2][32];
   uint32_t bv[16];
   uint32_t pr[16];
@@ -321,6 +325,12 @@ __device__ __forceinline__ void p_tile(uint32_t t_s, int c0, const BiasRow& br, 
       silu_chunk<T, kBias, true>(sbuf[ch & 1], bv, pr, c_in, c_bias, scale, vis);
     }
     ptx::tmem_st16(t_s + ch * 16, pr);
+    if (ch == kTileN / 64 - 1) {
+      // columns 0..63 of P are written: hand them to the MMA issuer now
+      ptx::tmem_wait_st();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(bar_p_half0);
+    }
   }
 }
 
@@ -328,7 +338,7 @@ template <int D, typename T, int kBias>
 __global__ void __launch_bounds__(kThreads, 1)
 hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_bias,
-               const int bias_vec_ok) {
+               const __grid_constant__ CUtensorMap tm_out, const int bias_vec_ok) {
   using C = Cfg<D, kBias>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -337,7 +347,8 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
   const uint32_t sm_q = base;                    // 2 Q tiles
   const uint32_t sm_ring = base + C::kQBytes;    // K/V ring
   const uint32_t sm_bias = sm_ring + C::kRingBytes;  // kBias == 2: one staged bias tile per Q tile
-  Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + C::kQBytes + C::kRingBytes + C::kBiasBytes);
+  const uint32_t sm_out = sm_bias + C::kBiasBytes;   // kOutBytes > 0: output staging, two chunk buffers per group
+  Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + C::kQBytes + C::kRingBytes + C::kBiasBytes + C::kOutBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const Waiter w{&bars->abort_flag, p.ws_header};
@@ -347,11 +358,13 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     ptx::prefetch_tensormap(&tm_k);
     ptx::prefetch_tensormap(&tm_v);
     if (kBias == 2) ptx::prefetch_tensormap(&tm_bias);
+    if (C::kOutBytes > 0) ptx::prefetch_tensormap(&tm_out);
     for (int t = 0; t < 2; ++t) {
       ptx::mbar_init(ptx::smem_u32(&bars->q_full[t]), 1);
       ptx::mbar_init(ptx::smem_u32(&bars->q_free[t]), 1);
       ptx::mbar_init(ptx::smem_u32(&bars->s_full[t]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->p_full[t]), kTileM);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_full[t][0]), kTileM);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_full[t][1]), kTileM);
       ptx::mbar_init(ptx::smem_u32(&bars->o_full[t]), 1);
       ptx::mbar_init(ptx::smem_u32(&bars->o_free[t]), kTileM);
     }
@@ -454,7 +467,8 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       const uint32_t col_o = tmem + (t == 0 ? kColO0 : C::kColO1);
       const uint64_t qbase = kDescK | static_cast<uint64_t>((sm_q + t * C::kTileBytes) >> 4);
       const uint32_t bar_q_full = ptx::smem_u32(&bars->q_full[t]), bar_q_free = ptx::smem_u32(&bars->q_free[t]);
-      const uint32_t bar_s_full = ptx::smem_u32(&bars->s_full[t]), bar_p_full = ptx::smem_u32(&bars->p_full[t]);
+      const uint32_t bar_s_full = ptx::smem_u32(&bars->s_full[t]);
+      const uint32_t bar_p_full = ptx::smem_u32(&bars->p_full[t][0]), bar_p_half1 = ptx::smem_u32(&bars->p_full[t][1]);
       const uint32_t bar_o_full = ptx::smem_u32(&bars->o_full[t]), bar_o_free = ptx::smem_u32(&bars->o_free[t]);
       const uint32_t bar_turn_mine = ptx::smem_u32(&bars->turn[t]), bar_turn_other = ptx::smem_u32(&bars->turn[1 - t]);
       uint32_t q_uses = 0, p_uses = 0, o_uses = 0, turns = 0;
@@ -501,13 +515,19 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           TRACE(2 + t, 1);
           if (do_pv) {
             // O_t (+)= P_t(step-1) . V(step-1)
-            ++p_uses;
             PROF_T0(t_ipv);
             const uint64_t vbase = kDescV | static_cast<uint64_t>((sm_ring + st_v * C::kTileBytes) >> 4);
+            // first 64 keys of P as soon as that half is written; the group is still computing the second half
             ptx::mma_ts(col_o, col_s, vbase, idesc_pv, step > 1 ? 1u : 0u);
 #pragma unroll
-            for (int ks = 1; ks < kTileN / 16; ++ks)
+            for (int ks = 1; ks < kTileN / 32; ++ks)
               ptx::mma_ts(col_o, col_s + ks * 8, vbase + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv, 1u);
+            w.wait(bar_p_half1, p_uses & 1u);
+            ptx::tc_fence_after();
+#pragma unroll
+            for (int ks = kTileN / 32; ks < kTileN / 16; ++ks)
+              ptx::mma_ts(col_o, col_s + ks * 8, vbase + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv, 1u);
+            ++p_uses;
             PROF_ADD(4, t_ipv);
             if (step == n) {
               ptx::mma_commit(bar_o_full);
@@ -589,7 +609,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     const uint32_t t_s = tmem + lane_base + (t == 0 ? kColS0 : kColS1);
     const uint32_t t_o = tmem + lane_base + (t == 0 ? kColO0 : C::kColO1);
     const uint32_t bar_s = ptx::smem_u32(&bars->s_full[t]);
-    const uint32_t bar_p = ptx::smem_u32(&bars->p_full[t]);
+    const uint32_t bar_p = ptx::smem_u32(&bars->p_full[t][0]), bar_p1 = ptx::smem_u32(&bars->p_full[t][1]);
     const uint32_t bar_of = ptx::smem_u32(&bars->o_full[t]);
     const uint32_t bar_oe = ptx::smem_u32(&bars->o_free[t]);
     const bool alpha_first = (p.flags & HSTU_FLAG_ALPHA_BEFORE_BIAS) != 0;
@@ -652,9 +672,9 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         PROF_T0(t_pt);
 #ifndef HSTU_EXP_NOWG
         if (full)
-          p_tile<T, kBias, false>(t_s, c0, br, rb, c_in, c_bias, p.scale);
+          p_tile<T, kBias, false>(t_s, c0, br, rb, c_in, c_bias, p.scale, bar_p);
         else
-          p_tile<T, kBias, true>(t_s, c0, br, rb, c_in, c_bias, p.scale);
+          p_tile<T, kBias, true>(t_s, c0, br, rb, c_in, c_bias, p.scale, bar_p);
 #endif
         PROF_ADD(7, t_pt);
         if (kBias == 2) {
@@ -675,7 +695,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         }
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
-        ptx::mbar_arrive(bar_p);
+        ptx::mbar_arrive(bar_p1);
         if (row == 0) TRACE(t, 4);
         PROF_ADD(1, t_silu);
 #ifdef HSTU_PROF
@@ -691,12 +711,42 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         if (row == 0) TRACE(t, 5);
         ++o_uses;
         ptx::tc_fence_after();
+        // A Q tile that lies wholly inside its sequence leaves through shared memory and TMA stores (128 rows x 32
+        // columns per store, double buffered); a tile cut by the sequence end must not touch the rows after it and
+        // is written row by row.
+        const bool by_tma = C::kOutBytes > 0 && tile_r0 + kTileM <= it.s.lq;
 #pragma unroll 1
         for (int ch = 0; ch < D / 32; ++ch) {
           uint32_t orr[32];
           ptx::tmem_ld32(t_o + ch * 32, orr);
           ptx::tmem_wait_ld();
-          if (row_ok) {
+          if (by_tma) {
+            const uint32_t buf = sm_out + (t * 2 + (ch & 1)) * C::kOutChunkBytes;
+            // the store that last read this buffer (two chunks ago, or the previous item's) is done with it
+            if (row == 0) {
+              if (ch < 2) ptx::bulk_wait_read<0>();
+              else ptx::bulk_wait_read<1>();
+            }
+            ptx::named_bar_sync(1 + t, kTileM);
+            const uint32_t dst_row = buf + row * 64;
+            const uint32_t swz = (row >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index ^ address bits [7,9)
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              const uint32_t u0 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 0]), __uint_as_float(orr[q4 * 8 + 1]));
+              const uint32_t u1 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 2]), __uint_as_float(orr[q4 * 8 + 3]));
+              const uint32_t u2 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 4]), __uint_as_float(orr[q4 * 8 + 5]));
+              const uint32_t u3 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 6]), __uint_as_float(orr[q4 * 8 + 7]));
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + ((q4 ^ swz) << 4)), "r"(u0),
+                           "r"(u1), "r"(u2), "r"(u3)
+                           : "memory");
+            }
+            ptx::fence_proxy_async();
+            ptx::named_bar_sync(1 + t, kTileM);
+            if (row == 0) {
+              ptx::tma_store_3d(&tm_out, buf, ch * 32, it.h, static_cast<int>(it.s.q0) + tile_r0);
+              ptx::bulk_commit();
+            }
+          } else if (row_ok) {
             uint4* dst = reinterpret_cast<uint4*>(orow + ch * 32);
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
@@ -719,6 +769,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         for (int q4 = 0; q4 < D / 8; ++q4) dst[q4] = make_uint4(0, 0, 0, 0);
       }
     }
+    if (C::kOutBytes > 0 && row == 0) ptx::bulk_wait<0>();  // this thread's TMA stores have completed
     if (kBias == 2 && row == 0 && b_loads > 0) {
       // the last bias tile this thread requested has landed (already true unless a wait gave up)
       const uint32_t bar = ptx::smem_u32(&bars->bias_full[t]);
@@ -787,9 +838,25 @@ bool make_bias_map(CUtensorMap* m, const KParams& p, int dtype) {
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 3-D view (dim, heads, tokens) of the output for the epilogue's TMA stores; box = 32 x 1 x 128, 64-byte swizzle.
+bool make_out_map(CUtensorMap* m, const KParams& p, int dtype) {
+  auto fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(p.dv), static_cast<cuuint64_t>(p.hq),
+                        static_cast<cuuint64_t>(p.total_q > 0 ? p.total_q : 1)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(p.dv) * 2, static_cast<cuuint64_t>(p.dv) * 2 * p.hq};
+  cuuint32_t box[3] = {32, 1, static_cast<cuuint32_t>(kTileM)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = dtype == HSTU_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(m, dt, 3, p.out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int D, typename T, int kBias>
 cudaError_t launch_inst(const KParams& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                        const CUtensorMap& mb, int bias_vec_ok, int grid, cudaStream_t stream) {
+                        const CUtensorMap& mb, const CUtensorMap& mo, int bias_vec_ok, int grid,
+                        cudaStream_t stream) {
   auto kern = hstu_tc_kernel<D, T, kBias>;
   constexpr int smem = Cfg<D, kBias>::kSmemBytes;
   static_assert(smem <= 232448, "shared memory budget of one CTA exceeded");
@@ -805,7 +872,7 @@ cudaError_t launch_inst(const KParams& p, const CUtensorMap& mq, const CUtensorM
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, p, mq, mk, mv, mb, bias_vec_ok);
+  return cudaLaunchKernelEx(&cfg, kern, p, mq, mk, mv, mb, mo, bias_vec_ok);
 }
 
 }  // namespace
@@ -849,10 +916,12 @@ cudaError_t launch_tc(const KParams& p, int dtype, int num_sms, cudaStream_t str
       (p.bias_bstride == 0 || p.bias_bstride == static_cast<long long>(p.hq) * p.maxq * p.maxk) &&
       make_bias_map(&mb, p, dtype))
     bias_mode = 2;
-#define HSTU_TC_CASE(DD, TT)                                                                   \
-  return bias_mode == 2   ? launch_inst<DD, TT, 2>(p, mq, mk, mv, mb, vec_ok, g, stream)      \
-         : bias_mode == 1 ? launch_inst<DD, TT, 1>(p, mq, mk, mv, mb, vec_ok, g, stream)      \
-                          : launch_inst<DD, TT, 0>(p, mq, mk, mv, mb, vec_ok, g, stream)
+  CUtensorMap mo;
+  if (!make_out_map(&mo, p, dtype)) return cudaErrorNotSupported;
+#define HSTU_TC_CASE(DD, TT)                                                                       \
+  return bias_mode == 2   ? launch_inst<DD, TT, 2>(p, mq, mk, mv, mb, mo, vec_ok, g, stream)      \
+         : bias_mode == 1 ? launch_inst<DD, TT, 1>(p, mq, mk, mv, mb, mo, vec_ok, g, stream)      \
+                          : launch_inst<DD, TT, 0>(p, mq, mk, mv, mb, mo, vec_ok, g, stream)
   if (dtype == HSTU_DTYPE_BF16) {
     if (p.dqk == 128) { HSTU_TC_CASE(128, __nv_bfloat16); }
     HSTU_TC_CASE(64, __nv_bfloat16);
