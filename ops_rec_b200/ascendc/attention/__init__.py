@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-_OPS = ("hstu_jagged",)
+_OPS = ("hstu_jagged", "hstu_dense")
 
 
 def _available():

@@ -146,6 +146,37 @@ at::Tensor hstu_jagged_delta(const at::Tensor& q, const at::Tensor& k, const at:
                       seq_offset_k, num_context, num_target, target_group_size, alpha, deterministic);
 }
 
+// hstu_dense: [B, S, N, D] layout, every batch row one sequence of S tokens
+// (ascendc/attention/hstu_v1/torch_extension/hstu_dense_plugin.cpp:19-40).  It is the jagged forward over equal
+// lengths: the tensors are viewed as [B*S, N, D] and the offsets 0, S, 2S, ... are generated on the device.
+at::Tensor hstu_dense(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                      const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& attn_bias,
+                      int64_t mask_type, int64_t max_seq_len, double silu_scale) {
+  TORCH_CHECK(q.dim() == 4, "The q should be 4D in dense layout");
+  TORCH_CHECK(k.dim() == 4 && v.dim() == 4, "The k and v should be 4D in dense layout");
+  TORCH_CHECK(k.size(0) == q.size(0) && v.size(0) == q.size(0) && k.size(1) == v.size(1),
+              "q, k and v must agree in batch, and k and v in sequence length");
+  TORCH_CHECK(k.size(1) == q.size(1), "hstu_dense expects q and k of the same sequence length");
+  const int64_t B = q.size(0), S = q.size(1);
+  auto dq = q.contiguous().view({B * S, q.size(2), q.size(3)});
+  auto dk = k.contiguous().view({B * S, k.size(2), k.size(3)});
+  auto dv = v.contiguous().view({B * S, v.size(2), v.size(3)});
+  auto off = at::arange(0, (B + 1) * S, S, q.options().dtype(at::kLong));
+  // the reference takes max_seq_len only for the default silu_scale; the bias / mask row stride is S
+  const double scale = silu_scale == 0.0 ? 1.0 / static_cast<double>(max_seq_len > 0 ? max_seq_len : S) : silu_scale;
+  TORCH_CHECK(max_seq_len >= 1 && max_seq_len <= 20480, "maxSeqLen expect in [1, 20480], but value is ", max_seq_len);
+  auto out = forward_impl(dq, dk, dv, mask, attn_bias, mask_type, S, S, scale, off, off, c10::nullopt, c10::nullopt,
+                          0, 1.0, false);
+  return out.view({B, S, q.size(2), v.size(3)});
+}
+
+at::Tensor hstu_dense_meta(const at::Tensor& q, const at::Tensor&, const at::Tensor&,
+                           const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&, int64_t, int64_t,
+                           double) {
+  TORCH_CHECK(q.dim() == 4, "The q should be 4D in dense layout");
+  return at::empty_like(q, q.options().device(c10::kMeta));
+}
+
 at::Tensor meta_out(const at::Tensor& q, const at::Tensor& v) {
   TORCH_CHECK(q.dim() == 3, "The q should be 3D in jagged layout");
   std::vector<c10::SymInt> shape = {q.sym_size(0), q.sym_size(1), v.sym_size(2)};
@@ -178,14 +209,18 @@ TORCH_LIBRARY_FRAGMENT(ops_rec, m) {
         "int mask_type=0, int max_seq_len=0, int max_seq_len_k=0, float silu_scale=0.0, Tensor seq_offset=None, "
         "Tensor seq_offset_k=None, Tensor? num_context=None, Tensor? num_target=None, int? target_group_size=0, "
         "float? alpha=1.0, bool deterministic=False) -> Tensor");
+  m.def("hstu_dense(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
+        "int max_seq_len=0, float silu_scale=0.0) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(ops_rec, CUDA, m) {
   m.impl("hstu_jagged.equal", TORCH_FN(hstu_jagged_equal));
   m.impl("hstu_jagged.delta", TORCH_FN(hstu_jagged_delta));
+  m.impl("hstu_dense", TORCH_FN(hstu_dense));
 }
 
 TORCH_LIBRARY_IMPL(ops_rec, Meta, m) {
   m.impl("hstu_jagged.equal", TORCH_FN(hstu_jagged_equal_meta));
   m.impl("hstu_jagged.delta", TORCH_FN(hstu_jagged_delta_meta));
+  m.impl("hstu_dense", TORCH_FN(hstu_dense_meta));
 }

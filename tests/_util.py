@@ -18,7 +18,7 @@ def load_fixture(name):
         arr = raw[key]
         if key.endswith("__bf16"):
             out[key[:-6]] = torch.from_numpy(arr.view(np.int16).copy()).view(torch.bfloat16)
-        elif key in ("meta", "alpha"):
+        elif key in ("meta", "alpha", "silu_scale"):
             out[key] = arr
         else:
             out[key] = torch.from_numpy(np.ascontiguousarray(arr))
@@ -27,7 +27,11 @@ def load_fixture(name):
 
 def fixture_names():
     names = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
-    return [n for n in names if n != "mask_grid"]
+    return [n for n in names if n != "mask_grid" and not n.startswith("dense_")]
+
+
+def dense_fixture_names():
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "dense_*.npz")))
 
 
 def fixture_call_args(fx):

@@ -169,6 +169,21 @@ def main():
         _store(path, arrays)
         print(f"{case['name']:28s} tokens_q={arrays['q'].shape[0]:5d} {os.path.getsize(path) / 1024:8.1f} KiB")
 
+    # dense layout (hstu_dense): the reference's numpy golden get_golden (common.py:160-186)
+    for name, (B, S, N, D), bias_on, mask_type in [("dense_fp32_tril_bias", (2, 40, 2, 16), True, 0),
+                                                    ("dense_fp32_none", (3, 17, 1, 32), False, 2),
+                                                    ("dense_fp32_custom", (2, 33, 2, 16), True, 3)]:
+        torch.manual_seed(99 + S)
+        q, k, v = (torch.randn(B, S, N, D) for _ in range(3))
+        bias = torch.randn(B, N, S, S) if bias_on else None
+        mask = torch.randint(0, 2, (B, N, S, S)).float() if mask_type == 3 else None
+        out = v1c.get_golden(q.numpy(), k.numpy(), v.numpy(), mask.numpy() if mask is not None else None,
+                             bias.numpy() if bias is not None else None, mask_type, S, 1.0 / 256)
+        path = os.path.join(HERE, name + ".npz")
+        _store(path, dict(q=q, k=k, v=v, rab=bias, mask=mask, out_v1_numpy=out,
+                          meta=np.array([B, S, N, D, mask_type], dtype=np.int64), silu_scale=np.float64(1.0 / 256)))
+        print(f"{name:28s} {os.path.getsize(path) / 1024:8.1f} KiB")
+
     # mask-only fixtures: the reference's create_causal_mask over a grid incl. the boundary values its tests use
     grid = []
     masks = {}
