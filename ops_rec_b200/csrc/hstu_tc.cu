@@ -722,11 +722,8 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           ptx::tmem_wait_ld();
           if (by_tma) {
             const uint32_t buf = sm_out + (t * 2 + (ch & 1)) * C::kOutChunkBytes;
-            // the store that last read this buffer (two chunks ago, or the previous item's) is done with it
-            if (row == 0) {
-              if (ch < 2) ptx::bulk_wait_read<0>();
-              else ptx::bulk_wait_read<1>();
-            }
+            // the store that last read this buffer (two stores ago, possibly the previous item's) is done with it
+            if (row == 0) ptx::bulk_wait_read<1>();  // all but the newest store (the other buffer's) have been read
             ptx::named_bar_sync(1 + t, kTileM);
             const uint32_t dst_row = buf + row * 64;
             const uint32_t swz = (row >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index ^ address bits [7,9)
