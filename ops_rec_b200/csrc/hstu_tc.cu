@@ -103,9 +103,6 @@ struct Waiter {
     const long long t0 = clock64();
     unsigned spins = 0;
     while (!ptx::mbar_try_wait(bar, parity)) {
-#ifdef HSTU_EXP_SLEEP
-      __nanosleep(HSTU_EXP_SLEEP);
-#endif
       if ((++spins & 0x3ffu) == 0) {
         if (*reinterpret_cast<volatile int*>(abort_flag)) return;
         if (clock64() - t0 > kWaitLimitCycles) {
@@ -142,6 +139,8 @@ struct ItemFeed {
   }
 };
 
+// Investigation build (-DHSTU_PROF): per-role cycle counters and an event trace of CTA 0, read back through
+// hstu_debug_read_prof / hstu_debug_read_trace.  The production library is built without it.
 #ifdef HSTU_PROF
 __device__ unsigned long long g_prof[160][24];
 __device__ unsigned long long g_trace[4][512];   // CTA 0: roles 0,1 = P/O groups, 2,3 = MMA issuers
@@ -423,15 +422,11 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
             const uint32_t use = ring_pos / C::kStages;
             const uint32_t full = ptx::smem_u32(&bars->kv_full[stage]);
             w.wait(ptx::smem_u32(&bars->kv_free[stage]), (use & 1u) ^ 1u);
-#ifdef HSTU_EXP_NOTMA
-            ptx::mbar_arrive(full);
-#else
             ptx::mbar_expect_tx(full, C::kTileBytes);
 #pragma unroll
             for (int hf = 0; hf < C::kHalves; ++hf)
               ptx::tma_load_3d(sm_ring + stage * C::kTileBytes + hf * C::kHalfBytes, kv == 0 ? &tm_k : &tm_v, full,
                                hf * 64, it.hk, row);
-#endif
             ++ring_pos;
           }
         }
@@ -670,12 +665,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           ++b_uses;
         }
         PROF_T0(t_pt);
-#ifndef HSTU_EXP_NOWG
         if (full)
           p_tile<T, kBias, false>(t_s, c0, br, rb, c_in, c_bias, p.scale, bar_p);
         else
           p_tile<T, kBias, true>(t_s, c0, br, rb, c_in, c_bias, p.scale, bar_p);
-#endif
         PROF_ADD(7, t_pt);
         if (kBias == 2) {
           ptx::mbar_arrive(ptx::smem_u32(&bars->bias_free[t]));  // this thread has read its row of the staged tile
