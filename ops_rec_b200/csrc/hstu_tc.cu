@@ -76,11 +76,10 @@ struct Item {
 
 struct Barriers {
   uint64_t q_full[2], q_free[2];
-  uint64_t s_full[2], p_full[2][2];  // P is handed over in two 64-column halves
+  uint64_t s_full[2], p_full[2][2];  // P is handed over in two steps, each by all 256 P/O threads
   uint64_t o_full[2], o_free[2];
   uint64_t done[2];
   uint64_t bias_full[2], bias_free[2];
-  uint64_t turn[2];  // MMA issuers alternate: turn[t] completes a phase when issuer t may go
   uint64_t kv_full[8], kv_free[8];
   uint64_t sched_full[kSchedStages], sched_free[kSchedStages];
   Item sched_item[kSchedStages];
@@ -291,45 +290,48 @@ __device__ __forceinline__ uint32_t visible_bits(const RowBounds& rb, int j0) {
   return low_bits(rb.lim1 - j0) | (low_bits(rb.hi2 + 1 - j0) & ~low_bits(rb.lo2 - j0));
 }
 
-// One 128 x 128 score tile of this thread's row: S (TMEM, fp32) -> P (TMEM, packed 16-bit, in place).
-// The TMEM load of chunk c+1 is in flight while chunk c is computed.  In a tile the mask cuts through
-// (kMasked) every warp classifies each 32 x 32 chunk of its rows: all visible -> plain path, nothing visible ->
-// zeros without any arithmetic, mixed -> per-element select.
+// This thread's 64 columns of one 128 x 128 score tile, its row: S (TMEM, fp32) -> P (TMEM, packed 16-bit).
+// Group g reads the S columns [64g, 64g+64) and writes its half of P inside its own column range (keys 0..63 at
+// columns 0..31, keys 64..127 at columns 64..95), so neither group ever overwrites scores the other still has to
+// read.  The TMEM load of the second 32 columns is in flight while the first 32 are computed.  In a tile the mask
+// cuts through (kMasked) every warp classifies each 32 x 32 chunk of its rows: all visible -> plain path, nothing
+// visible -> zeros without any arithmetic, mixed -> per-element select.
 template <typename T, int kBias, bool kMasked>
-__device__ __forceinline__ void p_tile(uint32_t t_s, int c0, const BiasRow& br, const RowBounds& rb, float c_in,
-                                       float c_bias, float scale, uint32_t bar_p_half0) {
+__device__ __forceinline__ void p_half(uint32_t t_s, int grp, int c0, const BiasRow& br, const RowBounds& rb,
+                                       float c_in, float c_bias, float scale, uint32_t bar_p0) {
   uint32_t sbuf[2][32];
   uint32_t bv[16];
   uint32_t pr[16];
-  ptx::tmem_ld32(t_s, sbuf[0]);
+  const uint32_t s_col = t_s + 64 * grp;
+  const uint32_t p_col = t_s + 64 * grp;
+  const int j0 = c0 + 64 * grp;
+  ptx::tmem_ld32(s_col, sbuf[0]);
 #pragma unroll
-  for (int ch = 0; ch < kTileN / 32; ++ch) {
+  for (int ch = 0; ch < 2; ++ch) {
     uint32_t vis = 0xffffffffu;
     bool all_on = true, all_off = false;
     if (kMasked) {
-      vis = visible_bits(rb, c0 + ch * 32);
+      vis = visible_bits(rb, j0 + ch * 32);
       all_on = __all_sync(0xffffffffu, vis == 0xffffffffu);
       all_off = __all_sync(0xffffffffu, vis == 0u);
     }
-    if (kBias == 1 && !all_off) load_bias32<T>(br, c0 + ch * 32, bv);
-    if (kBias == 2 && !all_off) load_bias32_smem(br, ch, bv);
-    ptx::tmem_wait_ld_dep(sbuf[ch & 1]);
-    if (ch + 1 < kTileN / 32) ptx::tmem_ld32(t_s + (ch + 1) * 32, sbuf[(ch + 1) & 1]);
+    if (kBias == 1 && !all_off) load_bias32<T>(br, j0 + ch * 32, bv);
+    if (kBias == 2 && !all_off) load_bias32_smem(br, 2 * grp + ch, bv);
+    ptx::tmem_wait_ld_dep(sbuf[ch]);
+    if (ch == 0) ptx::tmem_ld32(s_col + 32, sbuf[1]);
     if (all_on) {
-      silu_chunk<T, kBias, false>(sbuf[ch & 1], bv, pr, c_in, c_bias, scale, 0u);
+      silu_chunk<T, kBias, false>(sbuf[ch], bv, pr, c_in, c_bias, scale, 0u);
     } else if (all_off) {
 #pragma unroll
       for (int e = 0; e < 16; ++e) pr[e] = 0u;
     } else {
-      silu_chunk<T, kBias, true>(sbuf[ch & 1], bv, pr, c_in, c_bias, scale, vis);
+      silu_chunk<T, kBias, true>(sbuf[ch], bv, pr, c_in, c_bias, scale, vis);
     }
-    ptx::tmem_st16(t_s + ch * 16, pr);
-    if (ch == kTileN / 64 - 1) {
-      // columns 0..63 of P are written: hand them to the MMA issuer now
-      ptx::tmem_wait_st();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(bar_p_half0);
-    }
+    ptx::tmem_st16(p_col + ch * 16, pr);
+    // hand these 32 keys to the MMA issuer (bar_p0 and the 8 bytes after it: the two hand-over barriers of the tile)
+    ptx::tmem_wait_st();
+    ptx::tc_fence_before();
+    ptx::mbar_arrive(bar_p0 + 8 * ch);
   }
 }
 
@@ -362,19 +364,17 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       ptx::mbar_init(ptx::smem_u32(&bars->q_full[t]), 1);
       ptx::mbar_init(ptx::smem_u32(&bars->q_free[t]), 1);
       ptx::mbar_init(ptx::smem_u32(&bars->s_full[t]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->p_full[t][0]), kTileM);
-      ptx::mbar_init(ptx::smem_u32(&bars->p_full[t][1]), kTileM);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_full[t][0]), 2 * kTileM);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_full[t][1]), 2 * kTileM);
       ptx::mbar_init(ptx::smem_u32(&bars->o_full[t]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->o_free[t]), kTileM);
+      ptx::mbar_init(ptx::smem_u32(&bars->o_free[t]), 2 * kTileM);
     }
     ptx::mbar_init(ptx::smem_u32(&bars->done[0]), 1);
     ptx::mbar_init(ptx::smem_u32(&bars->done[1]), 1);
     for (int t = 0; t < 2; ++t) {
       ptx::mbar_init(ptx::smem_u32(&bars->bias_full[t]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->bias_free[t]), kTileM);
+      ptx::mbar_init(ptx::smem_u32(&bars->bias_free[t]), 2 * kTileM);
     }
-    ptx::mbar_init(ptx::smem_u32(&bars->turn[0]), 1);
-    ptx::mbar_init(ptx::smem_u32(&bars->turn[1]), 1);
     for (int s = 0; s < C::kStages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&bars->kv_full[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&bars->kv_free[s]), 2);  // one arrival from each MMA issuer
@@ -465,8 +465,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       const uint32_t bar_s_full = ptx::smem_u32(&bars->s_full[t]);
       const uint32_t bar_p_full = ptx::smem_u32(&bars->p_full[t][0]), bar_p_half1 = ptx::smem_u32(&bars->p_full[t][1]);
       const uint32_t bar_o_full = ptx::smem_u32(&bars->o_full[t]), bar_o_free = ptx::smem_u32(&bars->o_free[t]);
-      const uint32_t bar_turn_mine = ptx::smem_u32(&bars->turn[t]), bar_turn_other = ptx::smem_u32(&bars->turn[1 - t]);
-      uint32_t q_uses = 0, p_uses = 0, o_uses = 0, turns = 0;
+      uint32_t q_uses = 0, p_uses = 0, o_uses = 0;
       uint32_t ring_base = 0;
 #ifdef HSTU_PROF
       unsigned long long prof_acc[6] = {0, 0, 0, 0, 0, 0};
@@ -483,14 +482,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           const bool do_pv = has_v && step - 1 < n, do_qk = has_k && step < n;
           const uint32_t bar_vf = ptx::smem_u32(&bars->kv_full[st_v]), par_vf = (pos_v / C::kStages) & 1u;
           const uint32_t bar_kf = ptx::smem_u32(&bars->kv_full[st_k]), par_kf = (pos_k / C::kStages) & 1u;
-          // The issuers alternate step by step (tile 0 first): when both P tiles become ready together the pipe
-          // serves one chain, then the other, which keeps the two P/O groups half a period apart - one computes
-          // while the other's MMAs run.  Issuer 0 waits for issuer 1's previous step, issuer 1 for issuer 0's
-          // current one.
-          const uint32_t par_turn = t == 0 ? ((turns & 1u) ^ 1u) : (turns & 1u);
+          // The two issuers run free of each other: the P/O groups serve the tiles in a fixed order (tile 0,
+          // tile 1, tile 0 ...), so the P tiles - and with them the MMA bursts - alternate by themselves.
           // poll everything this step needs at once
           PROF_T0(t_kv);
-          const bool ok_turn = ptx::mbar_try_wait(bar_turn_mine, par_turn);
           const bool ok_v = has_v ? ptx::mbar_try_wait(bar_vf, par_vf) : true;
           const bool ok_k = has_k ? ptx::mbar_try_wait(bar_kf, par_kf) : true;
           const bool ok_p = do_pv ? ptx::mbar_try_wait(bar_p_full, p_uses & 1u) : true;
@@ -503,25 +498,30 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           PROF_T0(t_of);
           if (do_pv && step == 1) w.wait(bar_o_free, (o_uses & 1u) ^ 1u);
           if (do_qk && step == 0) w.wait(bar_q_full, q_uses & 1u);
-          w.wait_polled(ok_turn, bar_turn_mine, par_turn);
           PROF_ADD(2, t_of);
-          ++turns;
           ptx::tc_fence_after();
           TRACE(2 + t, 1);
           if (do_pv) {
             // O_t (+)= P_t(step-1) . V(step-1)
             PROF_T0(t_ipv);
             const uint64_t vbase = kDescV | static_cast<uint64_t>((sm_ring + st_v * C::kTileBytes) >> 4);
-            // first 64 keys of P as soon as that half is written; the group is still computing the second half
-            ptx::mma_ts(col_o, col_s, vbase, idesc_pv, step > 1 ? 1u : 0u);
-#pragma unroll
-            for (int ks = 1; ks < kTileN / 32; ++ks)
-              ptx::mma_ts(col_o, col_s + ks * 8, vbase + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv, 1u);
+            // P arrives in two steps: first the leading 32 keys of both 64-key halves (k-steps 0, 1, 4, 5), then,
+            // while these MMAs run, the rest.  Keys 0..63 sit at columns 0..31 of the S tile, keys 64..127 at
+            // columns 64..95.
+            auto pv = [&](int ks, uint32_t acc) {
+              ptx::mma_ts(col_o, col_s + (ks >> 2) * 64 + (ks & 3) * 8, vbase + static_cast<uint64_t>((ks * 2048) >> 4),
+                          idesc_pv, acc);
+            };
+            pv(0, step > 1 ? 1u : 0u);
+            pv(1, 1u);
+            pv(4, 1u);
+            pv(5, 1u);
             w.wait(bar_p_half1, p_uses & 1u);
             ptx::tc_fence_after();
-#pragma unroll
-            for (int ks = kTileN / 32; ks < kTileN / 16; ++ks)
-              ptx::mma_ts(col_o, col_s + ks * 8, vbase + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv, 1u);
+            pv(2, 1u);
+            pv(3, 1u);
+            pv(6, 1u);
+            pv(7, 1u);
             ++p_uses;
             PROF_ADD(4, t_ipv);
             if (step == n) {
@@ -546,7 +546,6 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
             }
           }
           TRACE(2 + t, 2);
-          ptx::mbar_arrive(bar_turn_other);
           // release the K/V tiles of this step: after this tile's MMAs that read them, or at once when this
           // tile does not visit them (the tile is loaded - waited above - so the arrival counts for its
           // current use)
@@ -598,41 +597,52 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     __syncwarp();
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ P / O groups (thread = row)
-    const int t = (warp - 4) >> 2;                 // Q tile of this group
-    const int row = (threadIdx.x - 128) & 127;     // row inside the tile == TMEM lane
+    // Both groups work on BOTH Q tiles: group g owns the score columns [64g, 64g+64) of every S tile and the
+    // output columns [g*D/2, (g+1)*D/2) of every O tile.  A tile's P is therefore produced by two warps per SM
+    // sub-partition at once (their SFU and FMA work overlaps), the halves of P become ready together, and the
+    // groups are busy on one chain's tile while the other chain's MMAs run.
+    const int grp = (warp - 4) >> 2;
+    const int row = (threadIdx.x - 128) & 127;  // row inside a tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t t_s = tmem + lane_base + (t == 0 ? kColS0 : kColS1);
-    const uint32_t t_o = tmem + lane_base + (t == 0 ? kColO0 : C::kColO1);
-    const uint32_t bar_s = ptx::smem_u32(&bars->s_full[t]);
-    const uint32_t bar_p = ptx::smem_u32(&bars->p_full[t][0]), bar_p1 = ptx::smem_u32(&bars->p_full[t][1]);
-    const uint32_t bar_of = ptx::smem_u32(&bars->o_full[t]);
-    const uint32_t bar_oe = ptx::smem_u32(&bars->o_free[t]);
     const bool alpha_first = (p.flags & HSTU_FLAG_ALPHA_BEFORE_BIAS) != 0;
     constexpr bool kExact = Pack<T>::kFormat == 0;
     // bf16 works on a = y / 2 (tanh form), fp16 on y itself;  x = c_in * s + c_bias * bias
     const float c_in = kExact ? p.alpha : 0.5f * p.alpha;
     const float c_bias = alpha_first ? (kExact ? 1.f : 0.5f) : c_in;
-    uint32_t s_uses = 0, o_uses = 0, b_uses = 0, b_loads = 0;
-    bool bias_ahead = false;  // (first thread of the group) the next item's first bias tile is already requested
+    const bool bias_thread = kBias == 2 && grp == 0 && row == 0;  // fetches the staged bias tiles of both Q tiles
+    uint32_t s_uses[2] = {0, 0}, o_uses[2] = {0, 0}, b_uses[2] = {0, 0}, b_loads[2] = {0, 0};
+    bool bias_ahead[2] = {false, false};  // (bias thread) the next item's first bias tile is already requested
+    uint32_t out_chunks = 0;              // TMA-store chunks issued so far by this group (selects the staging buffer)
 #ifdef HSTU_PROF
     unsigned long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     int trace_n = 0;
 #endif
-    for (Item it; feed.next(it);) {
-      const int tile_r0 = it.r0 + t * kTileM;
-      if (tile_r0 >= it.s.lq) continue;
-      const int i = tile_r0 + row;
-      const bool row_ok = i < it.s.lq;
-      const RowBounds rb = row_bounds(it.s, row_ok ? i : it.s.lq - 1, p.mask_type, p.group);
-      const long long bias_row = kBias == 1 ? static_cast<long long>(it.b) * p.bias_bstride +
-                                             (static_cast<long long>(it.h) * p.maxq + i) * p.maxk
-                                       : 0;
-      // kBias == 2: TMA of the 128 x 128 bias tile of K tile jt into this group's staging buffer, once every thread
-      // of the group has released the previous contents.  Only the group's first thread calls it.
-      auto issue_bias = [&](const Item& of, int jt) {
+#ifdef HSTU_PROF
+    const long long t_role = clock64();
+#endif
+    for (Item it;;) {
+      PROF_T0(t_item);
+      if (!feed.next(it)) break;
+      PROF_ADD(4, t_item);
+      int i_row[2];
+      bool row_ok[2];
+      RowBounds rb[2];
+      long long bias_row[2];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        i_row[t] = it.r0 + t * kTileM + row;
+        row_ok[t] = i_row[t] < it.s.lq;
+        rb[t] = row_bounds(it.s, row_ok[t] ? i_row[t] : it.s.lq - 1, p.mask_type, p.group);
+        bias_row[t] = kBias == 1 ? static_cast<long long>(it.b) * p.bias_bstride +
+                                       (static_cast<long long>(it.h) * p.maxq + i_row[t]) * p.maxk
+                                 : 0;
+      }
+      // kBias == 2: TMA of the 128 x 128 bias tile (Q tile t, K tile jt) into that Q tile's staging buffer, once
+      // all 256 threads have released its previous contents.  Only the bias thread calls it.
+      auto issue_bias = [&](int t, const Item& of, int jt) {
         const uint32_t bfull = ptx::smem_u32(&bars->bias_full[t]);
-        w.wait(ptx::smem_u32(&bars->bias_free[t]), (b_loads & 1u) ^ 1u);
-        ++b_loads;
+        w.wait(ptx::smem_u32(&bars->bias_free[t]), (b_loads[t] & 1u) ^ 1u);
+        ++b_loads[t];
         ptx::mbar_expect_tx(bfull, kTileM * kTileN * 2);
         const int brow = of.b * (p.bias_bstride ? p.hq * p.maxq : 0) + of.h * p.maxq + of.r0 + t * kTileM;
 #pragma unroll
@@ -640,136 +650,147 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           ptx::tma_load_2d(sm_bias + t * (kTileM * kTileN * 2) + hf * (kTileM * 128), &tm_bias, bfull,
                            jt * kTileN + hf * 64, brow);
       };
-      for (int j = 0; j < it.n(t); ++j) {
-        const int c0 = j * kTileN;
-        const bool full = tile_is_full(it.s, tile_r0, kTileM, c0, kTileN, p.mask_type, p.group);
-        PROF_T0(t_ws);
-        w.wait(bar_s, s_uses & 1u);
-        PROF_ADD(0, t_ws);
-        PROF_T0(t_silu);
-        if (row == 0) TRACE(t, 3);
-        ++s_uses;
-        ptx::tc_fence_after();
-        const BiasRow br{p.bias, bias_row, row_ok, bias_vec_ok != 0, p.maxk, it.s.lk,
-                         sm_bias + t * (kTileM * kTileN * 2) + row * 128, static_cast<uint32_t>(row & 7)};
-        if (kBias == 2) {
-          // The group's first thread fetches the staged bias tiles itself: the first one of an item as soon as
-          // the item is known (its latency hides behind the wait for S), each later one as soon as all 128
-          // threads have read the previous tile.
-          if (j == 0 && row == 0 && !bias_ahead) issue_bias(it, 0);
-          bias_ahead = false;
-          __syncwarp();
-          PROF_T0(t_bw);
-          w.wait(ptx::smem_u32(&bars->bias_full[t]), b_uses & 1u);
-          PROF_ADD(6, t_bw);
-          ++b_uses;
+      // the S tiles arrive in the order the MMA issuers alternate: tile 0 step j, tile 1 step j, tile 0 step j+1 ..
+      for (int j = 0; j < it.nmax; ++j) {
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (j >= it.n(t)) continue;
+          const int tile_r0 = it.r0 + t * kTileM;
+          const int c0 = j * kTileN;
+          const bool full = tile_is_full(it.s, tile_r0, kTileM, c0, kTileN, p.mask_type, p.group);
+          const uint32_t t_s = tmem + lane_base + (t == 0 ? kColS0 : kColS1);
+          const uint32_t bar_p = ptx::smem_u32(&bars->p_full[t][0]);
+          PROF_T0(t_ws);
+          w.wait(ptx::smem_u32(&bars->s_full[t]), s_uses[t] & 1u);
+          PROF_ADD(0, t_ws);
+          PROF_T0(t_silu);
+          if (grp == 0 && row == 0) TRACE(t, 3);
+          ++s_uses[t];
+          ptx::tc_fence_after();
+          const BiasRow br{p.bias, bias_row[t], row_ok[t], bias_vec_ok != 0, p.maxk, it.s.lk,
+                           sm_bias + t * (kTileM * kTileN * 2) + row * 128, static_cast<uint32_t>(row & 7)};
+          if (kBias == 2) {
+            // the first bias tile of an item is requested as soon as the item is known (unless it was requested
+            // ahead, at the end of the previous item); its latency hides behind the wait for S
+            if (bias_thread && j == 0 && !bias_ahead[t]) issue_bias(t, it, 0);
+            bias_ahead[t] = false;
+            __syncwarp();
+            w.wait(ptx::smem_u32(&bars->bias_full[t]), b_uses[t] & 1u);
+            ++b_uses[t];
+          }
+          if (full)
+            p_half<T, kBias, false>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p);
+          else
+            p_half<T, kBias, true>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p);
+          if (kBias == 2) {
+            ptx::mbar_arrive(ptx::smem_u32(&bars->bias_free[t]));  // this thread has read its part of the staged tile
+            if (bias_thread) {
+              if (j + 1 < it.n(t)) {
+                issue_bias(t, it, j + 1);
+              } else {
+                // last K tile of this Q tile: start on the first bias tile of the next item if it is known already
+                Item nx;
+                if (feed.peek(nx) && nx.n(t) > 0) {
+                  issue_bias(t, nx, 0);
+                  bias_ahead[t] = true;
+                }
+              }
+            }
+            __syncwarp();
+          }
+          if (grp == 0 && row == 0) TRACE(t, 4);
+          PROF_ADD(1, t_silu);
+#ifdef HSTU_PROF
+          prof_acc[5] += 1;
+#endif
         }
-        PROF_T0(t_pt);
-        if (full)
-          p_tile<T, kBias, false>(t_s, c0, br, rb, c_in, c_bias, p.scale, bar_p);
-        else
-          p_tile<T, kBias, true>(t_s, c0, br, rb, c_in, c_bias, p.scale, bar_p);
-        PROF_ADD(7, t_pt);
-        if (kBias == 2) {
-          ptx::mbar_arrive(ptx::smem_u32(&bars->bias_free[t]));  // this thread has read its row of the staged tile
-          if (row == 0) {
-            if (j + 1 < it.n(t)) {
-              issue_bias(it, j + 1);
-            } else {
-              // last tile of this item: start on the first bias tile of the next item if it is already known
-              Item nx;
-              if (feed.peek(nx) && nx.n(t) > 0) {
-                issue_bias(nx, 0);
-                bias_ahead = true;
+      }
+      // O tiles: this group's half of the columns.  A Q tile that lies wholly inside its sequence leaves through
+      // shared memory and TMA stores (128 rows x 32 columns per store, double buffered); a tile cut by the
+      // sequence end must not touch the rows after it and is written row by row.
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int tile_r0 = it.r0 + t * kTileM;
+        if (tile_r0 >= it.s.lq) continue;
+        const int col0 = grp * (D / 2);
+        T* orow = static_cast<T*>(p.out) + ((it.s.q0 + i_row[t]) * p.hq + it.h) * D + col0;
+        if (it.n(t) > 0) {
+          const uint32_t t_o = tmem + lane_base + (t == 0 ? kColO0 : C::kColO1) + col0;
+          PROF_T0(t_wo);
+          w.wait(ptx::smem_u32(&bars->o_full[t]), o_uses[t] & 1u);
+          PROF_ADD(2, t_wo);
+          PROF_T0(t_epi);
+          if (grp == 0 && row == 0) TRACE(t, 5);
+          ++o_uses[t];
+          ptx::tc_fence_after();
+          const bool by_tma = C::kOutBytes > 0 && tile_r0 + kTileM <= it.s.lq;
+#pragma unroll 1
+          for (int ch = 0; ch < D / 64; ++ch) {
+            uint32_t orr[32];
+            ptx::tmem_ld32(t_o + ch * 32, orr);
+            ptx::tmem_wait_ld();
+            if (by_tma) {
+              const uint32_t buf = sm_out + (grp * 2 + (out_chunks & 1u)) * C::kOutChunkBytes;
+              ++out_chunks;
+              // the store that last read this buffer (two stores ago) is done with it
+              if (row == 0) ptx::bulk_wait_read<1>();
+              ptx::named_bar_sync(1 + grp, kTileM);
+              const uint32_t dst_row = buf + row * 64;
+              const uint32_t swz = (row >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index ^ address bits [7,9)
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const uint32_t u0 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 0]), __uint_as_float(orr[q4 * 8 + 1]));
+                const uint32_t u1 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 2]), __uint_as_float(orr[q4 * 8 + 3]));
+                const uint32_t u2 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 4]), __uint_as_float(orr[q4 * 8 + 5]));
+                const uint32_t u3 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 6]), __uint_as_float(orr[q4 * 8 + 7]));
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + ((q4 ^ swz) << 4)), "r"(u0),
+                             "r"(u1), "r"(u2), "r"(u3)
+                             : "memory");
+              }
+              ptx::fence_proxy_async();
+              ptx::named_bar_sync(1 + grp, kTileM);
+              if (row == 0) {
+                ptx::tma_store_3d(&tm_out, buf, col0 + ch * 32, it.h, static_cast<int>(it.s.q0) + tile_r0);
+                ptx::bulk_commit();
+              }
+            } else if (row_ok[t]) {
+              uint4* dst = reinterpret_cast<uint4*>(orow + ch * 32);
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                uint4 u;
+                u.x = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 0]), __uint_as_float(orr[q4 * 8 + 1]));
+                u.y = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 2]), __uint_as_float(orr[q4 * 8 + 3]));
+                u.z = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 4]), __uint_as_float(orr[q4 * 8 + 5]));
+                u.w = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 6]), __uint_as_float(orr[q4 * 8 + 7]));
+                dst[q4] = u;
               }
             }
           }
-          __syncwarp();
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(ptx::smem_u32(&bars->o_free[t]));
+          if (grp == 0 && row == 0) TRACE(t, 6);
+          PROF_ADD(3, t_epi);
+        } else if (row_ok[t]) {
+          uint4* dst = reinterpret_cast<uint4*>(orow);
+#pragma unroll
+          for (int q4 = 0; q4 < D / 16; ++q4) dst[q4] = make_uint4(0, 0, 0, 0);
         }
-        ptx::tmem_wait_st();
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(bar_p1);
-        if (row == 0) TRACE(t, 4);
-        PROF_ADD(1, t_silu);
-#ifdef HSTU_PROF
-        prof_acc[5] += 1;
-#endif
-      }
-      T* orow = static_cast<T*>(p.out) + ((it.s.q0 + i) * p.hq + it.h) * D;
-      if (it.n(t) > 0) {
-        PROF_T0(t_wo);
-        w.wait(bar_of, o_uses & 1u);
-        PROF_ADD(2, t_wo);
-        PROF_T0(t_epi);
-        if (row == 0) TRACE(t, 5);
-        ++o_uses;
-        ptx::tc_fence_after();
-        // A Q tile that lies wholly inside its sequence leaves through shared memory and TMA stores (128 rows x 32
-        // columns per store, double buffered); a tile cut by the sequence end must not touch the rows after it and
-        // is written row by row.
-        const bool by_tma = C::kOutBytes > 0 && tile_r0 + kTileM <= it.s.lq;
-#pragma unroll 1
-        for (int ch = 0; ch < D / 32; ++ch) {
-          uint32_t orr[32];
-          ptx::tmem_ld32(t_o + ch * 32, orr);
-          ptx::tmem_wait_ld();
-          if (by_tma) {
-            const uint32_t buf = sm_out + (t * 2 + (ch & 1)) * C::kOutChunkBytes;
-            // the store that last read this buffer (two stores ago, possibly the previous item's) is done with it
-            if (row == 0) ptx::bulk_wait_read<1>();  // all but the newest store (the other buffer's) have been read
-            ptx::named_bar_sync(1 + t, kTileM);
-            const uint32_t dst_row = buf + row * 64;
-            const uint32_t swz = (row >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index ^ address bits [7,9)
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              const uint32_t u0 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 0]), __uint_as_float(orr[q4 * 8 + 1]));
-              const uint32_t u1 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 2]), __uint_as_float(orr[q4 * 8 + 3]));
-              const uint32_t u2 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 4]), __uint_as_float(orr[q4 * 8 + 5]));
-              const uint32_t u3 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 6]), __uint_as_float(orr[q4 * 8 + 7]));
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + ((q4 ^ swz) << 4)), "r"(u0),
-                           "r"(u1), "r"(u2), "r"(u3)
-                           : "memory");
-            }
-            ptx::fence_proxy_async();
-            ptx::named_bar_sync(1 + t, kTileM);
-            if (row == 0) {
-              ptx::tma_store_3d(&tm_out, buf, ch * 32, it.h, static_cast<int>(it.s.q0) + tile_r0);
-              ptx::bulk_commit();
-            }
-          } else if (row_ok) {
-            uint4* dst = reinterpret_cast<uint4*>(orow + ch * 32);
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              uint4 u;
-              u.x = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 0]), __uint_as_float(orr[q4 * 8 + 1]));
-              u.y = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 2]), __uint_as_float(orr[q4 * 8 + 3]));
-              u.z = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 4]), __uint_as_float(orr[q4 * 8 + 5]));
-              u.w = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 6]), __uint_as_float(orr[q4 * 8 + 7]));
-              dst[q4] = u;
-            }
-          }
-        }
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(bar_oe);
-        if (row == 0) TRACE(t, 6);
-        PROF_ADD(3, t_epi);
-      } else if (row_ok) {
-        uint4* dst = reinterpret_cast<uint4*>(orow);
-#pragma unroll
-        for (int q4 = 0; q4 < D / 8; ++q4) dst[q4] = make_uint4(0, 0, 0, 0);
       }
     }
     if (C::kOutBytes > 0 && row == 0) ptx::bulk_wait<0>();  // this thread's TMA stores have completed
-    if (kBias == 2 && row == 0 && b_loads > 0) {
-      // the last bias tile this thread requested has landed (already true unless a wait gave up)
-      const uint32_t bar = ptx::smem_u32(&bars->bias_full[t]);
-      for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (b_loads - 1) & 1u); ++spin) {}
+    if (bias_thread) {
+      // the last bias tiles this thread requested have landed (already true unless a wait gave up)
+      for (int t = 0; t < 2; ++t) {
+        if (b_loads[t] == 0) continue;
+        const uint32_t bar = ptx::smem_u32(&bars->bias_full[t]);
+        for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (b_loads[t] - 1) & 1u); ++spin) {}
+      }
     }
 #ifdef HSTU_PROF
-    if (row == 0)
-      for (int i = 0; i < 6; ++i) g_prof[blockIdx.x][t * 6 + i] = prof_acc[i];
-    if (row == 0 && t == 0)
-      for (int i = 6; i < 10; ++i) g_prof[blockIdx.x][10 + i] = prof_acc[i];
+    if (row == 0) {
+      for (int i = 0; i < 6; ++i) g_prof[blockIdx.x][grp * 6 + i] = prof_acc[i];
+      g_prof[blockIdx.x][16 + grp] = clock64() - t_role;
+    }
 #endif
   }
 
