@@ -141,6 +141,32 @@ HSTU_API int hstu_jagged_fwd(const HstuJaggedArgs* args, void* workspace, uint64
  *     events) are safe; two calls that overlap on the GPU race on the block and give undefined results. */
 HSTU_API int hstu_jagged_fwd_static(const HstuJaggedArgs* args, void* stream);
 
+/* ---------------------------------------------------------------------------------------------------- backward
+ * Replaces the aclnnHstuJaggedBackward call of the reference adapter
+ * (ascendc/attention/hstu_v1/torch_extension/hstu_jagged_plugin.cpp:69-138, the EXEC_NPU_CMD at :126-128):
+ * gradients of the forward above with respect to q, k, v and attn_bias.
+ *   dV = P^T dO,  dS = (dO V^T) * scale * alpha * sg * (1 + x - x sg),  dQ = dS K,  dK = dS^T Q,  d_bias = dS
+ * with x = alpha (S + bias), sg = sigmoid(x) * M (hstu_backward_v1/op_kernel/vector_score.h:159-209); with grouped
+ * heads dK / dV sum over the query heads of a group.  `fwd` holds the arguments of the forward call (`fwd.out` is
+ * not read and may be null).  grad_bias is required exactly when fwd.attn_bias is given; EVERY element of it is
+ * written (zeros outside each sequence's visible region), so the caller need not clear it.  attn_bias must be
+ * per-sequence here (bias_batch_stride != 0 unless batch == 1). */
+typedef struct HstuJaggedBwdArgs {
+  uint32_t struct_bytes;  /* sizeof(HstuJaggedBwdArgs) */
+  uint32_t reserved;
+  HstuJaggedArgs fwd;
+  const void* grad_out;   /* [total_q, heads_q, dim_v], same dtype as q */
+  void* grad_q;           /* [total_q, heads_q, dim_qk] */
+  void* grad_k;           /* [total_k, heads_k, dim_qk] */
+  void* grad_v;           /* [total_k, heads_k, dim_v] */
+  void* grad_bias;        /* [batch, heads_q, max_seq_len_q, max_seq_len_k] or null */
+} HstuJaggedBwdArgs;
+
+/* Phase 1 / phase 2 of the backward, same contract as the forward pair (workspace: device memory, 256-byte
+ * aligned, alive until the work completes; asynchronous on `stream`). */
+HSTU_API int hstu_jagged_bwd_get_workspace_size(const HstuJaggedBwdArgs* args, uint64_t* workspace_bytes);
+HSTU_API int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t workspace_bytes, void* stream);
+
 /* Optional: wait for `stream` and fetch the device status word of the last launch that used `workspace`
  * (0 = inputs were consistent).  The reference reads out of bounds on such inputs without noticing. */
 HSTU_API int hstu_jagged_fwd_status(const void* workspace, void* stream, uint32_t* status);

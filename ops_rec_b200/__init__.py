@@ -2,7 +2,8 @@
 
 Importing this package loads the C-ABI library (CUDA kernels for sm_100a) and the torch shim that registers
 `torch.ops.ops_rec.hstu_jagged` (overloads `.equal` and `.delta`) with the reference's schema strings
-(ascendc/attention/hstu_v1/torch_extension/hstu_jagged_plugin.cpp:186-231).  The namespace mirrors the reference
+(ascendc/attention/hstu_v1/torch_extension/hstu_jagged_plugin.cpp:186-231), `hstu_jagged_backward` (same two
+overloads) and the autograd formula that binds it to the forward.  The namespace mirrors the reference
 package (ops_rec/__init__.py:223-236, ops_rec/ascendc/attention/__init__.py:31-49):
 
     import ops_rec_b200 as ops_rec
@@ -59,3 +60,6 @@ def install_as_ops_rec():
 
 load_native()
 from . import ascendc  # noqa: E402,F401
+from . import autograd as _autograd  # noqa: E402
+
+_autograd.register_autograd()

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-_OPS = ("hstu_jagged", "hstu_dense")
+_OPS = ("hstu_jagged", "hstu_jagged_backward", "hstu_dense")
 
 
 def _available():

@@ -24,6 +24,7 @@ EXPORTS = (
     "hstu_jagged_fwd_get_workspace_size", "hstu_jagged_fwd", "hstu_jagged_fwd_status",
     "hstu_jagged_fwd_kernel_kind", "hstu_plan_host", "hstu_debug_mask_host", "hstu_debug_tiles_host",
     "hstu_last_error", "hstu_b200_version", "hstu_jagged_fwd_static",
+    "hstu_jagged_bwd_get_workspace_size", "hstu_jagged_bwd",
 )
 STATIC_SCRATCH_BYTES = 1 << 20
 E_SCRATCH_LIMIT = -6
@@ -41,6 +42,14 @@ class HstuJaggedArgs(C.Structure):
         ("mask_type", C.c_int32), ("max_seq_len_q", C.c_int32), ("max_seq_len_k", C.c_int32),
         ("target_group_size", C.c_int32), ("silu_scale", C.c_float), ("alpha", C.c_float),
         ("flags", C.c_uint32), ("reserved", C.c_uint32),
+    ]
+
+
+class HstuJaggedBwdArgs(C.Structure):
+    _fields_ = [
+        ("struct_bytes", C.c_uint32), ("reserved", C.c_uint32), ("fwd", HstuJaggedArgs),
+        ("grad_out", C.c_void_p), ("grad_q", C.c_void_p), ("grad_k", C.c_void_p), ("grad_v", C.c_void_p),
+        ("grad_bias", C.c_void_p),
     ]
 
 
@@ -83,6 +92,11 @@ def load():
     lib.hstu_debug_tiles_host.restype = C.c_int
     lib.hstu_jagged_fwd_static.argtypes = [A, C.c_void_p]
     lib.hstu_jagged_fwd_static.restype = C.c_int
+    B = C.POINTER(HstuJaggedBwdArgs)
+    lib.hstu_jagged_bwd_get_workspace_size.argtypes = [B, C.POINTER(C.c_uint64)]
+    lib.hstu_jagged_bwd_get_workspace_size.restype = C.c_int
+    lib.hstu_jagged_bwd.argtypes = [B, C.c_void_p, C.c_uint64, C.c_void_p]
+    lib.hstu_jagged_bwd.restype = C.c_int
     lib.hstu_last_error.restype = C.c_char_p
     lib.hstu_b200_version.restype = C.c_int
     _lib = lib
@@ -187,6 +201,45 @@ def hstu_jagged_forward(q, k, v, mask=None, attn_bias=None, mask_type=0, max_seq
             return out, st.value
     del keep
     return out
+
+
+def hstu_jagged_backward(grad, q, k, v, mask=None, attn_bias=None, mask_type=0, max_seq_len=0, max_seq_len_k=0,
+                         silu_scale=0.0, seq_offset=None, seq_offset_k=None, num_context=None, num_target=None,
+                         target_group_size=0, alpha=1.0, *, flags=0, return_status=False):
+    """Gradients (dq, dk, dv, d_bias or None) through hstu_jagged_bwd on CUDA tensors; argument order of
+    ops_rec::hstu_jagged_backward.delta (hstu_v1/torch_extension/hstu_jagged_plugin.cpp:237-252).  d_bias needs no
+    clearing: the kernels write every element of it."""
+    import torch
+    if q.dim() != 3:
+        raise HstuError(-2, "The q should be 3D in jagged layout")
+    if not q.is_cuda:
+        raise HstuError(-2, "tensors must live on a CUDA device; there is no CPU implementation")
+    grad, q, k, v = grad.contiguous(), q.contiguous(), k.contiguous(), v.contiguous()
+    if attn_bias is not None:
+        attn_bias = attn_bias.contiguous()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dbias = torch.empty_like(attn_bias) if attn_bias is not None else None
+    fwd, keep = make_args(q, k, v, None, seq_offset, seq_offset_k=seq_offset_k, mask=mask, attn_bias=attn_bias,
+                          mask_type=mask_type, max_seq_len=max_seq_len, max_seq_len_k=max_seq_len_k or None,
+                          silu_scale=silu_scale, num_context=num_context, num_target=num_target,
+                          target_group_size=target_group_size, alpha=alpha, flags=flags)
+    a = HstuJaggedBwdArgs()
+    a.struct_bytes = C.sizeof(HstuJaggedBwdArgs)
+    a.fwd = fwd
+    a.grad_out, a.grad_q, a.grad_k, a.grad_v = grad.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.grad_bias = dbias.data_ptr() if dbias is not None else None
+    n = C.c_uint64(0)
+    check(load().hstu_jagged_bwd_get_workspace_size(C.byref(a), C.byref(n)))
+    ws = torch.empty(n.value, dtype=torch.uint8, device=q.device)
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+        check(load().hstu_jagged_bwd(C.byref(a), ws.data_ptr(), n.value, stream))
+        if return_status:
+            st = C.c_uint32(0)
+            check(load().hstu_jagged_fwd_status(ws.data_ptr(), stream, C.byref(st)))
+            return (dq, dk, dv, dbias), st.value
+    del keep
+    return dq, dk, dv, dbias
 
 
 def hstu_jagged_forward_static(q, k, v, out, mask=None, attn_bias=None, mask_type=0, max_seq_len=0, silu_scale=0.0,

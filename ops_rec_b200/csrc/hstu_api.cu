@@ -17,6 +17,7 @@ cudaError_t launch_prepass(const KParams& p, bool build_items, cudaStream_t stre
 long long plan_host(const KParams& p, uint32_t* items, long long capacity, uint32_t* status);
 bool tc_supported(const KParams& p, int dtype);
 cudaError_t launch_tc(const KParams& p, int dtype, int num_sms, cudaStream_t stream);
+cudaError_t launch_bwd_generic(const BwdParams& bp, int dtype, cudaStream_t stream);
 }  // namespace hstu
 
 namespace {
@@ -203,6 +204,66 @@ int hstu_jagged_fwd(const HstuJaggedArgs* args, void* workspace, uint64_t worksp
   } else {
     e = hstu::launch_generic(p, args->dtype, stream);
   }
+  if (e != cudaSuccess) return fail(HSTU_E_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+  return HSTU_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ backward
+static int validate_bwd(const HstuJaggedBwdArgs* a) {
+  if (!a) return fail(HSTU_E_NULL, "args is null");
+  if (a->struct_bytes != sizeof(HstuJaggedBwdArgs))
+    return fail(HSTU_E_PARAM, "struct_bytes is %u, this library expects %zu", a->struct_bytes,
+                sizeof(HstuJaggedBwdArgs));
+  int rc = validate(&a->fwd);
+  if (rc) return rc;
+  if (a->fwd.attn_bias && a->fwd.bias_batch_stride == 0 && a->fwd.batch > 1)
+    return fail(HSTU_E_PARAM, "the backward needs a per-sequence attn_bias (a bias shared by the batch has no "
+                              "per-sequence gradient slot)");
+  return HSTU_OK;
+}
+
+int hstu_jagged_bwd_get_workspace_size(const HstuJaggedBwdArgs* args, uint64_t* workspace_bytes) {
+  g_err[0] = 0;
+  if (!workspace_bytes) return fail(HSTU_E_NULL, "workspace_bytes is null");
+  int rc = validate_bwd(args);
+  if (rc) return rc;
+  *workspace_bytes = hstu::kWsHeaderBytes;  // status word only
+  return HSTU_OK;
+}
+
+int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t workspace_bytes, void* stream_v) {
+  g_err[0] = 0;
+  int rc = validate_bwd(args);
+  if (rc) return rc;
+  const HstuJaggedArgs* f = &args->fwd;
+  if (!f->seq_offset_q) return fail(HSTU_E_NULL, "seq_offset is null");
+  if (f->total_q > 0 && (!f->q || !args->grad_out || !args->grad_q)) return fail(HSTU_E_NULL, "q / grad / grad_q is null");
+  if (f->total_k > 0 && (!f->k || !f->v || !args->grad_k || !args->grad_v))
+    return fail(HSTU_E_NULL, "k / v / grad_k / grad_v is null");
+  if (f->attn_bias && !args->grad_bias) return fail(HSTU_E_NULL, "grad_bias is null but attn_bias is given");
+  if (!workspace) return fail(HSTU_E_WORKSPACE, "workspace is null (%llu bytes needed)",
+                              (unsigned long long)hstu::kWsHeaderBytes);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(HSTU_E_WORKSPACE, "workspace must be 256-byte aligned");
+  if (workspace_bytes < hstu::kWsHeaderBytes)
+    return fail(HSTU_E_WORKSPACE, "workspace has %llu bytes, %llu needed", (unsigned long long)workspace_bytes,
+                (unsigned long long)hstu::kWsHeaderBytes);
+  DeviceInfo dev;
+  rc = device_info(&dev);
+  if (rc) return rc;
+  if (dev.major != 10) return fail(HSTU_E_ARCH, "this library is built for sm_100a only; device has compute capability %d.x", dev.major);
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  hstu::BwdParams bp;
+  bp.f = to_params(f, workspace, hstu::kWsHeaderBytes);
+  bp.dout = args->grad_out;
+  bp.dq = args->grad_q;
+  bp.dk = args->grad_k;
+  bp.dv = args->grad_v;
+  bp.dbias = f->attn_bias ? args->grad_bias : nullptr;
+  cudaError_t e = hstu::launch_prepass(bp.f, false, stream);  // input consistency -> status word
+  if (e != cudaSuccess) return fail(HSTU_E_CUDA, "pre-pass launch: %s", cudaGetErrorString(e));
+  if (f->total_q == 0 && f->total_k == 0 && !bp.dbias) return HSTU_OK;
+  e = hstu::launch_bwd_generic(bp, f->dtype, stream);
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "kernel launch: %s", cudaGetErrorString(e));
   return HSTU_OK;
 }

@@ -55,6 +55,16 @@ struct KParams {
   long long item_capacity;
 };
 
+// Backward call: the forward's parameters plus the gradient tensors.
+struct BwdParams {
+  KParams f;          // the forward call (f.out unused)
+  const void* dout;   // [total_q, hq, dv]
+  void* dq;           // [total_q, hq, dqk]
+  void* dk;           // [total_k, hk, dqk]
+  void* dv;           // [total_k, hk, dv]
+  void* dbias;        // [batch, hq, maxq, maxk] or null
+};
+
 struct SeqInfo {
   long long q0, k0;  // first token of the sequence in q / k,v
   int lq, lk;        // lengths

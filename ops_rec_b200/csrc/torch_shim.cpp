@@ -1,4 +1,4 @@
-// torch operator registration for the HSTU jagged forward, dispatching into the C ABI (include/hstu_b200.h).
+// torch operator registration for the HSTU jagged forward and backward, dispatching into the C ABI (include/hstu_b200.h).
 //
 // Schema strings, argument defaults and argument normalisation are those of the reference adapter
 //   ascendc/attention/hstu_v1/torch_extension/hstu_jagged_plugin.cpp:22-67   (normalisation)
@@ -27,21 +27,30 @@ int dtype_code(at::ScalarType t) {
   }
 }
 
-at::Tensor forward_impl(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
-                        const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& attn_bias,
-                        int64_t mask_type, int64_t max_seq_len_q, int64_t max_seq_len_k, double silu_scale,
-                        const at::Tensor& seq_offset, const at::Tensor& seq_offset_k,
-                        const c10::optional<at::Tensor>& num_context, const c10::optional<at::Tensor>& num_target,
-                        const c10::optional<int64_t>& target_group_size, const c10::optional<double>& alpha,
-                        bool deterministic) {
+// The normalised arguments of one call: the C-ABI argument block plus the tensors that own what it points to.
+struct Prepared {
+  HstuJaggedArgs a;
+  at::Tensor q, k, v, bias, cmask, ctx, tgt, off_q, off_k;
+};
+
+Prepared prepare(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                 const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& attn_bias,
+                 int64_t mask_type, int64_t max_seq_len_q, int64_t max_seq_len_k, double silu_scale,
+                 const at::Tensor& seq_offset, const at::Tensor& seq_offset_k,
+                 const c10::optional<at::Tensor>& num_context, const c10::optional<at::Tensor>& num_target,
+                 const c10::optional<int64_t>& target_group_size, const c10::optional<double>& alpha,
+                 bool deterministic) {
   TORCH_CHECK(q.dim() == 3, "The q should be 3D in jagged layout");
   TORCH_CHECK(k.dim() == 3 && v.dim() == 3, "The k and v should be 3D in jagged layout");
   TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda() && seq_offset.is_cuda(),
               "hstu_jagged: tensors must be CUDA tensors (there is no CPU implementation)");
   TORCH_CHECK(seq_offset.scalar_type() == at::kInt || seq_offset.scalar_type() == at::kLong,
               "seq_offset must be int32 or int64");
-  auto off_q = seq_offset.contiguous();
-  auto off_k = seq_offset_k.to(off_q.scalar_type()).contiguous();
+  Prepared pr;
+  at::Tensor& off_q = pr.off_q;
+  at::Tensor& off_k = pr.off_k;
+  off_q = seq_offset.contiguous();
+  off_k = seq_offset_k.to(off_q.scalar_type()).contiguous();
   TORCH_CHECK(off_q.size(0) >= 2, "acSeqOffset params error should have at least two element.");
   TORCH_CHECK(off_k.size(0) >= 2, "acSeqOffsetK params error should have at least two element.");
   TORCH_CHECK(off_k.size(0) == off_q.size(0), "seq_offset and seq_offset_k must have the same length");
@@ -50,11 +59,13 @@ at::Tensor forward_impl(const at::Tensor& q, const at::Tensor& k, const at::Tens
   TORCH_CHECK(k.size(0) == v.size(0) && k.size(1) == v.size(1), "k and v must agree in tokens and heads");
   TORCH_CHECK(k.size(2) == q.size(2), "q and k must have the same head dim");
 
-  c10::cuda::CUDAGuard guard(q.device());
-  auto dq = q.contiguous(), dk = k.contiguous(), dv = v.contiguous();
+  at::Tensor &dq = pr.q, &dk = pr.k, &dv = pr.v;
+  dq = q.contiguous();
+  dk = k.contiguous();
+  dv = v.contiguous();
   const int64_t batch = off_q.size(0) - 1;
 
-  HstuJaggedArgs a;
+  HstuJaggedArgs& a = pr.a;
   memset(&a, 0, sizeof(a));
   a.struct_bytes = sizeof(a);
   a.dtype = dtype_code(q.scalar_type());
@@ -62,7 +73,7 @@ at::Tensor forward_impl(const at::Tensor& q, const at::Tensor& k, const at::Tens
   a.k = dk.data_ptr();
   a.v = dv.data_ptr();
 
-  at::Tensor bias, cmask, ctx, tgt;
+  at::Tensor &bias = pr.bias, &cmask = pr.cmask, &ctx = pr.ctx, &tgt = pr.tgt;
   if (attn_bias.has_value() && attn_bias->defined()) {
     bias = attn_bias->to(q.scalar_type()).contiguous();
     TORCH_CHECK(bias.dim() == 4 || bias.dim() == 3, "attn_bias must be [B,H,Sq,Sk] (or [H,Sq,Sk] shared by the batch)");
@@ -115,7 +126,22 @@ at::Tensor forward_impl(const at::Tensor& q, const at::Tensor& k, const at::Tens
     a.mask = nullptr;
   }
 
-  auto out = at::empty({dq.size(0), dq.size(1), dv.size(2)}, dq.options());
+  return pr;
+}
+
+at::Tensor forward_impl(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                        const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& attn_bias,
+                        int64_t mask_type, int64_t max_seq_len_q, int64_t max_seq_len_k, double silu_scale,
+                        const at::Tensor& seq_offset, const at::Tensor& seq_offset_k,
+                        const c10::optional<at::Tensor>& num_context, const c10::optional<at::Tensor>& num_target,
+                        const c10::optional<int64_t>& target_group_size, const c10::optional<double>& alpha,
+                        bool deterministic) {
+  c10::cuda::CUDAGuard guard(q.device());
+  Prepared pr = prepare(q, k, v, mask, attn_bias, mask_type, max_seq_len_q, max_seq_len_k, silu_scale, seq_offset,
+                        seq_offset_k, num_context, num_target, target_group_size, alpha, deterministic);
+  HstuJaggedArgs& a = pr.a;
+  const at::Tensor& dq = pr.q;
+  auto out = at::empty({pr.q.size(0), pr.q.size(1), pr.v.size(2)}, pr.q.options());
   a.out = out.data_ptr();
 
   uint64_t ws_bytes = 0;
@@ -144,6 +170,102 @@ at::Tensor hstu_jagged_delta(const at::Tensor& q, const at::Tensor& k, const at:
                              c10::optional<int64_t> target_group_size, c10::optional<double> alpha, bool deterministic) {
   return forward_impl(q, k, v, mask, attn_bias, mask_type, max_seq_len, max_seq_len_k, silu_scale, seq_offset,
                       seq_offset_k, num_context, num_target, target_group_size, alpha, deterministic);
+}
+
+// Backward: (dq, dk, dv, d_bias) through hstu_jagged_bwd.  Argument checks of the reference adapter
+// (hstu_jagged_plugin.cpp:77-95); the fourth result is an undefined tensor without attn_bias, as there (:131-137).
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> backward_impl(
+    const at::Tensor& grad, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+    const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& attn_bias, int64_t mask_type,
+    int64_t max_seq_len_q, int64_t max_seq_len_k, double silu_scale, const at::Tensor& seq_offset,
+    const at::Tensor& seq_offset_k, const c10::optional<at::Tensor>& num_context,
+    const c10::optional<at::Tensor>& num_target, const c10::optional<int64_t>& target_group_size,
+    const c10::optional<double>& alpha) {
+  const bool has_ctx = num_context.has_value() && num_context->defined();
+  const bool has_tgt = num_target.has_value() && num_target->defined();
+  if (has_ctx || has_tgt) {
+    TORCH_CHECK(has_ctx, "numContext is required when numTarget or targetGroupSize is not None");
+    TORCH_CHECK(has_tgt, "numTarget is required when numContext or targetGroupSize is not None");
+    TORCH_CHECK(num_context->dim() == 1, "The numContext should be 1D in normal layout");
+    TORCH_CHECK(num_target->dim() == 1, "The numTarget should be 1D in normal layout");
+  }
+  TORCH_CHECK(grad.dim() == 3 && grad.is_cuda() && grad.scalar_type() == q.scalar_type(),
+              "grad must be a 3D CUDA tensor of q's dtype");
+  c10::cuda::CUDAGuard guard(q.device());
+  Prepared pr = prepare(q, k, v, mask, attn_bias, mask_type, max_seq_len_q, max_seq_len_k, silu_scale, seq_offset,
+                        seq_offset_k, num_context, num_target, target_group_size, alpha, false);
+  TORCH_CHECK(grad.size(0) == pr.q.size(0) && grad.size(1) == pr.q.size(1) && grad.size(2) == pr.v.size(2),
+              "grad must be [total_q, heads_q, dim_v]");
+  auto g = grad.contiguous();
+  HstuJaggedBwdArgs b;
+  memset(&b, 0, sizeof(b));
+  b.struct_bytes = sizeof(b);
+  b.fwd = pr.a;
+  auto gq = at::empty_like(pr.q), gk = at::empty_like(pr.k), gv = at::empty_like(pr.v);
+  at::Tensor gbias;
+  if (pr.bias.defined()) {
+    TORCH_CHECK(pr.bias.dim() == 4, "the backward needs attn_bias as [B, heads_q, max_seq_len, max_seq_len_k]");
+    // the kernels write every element of the first `batch` blocks; a bias with spare blocks gets them zeroed
+    gbias = pr.bias.size(0) == pr.a.batch ? at::empty_like(pr.bias) : at::zeros_like(pr.bias);
+    b.grad_bias = gbias.data_ptr();
+  }
+  b.grad_out = g.data_ptr();
+  b.grad_q = gq.data_ptr();
+  b.grad_k = gk.data_ptr();
+  b.grad_v = gv.data_ptr();
+  uint64_t ws_bytes = 0;
+  int rc = hstu_jagged_bwd_get_workspace_size(&b, &ws_bytes);
+  TORCH_CHECK(rc == 0, "hstu_jagged_backward: ", hstu_last_error());
+  auto ws = at::empty({static_cast<int64_t>(ws_bytes)}, pr.q.options().dtype(at::kByte));
+  rc = hstu_jagged_bwd(&b, ws.data_ptr(), ws_bytes, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "hstu_jagged_backward: ", hstu_last_error());
+  return std::make_tuple(gq, gk, gv, gbias);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> hstu_jagged_backward_equal(
+    const at::Tensor& grad, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+    const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& attn_bias, int64_t mask_type,
+    int64_t max_seq_len, double silu_scale, const at::Tensor& seq_offset,
+    const c10::optional<at::Tensor>& num_context, const c10::optional<at::Tensor>& num_target,
+    c10::optional<int64_t> target_group_size, c10::optional<double> alpha) {
+  return backward_impl(grad, q, k, v, mask, attn_bias, mask_type, max_seq_len, max_seq_len, silu_scale, seq_offset,
+                       seq_offset, num_context, num_target, target_group_size, alpha);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> hstu_jagged_backward_delta(
+    const at::Tensor& grad, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+    const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& attn_bias, int64_t mask_type,
+    int64_t max_seq_len, int64_t max_seq_len_k, double silu_scale, const at::Tensor& seq_offset,
+    const at::Tensor& seq_offset_k, const c10::optional<at::Tensor>& num_context,
+    const c10::optional<at::Tensor>& num_target, c10::optional<int64_t> target_group_size,
+    c10::optional<double> alpha) {
+  return backward_impl(grad, q, k, v, mask, attn_bias, mask_type, max_seq_len, max_seq_len_k, silu_scale, seq_offset,
+                       seq_offset_k, num_context, num_target, target_group_size, alpha);
+}
+
+// Meta: gradients shaped like their inputs (hstu_jagged_plugin.cpp:284-310)
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> backward_meta_out(
+    const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const c10::optional<at::Tensor>& attn_bias) {
+  auto m = [](const at::Tensor& t) { return at::empty_like(t, t.options().device(c10::kMeta)); };
+  at::Tensor gb;
+  if (attn_bias.has_value() && attn_bias->defined()) gb = m(*attn_bias);
+  return std::make_tuple(m(q), m(k), m(v), gb);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> hstu_jagged_backward_equal_meta(
+    const at::Tensor&, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+    const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>& attn_bias, int64_t, int64_t, double,
+    const at::Tensor&, const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&, c10::optional<int64_t>,
+    c10::optional<double>) {
+  return backward_meta_out(q, k, v, attn_bias);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> hstu_jagged_backward_delta_meta(
+    const at::Tensor&, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+    const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>& attn_bias, int64_t, int64_t, int64_t, double,
+    const at::Tensor&, const at::Tensor&, const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&,
+    c10::optional<int64_t>, c10::optional<double>) {
+  return backward_meta_out(q, k, v, attn_bias);
 }
 
 // hstu_dense: [B, S, N, D] layout, every batch row one sequence of S tokens
@@ -209,6 +331,14 @@ TORCH_LIBRARY_FRAGMENT(ops_rec, m) {
         "int mask_type=0, int max_seq_len=0, int max_seq_len_k=0, float silu_scale=0.0, Tensor seq_offset=None, "
         "Tensor seq_offset_k=None, Tensor? num_context=None, Tensor? num_target=None, int? target_group_size=0, "
         "float? alpha=1.0, bool deterministic=False) -> Tensor");
+  m.def("hstu_jagged_backward.equal(Tensor grad, Tensor q, Tensor k, Tensor v, Tensor? mask=None, "
+        "Tensor? attn_bias=None, int mask_type=0, int max_seq_len=0, float silu_scale=0.0, Tensor seq_offset=None, "
+        "Tensor? num_context=None, Tensor? num_target=None, int? target_group_size=0, float? alpha=1.0) "
+        "-> (Tensor, Tensor, Tensor, Tensor)");
+  m.def("hstu_jagged_backward.delta(Tensor grad, Tensor q, Tensor k, Tensor v, Tensor? mask=None, "
+        "Tensor? attn_bias=None, int mask_type=0, int max_seq_len=0, int max_seq_len_k=0, float silu_scale=0.0, "
+        "Tensor seq_offset=None, Tensor seq_offset_k=None, Tensor? num_context=None, Tensor? num_target=None, "
+        "int? target_group_size=0, float? alpha=1.0) -> (Tensor, Tensor, Tensor, Tensor)");
   m.def("hstu_dense(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
         "int max_seq_len=0, float silu_scale=0.0) -> Tensor");
 }
@@ -216,11 +346,15 @@ TORCH_LIBRARY_FRAGMENT(ops_rec, m) {
 TORCH_LIBRARY_IMPL(ops_rec, CUDA, m) {
   m.impl("hstu_jagged.equal", TORCH_FN(hstu_jagged_equal));
   m.impl("hstu_jagged.delta", TORCH_FN(hstu_jagged_delta));
+  m.impl("hstu_jagged_backward.equal", TORCH_FN(hstu_jagged_backward_equal));
+  m.impl("hstu_jagged_backward.delta", TORCH_FN(hstu_jagged_backward_delta));
   m.impl("hstu_dense", TORCH_FN(hstu_dense));
 }
 
 TORCH_LIBRARY_IMPL(ops_rec, Meta, m) {
   m.impl("hstu_jagged.equal", TORCH_FN(hstu_jagged_equal_meta));
   m.impl("hstu_jagged.delta", TORCH_FN(hstu_jagged_delta_meta));
+  m.impl("hstu_jagged_backward.equal", TORCH_FN(hstu_jagged_backward_equal_meta));
+  m.impl("hstu_jagged_backward.delta", TORCH_FN(hstu_jagged_backward_delta_meta));
   m.impl("hstu_dense", TORCH_FN(hstu_dense_meta));
 }

@@ -27,7 +27,11 @@ def load_fixture(name):
 
 def fixture_names():
     names = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
-    return [n for n in names if n != "mask_grid" and not n.startswith("dense_")]
+    return [n for n in names if n != "mask_grid" and not n.startswith(("dense_", "bwd_"))]
+
+
+def bwd_fixture_names():
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "bwd_*.npz")))
 
 
 def dense_fixture_names():
@@ -39,7 +43,7 @@ def fixture_call_args(fx):
     B, Hq, Hk, Dqk, Dv, maxL, ctx, tgt, g, mask_type = (int(x) for x in fx["meta"])
     return dict(
         q=fx["q"], k=fx["k"], v=fx["v"], mask=fx.get("mask"), attn_bias=fx.get("rab"), mask_type=mask_type,
-        max_seq_len=maxL, silu_scale=0.0, seq_offset=fx["seq_offset"],
+        max_seq_len=maxL, silu_scale=float(fx["silu_scale"]) if "grad" in fx else 0.0, seq_offset=fx["seq_offset"],
         num_context=fx["num_context"] if ctx else None, num_target=fx["num_target"] if tgt else None,
         target_group_size=g, alpha=float(fx["alpha"]), max_seq_len_k=maxL, seq_offset_k=fx["seq_offset_k"])
 

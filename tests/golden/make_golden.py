@@ -160,9 +160,106 @@ def build_case(case, v1c, v2b):
     return arrays
 
 
+def _load_reference_backward(ref_root):
+    """The reference's backward golden: TestHstuJaggedDemo.pytorch_hstu_mha (autograd through the padded dense
+    forward) from ascendc/attention/hstu_v1/hstu_backward_v1/test/pytest/test_hstu_jagged_backward.py:160-223.
+    The file imports the NPU packages at module level; empty stand-ins satisfy those imports, the golden itself is
+    pure torch."""
+    d = os.path.join(ref_root, "ascendc/attention/hstu_v1/hstu_backward_v1/test/pytest")
+    for name in ("torch_npu", "ops_rec"):
+        sys.modules.setdefault(name, types.ModuleType(name))
+    # its helper module sets the NPU device at import time (test_common_utils.py:30-32)
+    torch.npu = types.SimpleNamespace(config=types.SimpleNamespace(), set_device=lambda *_: None)
+    sys.path.insert(0, d)
+    try:
+        spec = importlib.util.spec_from_file_location("ref_bwd_test", os.path.join(d, "test_hstu_jagged_backward.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    finally:
+        sys.path.remove(d)
+    return mod
+
+
+# name, B, Hq, Hk, Dqk, Dv, maxL, dtype, alpha, silu_scale, rab, ctx, tgt, g, mask_type, delta
+BWD_CASES = [
+    dict(name="bwd_fp32_causal", B=3, Hq=2, Hk=2, Dqk=16, Dv=16, maxL=40, dtype="fp32", alpha=0.5, silu_scale=0.0,
+         rab=False, ctx=0, tgt=0, g=0, mask_type=0),
+    dict(name="bwd_fp32_rab_gqa_ctx_target", B=3, Hq=4, Hk=2, Dqk=24, Dv=16, maxL=70, dtype="fp32", alpha=0.37,
+         silu_scale=1.0 / 256, rab=True, ctx=3, tgt=20, g=3, mask_type=0),
+    dict(name="bwd_fp32_delta_rab", B=3, Hq=2, Hk=1, Dqk=16, Dv=32, maxL=48, dtype="fp32", alpha=0.5, silu_scale=0.0,
+         rab=True, ctx=0, tgt=0, g=0, mask_type=0, delta=True),
+    dict(name="bwd_fp32_mask_none", B=2, Hq=2, Hk=2, Dqk=16, Dv=16, maxL=33, dtype="fp32", alpha=0.25,
+         silu_scale=0.0, rab=True, ctx=0, tgt=0, g=0, mask_type=2),
+    dict(name="bwd_fp32_mask_custom", B=2, Hq=2, Hk=2, Dqk=16, Dv=16, maxL=29, dtype="fp32", alpha=1.0,
+         silu_scale=0.0, rab=True, ctx=0, tgt=0, g=0, mask_type=3),
+    dict(name="bwd_bf16_d64_rab_target", B=3, Hq=2, Hk=2, Dqk=64, Dv=64, maxL=96, dtype="bf16", alpha=0.5,
+         silu_scale=0.0, rab=True, ctx=0, tgt=9, g=1, mask_type=0),
+]
+
+
+def build_bwd_case(case, v1c, ref_bwd):
+    torch.manual_seed(4321 + len(case["name"]))
+    rng = np.random.default_rng(7)
+    B, Hq, Hk, Dqk, Dv, maxL = (case[k] for k in ("B", "Hq", "Hk", "Dqk", "Dv", "maxL"))
+    dtype = torch.float32 if case["dtype"] == "fp32" else torch.bfloat16
+    ctx, tgt, g = case["ctx"], case["tgt"], case["g"]
+    lo = 1 + ctx + tgt
+    len_k = rng.integers(lo, maxL + 1, B)
+    len_q = np.maximum(lo, len_k - rng.integers(0, 9, B)) if case.get("delta") else len_k.copy()
+    offq = np.concatenate([[0], np.cumsum(len_q)]).astype(np.int64)
+    offk = np.concatenate([[0], np.cumsum(len_k)]).astype(np.int64)
+    # value ranges of the reference's own generator (jagged_data_gen, :58-63): uniform(-1, 1)
+    grad = torch.empty(int(offq[-1]), Hq, Dv).uniform_(-1, 1).to(dtype)
+    q = torch.empty(int(offq[-1]), Hq, Dqk).uniform_(-1, 1).to(dtype)
+    k = torch.empty(int(offk[-1]), Hk, Dqk).uniform_(-1, 1).to(dtype)
+    v = torch.empty(int(offk[-1]), Hk, Dv).uniform_(-1, 1).to(dtype)
+    rab = torch.empty(B, Hq, maxL, maxL).uniform_(-1, 1).to(dtype)
+    mask = torch.randint(0, 2, (B, Hq, maxL, maxL)).to(dtype) if case["mask_type"] == 3 else None
+    dense_mask = None
+    if case["mask_type"] == 0:
+        dense_mask = torch.zeros(B, Hq, maxL, maxL)
+        for b in range(B):
+            lq, lk = int(len_q[b]), int(len_k[b])
+            dense_mask[b, :, :lq, :lk] = v1c.create_causal_mask(lq, lk, ctx or None, tgt or None, g or None)
+    elif case["mask_type"] == 3:
+        dense_mask = mask.float()
+
+    def golden(dt):
+        m = dense_mask.to(dt) if dense_mask is not None else None
+        res = ref_bwd.TestHstuJaggedDemo.pytorch_hstu_mha(
+            maxL, case["alpha"], grad.to(dt), q.to(dt).clone(), k.to(dt).clone(), v.to(dt).clone(),
+            torch.from_numpy(offq), torch.from_numpy(offk), m, rab.to(dt).clone(), case["rab"], case["silu_scale"])
+        return [r.detach() if r is not None else None for r in res]
+
+    dq32, dk32, dv32, db32 = golden(torch.float32)
+    arrays = dict(grad=grad, q=q, k=k, v=v, rab=rab if case["rab"] else None, mask=mask, seq_offset=offq,
+                  seq_offset_k=offk, num_context=np.full(B, ctx, dtype=np.int64),
+                  num_target=np.full(B, tgt, dtype=np.int64),
+                  meta=np.array([B, Hq, Hk, Dqk, Dv, maxL, ctx, tgt, g, case["mask_type"]], dtype=np.int64),
+                  alpha=np.float64(case["alpha"]), silu_scale=np.float64(case["silu_scale"]),
+                  dq_fp32=dq32, dk_fp32=dk32, dv_fp32=dv32, dbias_fp32=db32)
+    if dtype != torch.float32:
+        dql, dkl, dvl, dbl = golden(dtype)
+        arrays.update(dq_lowp=dql, dk_lowp=dkl, dv_lowp=dvl, dbias_lowp=dbl)
+    return arrays
+
+
+def main_backward(ref_root, v1c):
+    ref_bwd = _load_reference_backward(ref_root)
+    for case in BWD_CASES:
+        arrays = build_bwd_case(case, v1c, ref_bwd)
+        path = os.path.join(HERE, case["name"] + ".npz")
+        _store(path, arrays)
+        print(f"{case['name']:28s} tokens_q={arrays['q'].shape[0]:5d} {os.path.getsize(path) / 1024:8.1f} KiB")
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     v1c, v2b = _load_reference(ref_root)
+    if len(sys.argv) > 2 and sys.argv[2] == "backward":   # only the backward fixtures
+        main_backward(ref_root, v1c)
+        return
+    main_backward(ref_root, v1c)
     for case in CASES:
         arrays = build_case(case, v1c, v2b)
         path = os.path.join(HERE, case["name"] + ".npz")

@@ -72,3 +72,40 @@ def test_empty_and_padded_offsets():
     mid = torch.cat([off[:2], off[1:]])
     args3 = dict(args, seq_offset=mid, seq_offset_k=mid)
     torch.testing.assert_close(O.hstu_jagged_forward(**args3), base, rtol=0, atol=0)
+
+
+# ---------------------------------------------------------------------------------------------- backward
+# Fixtures: outputs of the reference's autograd golden (hstu_backward_v1/test/pytest/test_hstu_jagged_backward.py
+# :160-223, TestHstuJaggedDemo.pytorch_hstu_mha), produced by tests/golden/make_golden.py.
+from tests._util import bwd_fixture_names  # noqa: E402
+
+
+@pytest.mark.parametrize("name", bwd_fixture_names())
+def test_backward_oracle_matches_reference_autograd_golden(name):
+    fx = load_fixture(name)
+    args = fixture_call_args(fx)
+    got = O.hstu_jagged_backward(fx["grad"], **args, round_mid=False, out_dtype=torch.float32)
+    for g, key in zip(got, ("dq_fp32", "dk_fp32", "dv_fp32", "dbias_fp32")):
+        if key not in fx:
+            assert g is None
+            continue
+        assert g.shape == fx[key].shape
+        torch.testing.assert_close(g, fx[key], rtol=1e-5, atol=2e-6, msg=lambda m: f"{key}: {m}")
+    if "dq_lowp" in fx:
+        # low precision: the rounded-intermediate oracle passes the reference's own acceptance rule (x5)
+        low = O.hstu_jagged_backward(fx["grad"], **args)
+        for g, key in zip(low, ("dq", "dk", "dv", "dbias")):
+            ok, detail = O.double_reference_ok(g, fx[key + "_lowp"], fx[key + "_fp32"], multiplier=5)
+            assert ok, (key, detail)
+
+
+def test_backward_oracle_is_the_gradient_of_the_forward_oracle():
+    fx = load_fixture("bwd_fp32_rab_gqa_ctx_target")
+    args = fixture_call_args(fx)
+    leaves = {n: args[n].double().requires_grad_(True) for n in ("q", "k", "v", "attn_bias")}
+    out = O.hstu_jagged_forward(**dict(args, **leaves), round_p=False, compute_dtype=torch.float64)
+    want = torch.autograd.grad(out, list(leaves.values()), fx["grad"].double())
+    got = O.hstu_jagged_backward(fx["grad"].double(), **dict(args, **{n: t.detach() for n, t in leaves.items()}),
+                                 round_mid=False, compute_dtype=torch.float64)
+    for w, g in zip(want, got):
+        torch.testing.assert_close(g, w, rtol=1e-10, atol=1e-12)
