@@ -182,6 +182,56 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_backward(args, ops_rec, W, full, mine, kw, dev, rank, world, local_rank, warmup, barrier):
+    """--op backward: hstu_jagged_backward on the same workload, inputs resident in HBM.  FLOPs: the five products
+    of the backward (S, dP, dV, dK, dQ) = 2.5 x the forward's two; the kernels recompute S and dP in both passes,
+    which is not counted."""
+    import statistics
+    import torch
+    import torch.distributed as dist
+    hb = ops_rec.ascendc.attention.hstu_jagged_backward
+    grad = torch.randn_like(kw["q"]) * 0.1
+    flops = 2.5 * full.flops()
+
+    def step():
+        return hb(grad, kw["q"], kw["k"], kw["v"], None, kw["attn_bias"], 0, kw["max_seq_len"], 0.0,
+                  kw["seq_offset"], None if kw["num_target"] is None else torch.zeros_like(kw["num_target"]),
+                  kw["num_target"], kw["target_group_size"], kw["alpha"])
+
+    for _ in range(warmup):
+        step()
+    barrier()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        for i in range(args.steps):
+            starts[i].record()
+            step()
+            ends[i].record()
+        barrier()
+    t = torch.tensor([starts[0].elapsed_time(ends[-1])], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        peaks = load_peaks()
+        ms = float(t.item()) / args.steps
+        k_ms = statistics.mean(s.elapsed_time(e) for s, e in zip(starts, ends))
+        achieved = 2.5 * mine.flops() / (k_ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "hstu_jagged_bwd_causal_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": full.dtype, "data": "synthetic",
+            "config": {"workload": WORKLOAD_DESC[args.workload], "op": "hstu_jagged_backward"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["tflops_burst"], "traffic": None,
+                         "kernel": "hstu_bwd_dq_kernel + hstu_bwd_dkv_kernel (fp32 CUDA cores)"},
+            "gpu_launches": 3 * args.steps, "clocks": clocks.summary()}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -189,7 +239,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="cfg4", choices=sorted(WORKLOAD_DESC))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--op", default="forward", choices=["forward", "backward"],
+                    help="backward: time hstu_jagged_backward (device-resident only) instead of the forward")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-chunks", type=int, default=8,
+                    help="the end-to-end run sends the batch through in this many chunks of whole sequences")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--max-batch", type=int, default=0,
                     help="keep only the first N sequences of the workload (small cases for profiler captures)")
@@ -236,6 +290,9 @@ def main():
                   None, kw["num_target"], kw["target_group_size"], kw["alpha"])
 
     warmup = max(args.warmup, 3)
+    if args.op == "backward":
+        run_backward(args, ops_rec, W, full, mine, kw, dev, rank, world, local_rank, warmup, barrier)
+        return
     for _ in range(warmup):
         out = step()
     barrier()
@@ -263,19 +320,69 @@ def main():
         kw["num_target"], kw["target_group_size"], kw["alpha"], return_status=True)
     assert status == 0, f"device status word {status:#x}"
 
-    # ---- end-to-end: pinned host inputs -> device -> operator -> pinned host result, all inside the timed region
+    # ---- end-to-end: pinned host inputs -> device -> operator -> pinned host result, all inside the timed region.
+    # The batch goes through in chunks of whole sequences (equal token counts): chunk c+1 is copied in and chunk c-1
+    # copied out while chunk c is computed, on three streams; every chunk is one call of the public operator.
     host_in = {k: v.cpu().pin_memory() for k, v in kw.items() if isinstance(v, torch.Tensor)}
     host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
     h2d = sum(v.numel() * v.element_size() for v in host_in.values())
     d2h = host_out.numel() * host_out.element_size()
+    off_h = host_in["seq_offset"]
+    nseq = off_h.numel() - 1
+    nchunks = max(1, min(args.e2e_chunks, nseq))
+    cuts = [0]
+    for c in range(1, nchunks):
+        target = int(off_h[-1]) * c // nchunks
+        cuts.append(max(cuts[-1], int(torch.searchsorted(off_h, target))))
+    cuts.append(nseq)
+    per_seq_bias = host_in.get("attn_bias") is not None and host_in["attn_bias"].dim() == 4 \
+        and host_in["attn_bias"].shape[0] == nseq
+    chunks = []
+    for s0, s1 in zip(cuts[:-1], cuts[1:]):
+        if s1 <= s0:
+            continue
+        t0, t1 = int(off_h[s0]), int(off_h[s1])
+        hc = {"q": host_in["q"][t0:t1], "k": host_in["k"][t0:t1], "v": host_in["v"][t0:t1],
+              "seq_offset": (off_h[s0:s1 + 1] - t0).pin_memory()}
+        if host_in.get("num_target") is not None:
+            hc["num_target"] = host_in["num_target"][s0:s1]
+        if host_in.get("attn_bias") is not None and per_seq_bias:
+            hc["attn_bias"] = host_in["attn_bias"][s0:s1]
+        dc = {k: torch.empty(v.shape, dtype=v.dtype, device=dev) for k, v in hc.items()}
+        chunks.append((t0, t1, hc, dc))
+    shared_bias_h = host_in.get("attn_bias") if not per_seq_bias else None
+    shared_bias_d = torch.empty_like(shared_bias_h, device=dev) if shared_bias_h is not None else None
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
 
     def e2e_step():
-        d = {k: v.to(dev, non_blocking=True) for k, v in host_in.items()}
-        o = hj(d["q"], d["k"], d["v"], None, d.get("attn_bias"), 0, kw["max_seq_len"], 0.0, d["seq_offset"], None,
-               d.get("num_target"), kw["target_group_size"], kw["alpha"])
-        host_out.copy_(o, non_blocking=True)
+        cur = torch.cuda.current_stream(dev)
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        with torch.cuda.stream(s_in):
+            if shared_bias_h is not None:
+                shared_bias_d.copy_(shared_bias_h, non_blocking=True)
+        for t0, t1, hc, dc in chunks:
+            with torch.cuda.stream(s_in):
+                for k, v in hc.items():
+                    dc[k].copy_(v, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            cur.wait_event(ready)
+            o = hj(dc["q"], dc["k"], dc["v"], None, dc.get("attn_bias", shared_bias_d), 0, kw["max_seq_len"], 0.0,
+                   dc["seq_offset"], None, dc.get("num_target"), kw["target_group_size"], kw["alpha"])
+            done = torch.cuda.Event()
+            done.record(cur)
+            s_out.wait_event(done)
+            with torch.cuda.stream(s_out):
+                host_out[t0:t1].copy_(o, non_blocking=True)
+            o.record_stream(s_out)
+        cur.wait_stream(s_out)
+        cur.wait_stream(s_in)
 
     e2e_step()
+    torch.cuda.synchronize(dev)
+    # the chunked run gives bit-for-bit what the whole-batch, device-resident run gave
+    assert torch.equal(host_out, out.cpu()), "end-to-end result differs from the device-resident result"
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -321,7 +428,8 @@ def main():
                 "hbm_gbs_algorithmic": hbm_gbs, "hbm_frac": hbm_gbs / peaks["hbm"],
             },
             "e2e": {"value": full.flops() / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.e2e_steps},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.e2e_steps,
+                    "chunks": len(chunks)},
             "gpu_launches": 2 * args.steps,
             "clocks": clocks.summary(),
         }

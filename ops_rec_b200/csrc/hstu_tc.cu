@@ -57,8 +57,8 @@ struct Cfg {
   static constexpr int kBarBytes = 1024;
   // output staging for TMA stores: per P/O group two buffers of 128 rows x 32 columns (16 bit); not available
   // when the staged bias tiles already fill the shared memory
-  static constexpr int kOutChunkBytes = kTileM * 32 * 2;
-  static constexpr int kOutBytes = kBias == 2 ? 0 : 2 * 2 * kOutChunkBytes;
+  static constexpr int kOutWarpBytes = 32 * 32 * 2;   // output staging: 32 rows x 32 columns per warp and buffer
+  static constexpr int kOutBytes = kBias == 2 ? 0 : 8 * 2 * kOutWarpBytes;
   static constexpr int kSmemBytes = 1024 + kQBytes + kRingBytes + kBiasBytes + kOutBytes + kBarBytes;
   static constexpr int kColO1 = kColO0 + D;
 };
@@ -72,6 +72,15 @@ struct Item {
   int nmax;
   int valid;  // 0 = end of work
   __device__ __forceinline__ int n(int t) const { return t == 0 ? n0 : n1; }
+};
+
+// What the output store of one Q tile needs to know.
+struct OutTile {
+  long long q0;   // first token of the sequence
+  int lq;         // its length (rows at or after it are never written)
+  int tile_r0;    // first row of the tile inside the sequence
+  int h;          // query head
+  int n;          // K tiles the tile visited (0: its rows are zeros)
 };
 
 struct Barriers {
@@ -348,7 +357,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
   const uint32_t sm_q = base;                    // 2 Q tiles
   const uint32_t sm_ring = base + C::kQBytes;    // K/V ring
   const uint32_t sm_bias = sm_ring + C::kRingBytes;  // kBias == 2: one staged bias tile per Q tile
-  const uint32_t sm_out = sm_bias + C::kBiasBytes;   // kOutBytes > 0: output staging, two chunk buffers per group
+  const uint32_t sm_out = sm_bias + C::kBiasBytes;   // kOutBytes > 0: output staging, two 2 KB buffers per P/O warp
   Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + C::kQBytes + C::kRingBytes + C::kBiasBytes + C::kOutBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -403,8 +412,9 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       uint32_t q_uses[2] = {0, 0};
       uint32_t ring_pos = 0;
       for (Item it; feed.next(it);) {
-        for (int t = 0; t < 2; ++t) {
-          if (it.n(t) == 0) continue;
+        // Q tile t of this item, once the MMAs of the previous item have finished with the buffer
+        auto load_q = [&](int t) {
+          if (it.n(t) == 0) return;
           const uint32_t full = ptx::smem_u32(&bars->q_full[t]);
           w.wait(ptx::smem_u32(&bars->q_free[t]), (q_uses[t] & 1u) ^ 1u);
           ptx::mbar_expect_tx(full, C::kTileBytes);
@@ -413,7 +423,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           for (int hf = 0; hf < C::kHalves; ++hf)
             ptx::tma_load_3d(sm_q + t * C::kTileBytes + hf * C::kHalfBytes, &tm_q, full, hf * 64, it.h, row);
           ++q_uses[t];
-        }
+        };
+        // Order: Q tile 0, K tile 0, Q tile 1, V tile 0, ...  Tile 1's buffer is released last by the previous
+        // item (its chain ends one step later), and the first S tile of this item needs only Q tile 0 and K tile 0.
+        load_q(0);
         for (int j = 0; j < it.nmax; ++j) {
           const int row = static_cast<int>(it.s.k0) + j * kTileN;
 #pragma unroll
@@ -428,6 +441,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
               ptx::tma_load_3d(sm_ring + stage * C::kTileBytes + hf * C::kHalfBytes, kv == 0 ? &tm_k : &tm_v, full,
                                hf * 64, it.hk, row);
             ++ring_pos;
+            if (j == 0 && kv == 0) load_q(1);
           }
         }
       }
@@ -612,11 +626,86 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     const bool bias_thread = kBias == 2 && grp == 0 && row == 0;  // fetches the staged bias tiles of both Q tiles
     uint32_t s_uses[2] = {0, 0}, o_uses[2] = {0, 0}, b_uses[2] = {0, 0}, b_loads[2] = {0, 0};
     bool bias_ahead[2] = {false, false};  // (bias thread) the next item's first bias tile is already requested
-    uint32_t out_chunks = 0;              // TMA-store chunks issued so far by this group (selects the staging buffer)
+    uint32_t out_chunks = 0;              // TMA-store chunks issued so far by this warp (selects the staging buffer)
 #ifdef HSTU_PROF
     unsigned long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     int trace_n = 0;
 #endif
+    // O tiles: this group's half of the columns.  A Q tile that lies wholly inside its sequence leaves through
+    // shared memory and TMA stores (32 rows x 32 columns per warp and store, double buffered); a tile cut by the
+    // sequence end must not touch the rows after it and is written row by row.
+    auto store_o = [&](const int t, const OutTile& ot) {
+      const int tile_r0 = ot.tile_r0;
+      if (tile_r0 >= ot.lq) return;
+      const int col0 = grp * (D / 2);
+      const bool row_ok_t = tile_r0 + row < ot.lq;
+      T* orow = static_cast<T*>(p.out) + ((ot.q0 + tile_r0 + row) * p.hq + ot.h) * D + col0;
+      if (ot.n > 0) {
+        const uint32_t t_o = tmem + lane_base + (t == 0 ? kColO0 : C::kColO1) + col0;
+        PROF_T0(t_wo);
+        w.wait(ptx::smem_u32(&bars->o_full[t]), o_uses[t] & 1u);
+        PROF_ADD(2, t_wo);
+        PROF_T0(t_epi);
+        if (grp == 0 && row == 0) TRACE(t, 5);
+        ++o_uses[t];
+        ptx::tc_fence_after();
+        const bool by_tma = C::kOutBytes > 0 && tile_r0 + kTileM <= ot.lq;
+#pragma unroll 1
+        for (int ch = 0; ch < D / 64; ++ch) {
+          uint32_t orr[32];
+          ptx::tmem_ld32(t_o + ch * 32, orr);
+          ptx::tmem_wait_ld();
+          if (by_tma) {
+            // every warp stores its own 32 rows (its TMEM lane quarter) with its own TMA store: no CTA-level
+            // barrier, only the warp's lanes meet
+            const uint32_t buf = sm_out + ((warp - 4) * 2 + (out_chunks & 1u)) * C::kOutWarpBytes;
+            ++out_chunks;
+            // the store that last read this buffer (two stores ago) is done with it
+            if (lane == 0) ptx::bulk_wait_read<1>();
+            __syncwarp();
+            const uint32_t dst_row = buf + lane * 64;
+            const uint32_t swz = (lane >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index ^ address bits [7,9)
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              const uint32_t u0 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 0]), __uint_as_float(orr[q4 * 8 + 1]));
+              const uint32_t u1 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 2]), __uint_as_float(orr[q4 * 8 + 3]));
+              const uint32_t u2 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 4]), __uint_as_float(orr[q4 * 8 + 5]));
+              const uint32_t u3 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 6]), __uint_as_float(orr[q4 * 8 + 7]));
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + ((q4 ^ swz) << 4)), "r"(u0),
+                           "r"(u1), "r"(u2), "r"(u3)
+                           : "memory");
+            }
+            ptx::fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_3d(&tm_out, buf, col0 + ch * 32, ot.h,
+                                static_cast<int>(ot.q0) + tile_r0 + (warp & 3) * 32);
+              ptx::bulk_commit();
+            }
+          } else if (row_ok_t) {
+            uint4* dst = reinterpret_cast<uint4*>(orow + ch * 32);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 u;
+              u.x = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 0]), __uint_as_float(orr[q4 * 8 + 1]));
+              u.y = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 2]), __uint_as_float(orr[q4 * 8 + 3]));
+              u.z = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 4]), __uint_as_float(orr[q4 * 8 + 5]));
+              u.w = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 6]), __uint_as_float(orr[q4 * 8 + 7]));
+              dst[q4] = u;
+            }
+          }
+        }
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(ptx::smem_u32(&bars->o_free[t]));
+        if (grp == 0 && row == 0) TRACE(t, 6);
+        PROF_ADD(3, t_epi);
+      } else if (row_ok_t) {
+        uint4* dst = reinterpret_cast<uint4*>(orow);
+#pragma unroll
+        for (int q4 = 0; q4 < D / 16; ++q4) dst[q4] = make_uint4(0, 0, 0, 0);
+      }
+    };
+    // the S tiles arrive in the order the MMA issuers alternate: tile 0 step j, tile 1 step j, tile 0 step j+1 ..
 #ifdef HSTU_PROF
     const long long t_role = clock64();
 #endif
@@ -650,8 +739,16 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           ptx::tma_load_2d(sm_bias + t * (kTileM * kTileN * 2) + hf * (kTileM * 128), &tm_bias, bfull,
                            jt * kTileN + hf * 64, brow);
       };
-      // the S tiles arrive in the order the MMA issuers alternate: tile 0 step j, tile 1 step j, tile 0 step j+1 ..
+      // Tile 0 usually ends one K tile before tile 1: its output leaves while tile 1's last S tile is computed.
+      // (Keeping tile 1's output back until the next item's first score tile has been served was measured too:
+      // slower on every workload.)
+      const OutTile out0{it.s.q0, it.s.lq, it.r0, it.h, it.n0};
+      bool o0_stored = false;
       for (int j = 0; j < it.nmax; ++j) {
+        if (!o0_stored && j >= it.n(0)) {
+          store_o(0, out0);
+          o0_stored = true;
+        }
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j >= it.n(t)) continue;
@@ -705,79 +802,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
 #endif
         }
       }
-      // O tiles: this group's half of the columns.  A Q tile that lies wholly inside its sequence leaves through
-      // shared memory and TMA stores (128 rows x 32 columns per store, double buffered); a tile cut by the
-      // sequence end must not touch the rows after it and is written row by row.
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        const int tile_r0 = it.r0 + t * kTileM;
-        if (tile_r0 >= it.s.lq) continue;
-        const int col0 = grp * (D / 2);
-        T* orow = static_cast<T*>(p.out) + ((it.s.q0 + i_row[t]) * p.hq + it.h) * D + col0;
-        if (it.n(t) > 0) {
-          const uint32_t t_o = tmem + lane_base + (t == 0 ? kColO0 : C::kColO1) + col0;
-          PROF_T0(t_wo);
-          w.wait(ptx::smem_u32(&bars->o_full[t]), o_uses[t] & 1u);
-          PROF_ADD(2, t_wo);
-          PROF_T0(t_epi);
-          if (grp == 0 && row == 0) TRACE(t, 5);
-          ++o_uses[t];
-          ptx::tc_fence_after();
-          const bool by_tma = C::kOutBytes > 0 && tile_r0 + kTileM <= it.s.lq;
-#pragma unroll 1
-          for (int ch = 0; ch < D / 64; ++ch) {
-            uint32_t orr[32];
-            ptx::tmem_ld32(t_o + ch * 32, orr);
-            ptx::tmem_wait_ld();
-            if (by_tma) {
-              const uint32_t buf = sm_out + (grp * 2 + (out_chunks & 1u)) * C::kOutChunkBytes;
-              ++out_chunks;
-              // the store that last read this buffer (two stores ago) is done with it
-              if (row == 0) ptx::bulk_wait_read<1>();
-              ptx::named_bar_sync(1 + grp, kTileM);
-              const uint32_t dst_row = buf + row * 64;
-              const uint32_t swz = (row >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index ^ address bits [7,9)
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4) {
-                const uint32_t u0 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 0]), __uint_as_float(orr[q4 * 8 + 1]));
-                const uint32_t u1 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 2]), __uint_as_float(orr[q4 * 8 + 3]));
-                const uint32_t u2 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 4]), __uint_as_float(orr[q4 * 8 + 5]));
-                const uint32_t u3 = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 6]), __uint_as_float(orr[q4 * 8 + 7]));
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_row + ((q4 ^ swz) << 4)), "r"(u0),
-                             "r"(u1), "r"(u2), "r"(u3)
-                             : "memory");
-              }
-              ptx::fence_proxy_async();
-              ptx::named_bar_sync(1 + grp, kTileM);
-              if (row == 0) {
-                ptx::tma_store_3d(&tm_out, buf, col0 + ch * 32, it.h, static_cast<int>(it.s.q0) + tile_r0);
-                ptx::bulk_commit();
-              }
-            } else if (row_ok[t]) {
-              uint4* dst = reinterpret_cast<uint4*>(orow + ch * 32);
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4) {
-                uint4 u;
-                u.x = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 0]), __uint_as_float(orr[q4 * 8 + 1]));
-                u.y = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 2]), __uint_as_float(orr[q4 * 8 + 3]));
-                u.z = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 4]), __uint_as_float(orr[q4 * 8 + 5]));
-                u.w = Pack<T>::pack(__uint_as_float(orr[q4 * 8 + 6]), __uint_as_float(orr[q4 * 8 + 7]));
-                dst[q4] = u;
-              }
-            }
-          }
-          ptx::tc_fence_before();
-          ptx::mbar_arrive(ptx::smem_u32(&bars->o_free[t]));
-          if (grp == 0 && row == 0) TRACE(t, 6);
-          PROF_ADD(3, t_epi);
-        } else if (row_ok[t]) {
-          uint4* dst = reinterpret_cast<uint4*>(orow);
-#pragma unroll
-          for (int q4 = 0; q4 < D / 16; ++q4) dst[q4] = make_uint4(0, 0, 0, 0);
-        }
-      }
+      if (!o0_stored) store_o(0, out0);
+      store_o(1, OutTile{it.s.q0, it.s.lq, it.r0 + kTileM, it.h, it.n1});
     }
-    if (C::kOutBytes > 0 && row == 0) ptx::bulk_wait<0>();  // this thread's TMA stores have completed
+    if (C::kOutBytes > 0 && lane == 0) ptx::bulk_wait<0>();  // this thread's TMA stores have completed
     if (bias_thread) {
       // the last bias tiles this thread requested have landed (already true unless a wait gave up)
       for (int t = 0; t < 2; ++t) {
@@ -856,7 +884,7 @@ bool make_out_map(CUtensorMap* m, const KParams& p, int dtype) {
   cuuint64_t dims[3] = {static_cast<cuuint64_t>(p.dv), static_cast<cuuint64_t>(p.hq),
                         static_cast<cuuint64_t>(p.total_q > 0 ? p.total_q : 1)};
   cuuint64_t strides[2] = {static_cast<cuuint64_t>(p.dv) * 2, static_cast<cuuint64_t>(p.dv) * 2 * p.hq};
-  cuuint32_t box[3] = {32, 1, static_cast<cuuint32_t>(kTileM)};
+  cuuint32_t box[3] = {32, 1, 32};  // one warp's rows
   cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapDataType dt = dtype == HSTU_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
