@@ -35,9 +35,9 @@ METRIC = "hstu_jagged_fwd_causal_tflops"
 UNIT = "TFLOP/s"
 
 # DRAM bytes (read + write) per token of one attention-kernel launch, from the ncu capture summarised in
-# profiles/hstu_tc_kernel_cfg4.md (first 24 sequences of cfg4: 583 MB for 51 883 tokens; the traffic is q/k/v/out
+# profiles/hstu_tc_kernel_cfg4.md (first 24 sequences of cfg4: 613 MB for 51 883 tokens; the traffic is q/k/v/out
 # movement plus K/V re-reads and scales with the tokens a launch processes).
-TRAFFIC_BYTES_PER_TOKEN = {"cfg4": 582.97e6 / 51883}
+TRAFFIC_BYTES_PER_TOKEN = {"cfg4": 612.8e6 / 51883}
 
 WORKLOAD_DESC = {
     "cfg2": "cfg2: B=32 H=4 d=128 bf16, L~U[256,1024], max_seq_len=1024, causal, no rab",
