@@ -44,6 +44,7 @@ constexpr int kSchedStages = 8;                       // depth of the work-item 
 constexpr int kSchedReaders = 3 + 2 * 128;            // producer lane + two MMA lanes + every thread of both P/O groups
 
 // kBias: 0 = no attn_bias, 1 = bias read by plain loads (fallback when its rows are not 16-byte aligned),
+// 3 = no bias, but a custom mask (mask_type 3) read by plain loads through the same operand path: P *= mask,
 // 2 = bias tiles staged in shared memory by TMA.
 template <int D, int kBias = 0>
 struct Cfg {
@@ -268,7 +269,7 @@ __device__ __forceinline__ void silu_chunk(const uint32_t (&sr)[32], const uint3
 #pragma unroll
   for (int e = 0; e < 16; ++e) {
     float2 x = make_float2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1]));
-    if (kBias)
+    if (kBias == 1 || kBias == 2)
       x = __ffma2_rn(x, cin2, __fmul2_rn(Pack<T>::unpack(bv[e]), cb2));
     else
       x = __fmul2_rn(x, cin2);
@@ -283,6 +284,7 @@ __device__ __forceinline__ void silu_chunk(const uint32_t (&sr)[32], const uint3
       // tanh form on x = y/2: o = x*scale*(1 + tanh x)
       o = __ffma2_rn(r, make_float2(ptx::tanh_approx(x.x), ptx::tanh_approx(x.y)), r);
     }
+    if (kBias == 3) o = __fmul2_rn(o, Pack<T>::unpack(bv[e]));  // custom mask: its values multiply (fp32)
     if (kMasked) {  // a select, not a multiply: scores of rows past the sequence end may be Inf or NaN
       o.x = (visible & (1u << (2 * e))) ? o.x : 0.f;
       o.y = (visible & (2u << (2 * e))) ? o.y : 0.f;
@@ -324,7 +326,7 @@ __device__ __forceinline__ void p_half(uint32_t t_s, int grp, int c0, const Bias
       all_on = __all_sync(0xffffffffu, vis == 0xffffffffu);
       all_off = __all_sync(0xffffffffu, vis == 0u);
     }
-    if (kBias == 1 && !all_off) load_bias32<T>(br, j0 + ch * 32, bv);
+    if ((kBias == 1 || kBias == 3) && !all_off) load_bias32<T>(br, j0 + ch * 32, bv);
     if (kBias == 2 && !all_off) load_bias32_smem(br, 2 * grp + ch, bv);
     ptx::tmem_wait_ld_dep(sbuf[ch]);
     if (ch == 0) ptx::tmem_ld32(s_col + 32, sbuf[1]);
@@ -722,7 +724,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         i_row[t] = it.r0 + t * kTileM + row;
         row_ok[t] = i_row[t] < it.s.lq;
         rb[t] = row_bounds(it.s, row_ok[t] ? i_row[t] : it.s.lq - 1, p.mask_type, p.group);
-        bias_row[t] = kBias == 1 ? static_cast<long long>(it.b) * p.bias_bstride +
+        bias_row[t] = (kBias == 1 || kBias == 3) ? static_cast<long long>(it.b) * p.bias_bstride +
                                        (static_cast<long long>(it.h) * p.maxq + i_row[t]) * p.maxk
                                  : 0;
       }
@@ -930,7 +932,8 @@ namespace hstu {
 bool tc_supported(const KParams& p, int dtype) {
   if (dtype != HSTU_DTYPE_BF16 && dtype != HSTU_DTYPE_FP16) return false;
   if (p.dqk != p.dv || (p.dqk != 64 && p.dqk != 128)) return false;
-  if (p.mask_type != HSTU_MASK_TRIL && p.mask_type != HSTU_MASK_NONE) return false;
+  // a custom mask takes the operand slot of the bias (plain loads), so the two together run on the generic kernel
+  if (p.mask_type == HSTU_MASK_CUSTOM && (!p.mask || p.bias)) return false;
   if (p.hq > 0xffff || p.total_q > 0x7fffff00ll || p.total_k > 0x7fffff00ll) return false;
   const uintptr_t align = reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) |
                           reinterpret_cast<uintptr_t>(p.v) | reinterpret_cast<uintptr_t>(p.out);
@@ -938,7 +941,13 @@ bool tc_supported(const KParams& p, int dtype) {
 }
 
 // Returns cudaSuccess, a CUDA error, or cudaErrorNotSupported when the tensor maps could not be encoded.
-cudaError_t launch_tc(const KParams& p, int dtype, int num_sms, cudaStream_t stream) {
+cudaError_t launch_tc(const KParams& p_in, int dtype, int num_sms, cudaStream_t stream) {
+  KParams p = p_in;
+  const bool custom_mask = p.mask_type == HSTU_MASK_CUSTOM;
+  if (custom_mask) {  // the kernel reads the mask [B, Hq, maxq, maxk] through its bias operand path (mode 3)
+    p.bias = p.mask;
+    p.bias_bstride = static_cast<long long>(p.hq) * p.maxq * p.maxk;
+  }
   CUtensorMap mq, mk, mv;
   if (!make_map(&mq, p.q, p.total_q, p.hq, p.dqk, dtype) || !make_map(&mk, p.k, p.total_k, p.hk, p.dqk, dtype) ||
       !make_map(&mv, p.v, p.total_k, p.hk, p.dv, dtype))
@@ -951,14 +960,16 @@ cudaError_t launch_tc(const KParams& p, int dtype, int num_sms, cudaStream_t str
   // bias staging by TMA needs 16-byte aligned rows and batch blocks laid out back to back (or one shared block)
   int bias_mode = p.bias ? 1 : 0;
   CUtensorMap mb = mq;
-  if (p.bias && vec_ok &&
+  if (custom_mask) bias_mode = 3;
+  if (!custom_mask && p.bias && vec_ok &&
       (p.bias_bstride == 0 || p.bias_bstride == static_cast<long long>(p.hq) * p.maxq * p.maxk) &&
       make_bias_map(&mb, p, dtype))
     bias_mode = 2;
   CUtensorMap mo;
   if (!make_out_map(&mo, p, dtype)) return cudaErrorNotSupported;
 #define HSTU_TC_CASE(DD, TT)                                                                       \
-  return bias_mode == 2   ? launch_inst<DD, TT, 2>(p, mq, mk, mv, mb, mo, vec_ok, g, stream)      \
+  return bias_mode == 3   ? launch_inst<DD, TT, 3>(p, mq, mk, mv, mb, mo, vec_ok, g, stream)      \
+         : bias_mode == 2 ? launch_inst<DD, TT, 2>(p, mq, mk, mv, mb, mo, vec_ok, g, stream)      \
          : bias_mode == 1 ? launch_inst<DD, TT, 1>(p, mq, mk, mv, mb, mo, vec_ok, g, stream)      \
                           : launch_inst<DD, TT, 0>(p, mq, mk, mv, mb, mo, vec_ok, g, stream)
   if (dtype == HSTU_DTYPE_BF16) {

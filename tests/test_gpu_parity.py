@@ -263,3 +263,35 @@ def test_large_batch_beyond_the_reference_limit():
     out, status = run_cabi(args)
     assert status == 0
     assert_parity(out, args, label="B3000")
+
+
+@pytest.mark.parametrize("D,dtype", [(128, BF16), (64, BF16), (128, FP16)])
+@pytest.mark.parametrize("maxL", [130, 517])
+def test_custom_mask_runs_on_the_tensor_core_kernel(D, dtype, maxL):
+    """mask_type 3 (the mask's values multiply, hstu_dense_forward_kernel_patten_bsnd.h:388-395): 0/1 masks as in the
+    reference tests (test_hstu_jagged.py: torch.randint(0, 2, ...)) and arbitrary multipliers; with an odd
+    max_seq_len the mask rows are not 16-byte aligned (scalar loads)."""
+    args = make_case(5, 4, 2, D, D, 1, maxL, dtype, seed=maxL + D, custom_mask=True)
+    a, _ = cabi.make_args(args["q"], args["k"], args["v"], None, args["seq_offset"], mask=args["mask"], mask_type=3,
+                          max_seq_len=args["max_seq_len"])
+    assert cabi.kernel_kind(a) == 1
+    tc, st = run_cabi(args)
+    assert st == 0
+    assert_parity(tc, args, label="0/1 mask")
+    gen, _ = run_cabi(args, flags=cabi.FLAG_FORCE_GENERIC)
+    assert (tc.float() - gen.float()).abs().max() <= 2e-2 * gen.float().abs().max()
+    gen_t = torch.Generator().manual_seed(7)
+    args["mask"] = (torch.rand(args["mask"].shape, generator=gen_t) * 2 - 0.5).to(dtype)   # multipliers in [-0.5, 1.5)
+    tc, st = run_cabi(args)
+    assert st == 0
+    assert_parity(tc, args, label="multiplier mask")
+
+
+def test_custom_mask_with_bias_takes_the_generic_kernel():
+    args = make_case(3, 2, 2, 128, 128, 1, 200, BF16, seed=9, custom_mask=True, rab="batch")
+    a, _ = cabi.make_args(args["q"], args["k"], args["v"], None, args["seq_offset"], mask=args["mask"],
+                          attn_bias=args["attn_bias"], mask_type=3, max_seq_len=args["max_seq_len"])
+    assert cabi.kernel_kind(a) == 0
+    out, st = run_cabi(args)
+    assert st == 0
+    assert_parity(out, args, label="mask + bias")
