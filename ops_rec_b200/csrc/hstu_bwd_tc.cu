@@ -1,0 +1,454 @@
+// HSTU jagged backward on Blackwell tensor cores (tcgen05 + TMEM + TMA), bf16 / fp16, Dqk = Dv in {64, 128},
+// mask tril / none, the reference's order x = alpha (S + bias).  Everything else runs on hstu_bwd_generic.cu.
+//
+// One kernel template, launched twice, no atomics (bitwise reproducible):
+//
+//   dQ pass   (kDKV = false)  one CTA per (sequence, query head, 128-row q-tile).  Resident: Q tile, dO tile.
+//             Streamed over the visible K tiles j: K_j, V_j.   S = Q.K_j^T, dP = dO.V_j^T  ->  dS  ->  dQ += dS.K_j.
+//             dS (rounded to the input type) is also this tile of d_bias; the CTA writes the zeros of its d_bias
+//             rows right of the visited tiles, so d_bias needs no clearing.
+//   dK/dV pass (kDKV = true)  one CTA per (sequence, kv head, 128-key tile).  Resident: K tile, V tile.
+//             Streamed over the query heads of the group and the q-tiles i that see the keys: Q_i, dO_i.
+//             S^T = K.Q_i^T, dP^T = V.dO_i^T  ->  P^T, dS^T  ->  dV += P^T.dO_i, dK += dS^T.Q_i.
+//
+// Both passes are the same pipeline: two "T" products (SS form, both operands K-major from shared memory) into
+// TMEM, an element-wise stage by 256 threads (thread = TMEM lane = row, two groups share the columns) that writes
+// the 16-bit results in place over the fp32 ones, and accumulate products (A operand = those results in TMEM, B =
+// the streamed tile again, read N-major).  TMEM: T1, T2 (128 columns each), Acc1, Acc2 (D columns each).
+// A step's element-wise stage and the MMAs do not overlap yet (one chain per CTA); the element-wise math follows
+// hstu_backward_v1/op_kernel/vector_score.h:159-209 with P and dS rounded to the input type.
+//
+// Every mbarrier wait is bounded; a wait that gives up sets HSTU_ST_PIPE_TIMEOUT and a CTA-wide abort flag, the
+// kernel still drains its TMA loads, frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "hstu_common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace hstu {
+
+bool make_tile_map(CUtensorMap* m, const void* base, long long tokens, int heads, int dim, int dtype);
+
+namespace {
+
+constexpr int kBwdThreads = 384;
+constexpr long long kBwdWaitLimit = 2000000000ll;  // ~1 s of SM clock
+
+template <typename T> struct BPack;
+template <> struct BPack<__nv_bfloat16> {
+  static constexpr int kFormat = 1;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ float one(const void* p, long long i) {
+    return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  }
+};
+template <> struct BPack<__half> {
+  static constexpr int kFormat = 0;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ float one(const void* p, long long i) {
+    return __half2float(static_cast<const __half*>(p)[i]);
+  }
+};
+
+struct BwdBars {
+  uint64_t a_full;             // the resident pair has landed
+  uint64_t b_full[2], b_free[2];
+  uint64_t t_full;             // T1 and T2 of the current step are complete
+  uint64_t u_full;             // their 16-bit replacements are written (256 arrivals)
+  uint64_t acc_full;           // every accumulate MMA is complete
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct BwdWaiter {
+  int* abort_flag;
+  uint32_t* status;
+  __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity) const {
+    if (ptx::mbar_try_wait(bar, parity)) return;
+    if (*reinterpret_cast<volatile int*>(abort_flag)) return;
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    while (!ptx::mbar_try_wait(bar, parity)) {
+      if ((++spins & 0x3ffu) == 0) {
+        if (*reinterpret_cast<volatile int*>(abort_flag)) return;
+        if (clock64() - t0 > kBwdWaitLimit) {
+          *reinterpret_cast<volatile int*>(abort_flag) = 1;
+          atomicOr(status, static_cast<uint32_t>(HSTU_ST_PIPE_TIMEOUT));
+          return;
+        }
+      }
+    }
+  }
+};
+
+// The steps of one CTA, in the order every role walks them.  f(stream_head, stream_row0, query_head):
+//   dQ pass:    stream = K/V tiles of kv head hk, rows stream_row0 = j * 128 (keys);   query_head = h
+//   dK/dV pass: stream = Q/dO tiles of query head h, rows stream_row0 = r0 (queries);  query_head = h
+template <bool kDKV, typename F>
+__device__ __forceinline__ void for_each_step(const KParams& p, const SeqInfo& s, int tile0, int head, F&& f) {
+  if (!kDKV) {
+    const int n = kv_tiles_for_rows(s, tile0, kTileM, p.mask_type, kTileN);
+    for (int j = 0; j < n; ++j) f(head / p.gqa_ratio, j * kTileN, head);
+  } else {
+    const int ktile = tile0 / kTileN;
+    for (int hh = 0; hh < p.gqa_ratio; ++hh)
+      for (int r0 = 0; r0 < s.lq; r0 += kTileM)
+        if (kv_tiles_for_rows(s, r0, kTileM, p.mask_type, kTileN) > ktile) f(head * p.gqa_ratio + hh, r0, head * p.gqa_ratio + hh);
+  }
+}
+
+// P and dS of one element from s = q.k and dp = dO.v (vector_score.h:175-197), zero where not visible.
+template <typename T>
+__device__ __forceinline__ void score_grad(float s, float dp, float bias, float alpha, float scale, bool visible,
+                                           float& p_out, float& ds_out) {
+  const float x = (s + bias) * alpha;
+  float sg;
+  if (BPack<T>::kFormat == 0) {
+    sg = ptx::rcp_approx(1.f + ptx::ex2_approx(-1.4426950408889634f * x));
+  } else {
+    sg = fmaf(0.5f, ptx::tanh_approx(0.5f * x), 0.5f);
+  }
+  const float xs = x * sg;
+  const float pv = xs * scale;
+  const float ds = dp * (scale * alpha) * sg * (1.f + x - xs);
+  p_out = visible ? pv : 0.f;    // selects: scores of rows past a sequence end may be Inf or NaN
+  ds_out = visible ? ds : 0.f;
+}
+
+template <int D, typename T, bool kDKV>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1,
+                   const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_b1,
+                   const __grid_constant__ CUtensorMap tm_b2) {
+  constexpr int kHalves = D / 64;
+  constexpr int kHalfBytes = kTileM * 128;
+  constexpr int kTileBytes = kHalves * kHalfBytes;
+  constexpr uint32_t kColT1 = 0, kColT2 = 128, kColAcc1 = 256, kColAcc2 = 256 + D;
+  const KParams& p = bp.f;
+  const int head = blockIdx.x % (kDKV ? p.hk : p.hq);   // dQ pass: query head; dK/dV pass: kv head
+  const int b = blockIdx.x / (kDKV ? p.hk : p.hq);
+  const int tile0 = blockIdx.y * kTileM;                // first query row (dQ pass) / first key (dK/dV pass)
+  const SeqInfo s = load_seq(p, b);
+  const int len = kDKV ? s.lk : s.lq;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (!kDKV && bp.dbias) {
+    // zeros of this CTA's d_bias rows right of the visited K tiles (all columns when nothing is visited)
+    const int first = kv_tiles_for_rows(s, tile0, kTileM, p.mask_type, kTileN) * kTileN;
+    const int width = p.maxk - first;
+    T* dbias = static_cast<T*>(bp.dbias);
+    const long long brow0 = (static_cast<long long>(b) * p.hq + head) * p.maxq;
+    if (width > 0)
+      for (int idx = tid; idx < kTileM * width; idx += kBwdThreads) {
+        const int r = idx / width, c = idx - r * width;
+        if (tile0 + r < p.maxq) dbias[(brow0 + tile0 + r) * p.maxk + first + c] = T(0.f);
+      }
+  }
+  if (tile0 >= len) return;   // uniform over the CTA
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t sm_a = base;                        // A1, A2
+  const uint32_t sm_b = base + 2 * kTileBytes;       // ring: stage x {B1, B2}
+  BwdBars* bars = reinterpret_cast<BwdBars*>(base_ptr + 6 * kTileBytes);
+  const BwdWaiter w{&bars->abort_flag, p.ws_header};
+
+  if (tid == 0) {
+    ptx::prefetch_tensormap(&tm_a1);
+    ptx::prefetch_tensormap(&tm_a2);
+    ptx::prefetch_tensormap(&tm_b1);
+    ptx::prefetch_tensormap(&tm_b2);
+    ptx::mbar_init(ptx::smem_u32(&bars->a_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(ptx::smem_u32(&bars->b_full[i]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->b_free[i]), 1);
+    }
+    ptx::mbar_init(ptx::smem_u32(&bars->t_full), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->u_full), 2 * kTileM);
+    ptx::mbar_init(ptx::smem_u32(&bars->acc_full), 1);
+    bars->abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+  // token row of the resident tiles and of the streamed ones, heads of both
+  const long long a_row = (kDKV ? s.k0 : s.q0) + tile0;
+  const long long b_row0 = kDKV ? s.q0 : s.k0;
+  const int a_head = head;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint32_t afull = ptx::smem_u32(&bars->a_full);
+      ptx::mbar_expect_tx(afull, 2 * kTileBytes);
+#pragma unroll
+      for (int hf = 0; hf < kHalves; ++hf) {
+        ptx::tma_load_3d(sm_a + hf * kHalfBytes, &tm_a1, afull, hf * 64, a_head, static_cast<int>(a_row));
+        ptx::tma_load_3d(sm_a + kTileBytes + hf * kHalfBytes, &tm_a2, afull, hf * 64, a_head, static_cast<int>(a_row));
+      }
+      uint32_t cnt = 0;
+      for_each_step<kDKV>(p, s, tile0, head, [&](int sh, int srow0, int) {
+        const uint32_t stage = cnt & 1u;
+        const uint32_t full = ptx::smem_u32(&bars->b_full[stage]);
+        w.wait(ptx::smem_u32(&bars->b_free[stage]), ((cnt >> 1) & 1u) ^ 1u);
+        ptx::mbar_expect_tx(full, 2 * kTileBytes);
+        const int row = static_cast<int>(b_row0) + srow0;
+#pragma unroll
+        for (int hf = 0; hf < kHalves; ++hf) {
+          ptx::tma_load_3d(sm_b + stage * 2 * kTileBytes + hf * kHalfBytes, &tm_b1, full, hf * 64, sh, row);
+          ptx::tma_load_3d(sm_b + stage * 2 * kTileBytes + kTileBytes + hf * kHalfBytes, &tm_b2, full, hf * 64, sh, row);
+        }
+        ++cnt;
+      });
+      // drain (matters only after an abort: otherwise the consumers have waited for every load)
+      for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(ptx::smem_u32(&bars->a_full), 0); ++spin) {}
+      for (uint32_t back = 0; back < 2 && back < cnt; ++back) {
+        const uint32_t c = cnt - 1 - back;
+        const uint32_t bar = ptx::smem_u32(&bars->b_full[c & 1u]);
+        for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (c >> 1) & 1u); ++spin) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_t = ptx::umma_idesc_f16(BPack<T>::kFormat, kTileM, kTileN, 0);
+      constexpr uint32_t idesc_acc = ptx::umma_idesc_f16(BPack<T>::kFormat, kTileM, D, 1);
+      constexpr uint64_t kDescK = ptx::umma_desc_sw128_hi(16, 1024);           // K-major tiles
+      constexpr uint64_t kDescN = ptx::umma_desc_sw128_hi(kHalfBytes, 1024);   // the same tiles read N-major
+      const uint64_t a1 = kDescK | static_cast<uint64_t>(sm_a >> 4);
+      const uint64_t a2 = kDescK | static_cast<uint64_t>((sm_a + kTileBytes) >> 4);
+      // accumulate products of step c (its U1 / U2 are written): Acc1 += U1.B2, Acc2 += U2.B1
+      auto accumulate = [&](uint32_t c) {
+        w.wait(ptx::smem_u32(&bars->u_full), c & 1u);
+        ptx::tc_fence_after();
+        const uint32_t stage = c & 1u;
+        const uint64_t b1n = kDescN | static_cast<uint64_t>((sm_b + stage * 2 * kTileBytes) >> 4);
+        const uint64_t b2n = kDescN | static_cast<uint64_t>((sm_b + stage * 2 * kTileBytes + kTileBytes) >> 4);
+#pragma unroll
+        for (int ks = 0; ks < kTileN / 16; ++ks) {
+          const uint32_t ucol = (ks >> 2) * 64 + (ks & 3) * 8;
+          const uint64_t off = static_cast<uint64_t>((ks * 2048) >> 4);
+          if (kDKV) ptx::mma_ts(tmem + kColAcc1, tmem + kColT1 + ucol, b2n + off, idesc_acc, (c > 0 || ks > 0) ? 1u : 0u);
+          ptx::mma_ts(tmem + kColAcc2, tmem + kColT2 + ucol, b1n + off, idesc_acc, (c > 0 || ks > 0) ? 1u : 0u);
+        }
+        ptx::mma_commit(ptx::smem_u32(&bars->b_free[stage]));
+      };
+      uint32_t cnt = 0;
+      w.wait(ptx::smem_u32(&bars->a_full), 0);
+      for_each_step<kDKV>(p, s, tile0, head, [&](int, int, int) {
+        if (cnt > 0) accumulate(cnt - 1);   // must precede this step's T products: they overwrite U1 / U2
+        const uint32_t stage = cnt & 1u;
+        w.wait(ptx::smem_u32(&bars->b_full[stage]), (cnt >> 1) & 1u);
+        ptx::tc_fence_after();
+        const uint64_t b1 = kDescK | static_cast<uint64_t>((sm_b + stage * 2 * kTileBytes) >> 4);
+        const uint64_t b2 = kDescK | static_cast<uint64_t>((sm_b + stage * 2 * kTileBytes + kTileBytes) >> 4);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
+          ptx::mma_ss(tmem + kColT1, a1 + off, b1 + off, idesc_t, ks > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
+          ptx::mma_ss(tmem + kColT2, a2 + off, b2 + off, idesc_t, ks > 0 ? 1u : 0u);
+        }
+        ptx::mma_commit(ptx::smem_u32(&bars->t_full));
+        ++cnt;
+      });
+      if (cnt > 0) accumulate(cnt - 1);
+      ptx::mma_commit(ptx::smem_u32(&bars->acc_full));
+      w.wait(ptx::smem_u32(&bars->acc_full), 0);   // all MMAs and their barrier arrivals are done before teardown
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ element-wise groups (thread = row)
+    // Group g owns the columns [64g, 64g + 64) of T1 / T2 and the columns [g D/2, (g+1) D/2) of the accumulators.
+    // The 16-bit results replace the fp32 values inside the group's own column range (values 0..63 of a tile
+    // row at columns 0..31, values 64..127 at columns 64..95), so no group overwrites what the other still reads.
+    const int grp = (warp - 4) >> 2;
+    const int row = (tid - 128) & 127;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int mine = tile0 + row;                 // this thread's query row (dQ pass) / key (dK/dV pass)
+    const bool mine_ok = mine < len;
+    const RowBounds rb_mine = row_bounds(s, (mine_ok || kDKV) ? mine : s.lq - 1, p.mask_type, p.group);  // dQ pass
+    T* dbias = static_cast<T*>(bp.dbias);
+    const bool dbias_vec = dbias && (p.maxk % 8 == 0) && (reinterpret_cast<uintptr_t>(bp.dbias) & 15u) == 0;
+    uint32_t cnt = 0;
+    for_each_step<kDKV>(p, s, tile0, head, [&](int, int srow0, int qh) {
+      w.wait(ptx::smem_u32(&bars->t_full), cnt & 1u);
+      ptx::tc_fence_after();
+      // rows of the score tile are queries, columns keys - in the dK/dV pass the tile is held transposed
+      const int q_first = kDKV ? srow0 : tile0, k_first = kDKV ? tile0 : srow0;
+      const bool full = tile_is_full(s, q_first, kTileM, k_first, kTileN, p.mask_type, p.group) &&
+                        (!kDKV || q_first + kTileM <= s.lq);
+      const long long bias_bh = static_cast<long long>(b) * p.bias_bstride + static_cast<long long>(qh) * p.maxq * p.maxk;
+#pragma unroll 1
+      for (int ch = 0; ch < 2; ++ch) {
+        const int col = 64 * grp + 32 * ch;
+        uint32_t t1[32], t2[32];
+        ptx::tmem_ld32(tmem + lane_base + kColT1 + col, t1);
+        ptx::tmem_ld32(tmem + lane_base + kColT2 + col, t2);
+        ptx::tmem_wait_ld();
+        uint32_t u1[16], u2[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          float pv[2], ds[2];
+#pragma unroll
+          for (int hx = 0; hx < 2; ++hx) {
+            const int c = col + 2 * e + hx;
+            const int i = kDKV ? srow0 + c : mine;
+            const int j = kDKV ? mine : srow0 + c;
+            const bool inside = i < s.lq && j < s.lk;
+            bool vis = inside;
+            if (!full && inside) vis = allowed(kDKV ? row_bounds(s, i, p.mask_type, p.group) : rb_mine, j);
+            float bias = 0.f;
+            if (p.bias && inside) bias = BPack<T>::one(p.bias, bias_bh + static_cast<long long>(i) * p.maxk + j);
+            score_grad<T>(__uint_as_float(t1[2 * e + hx]), __uint_as_float(t2[2 * e + hx]), bias, p.alpha, p.scale,
+                          vis, pv[hx], ds[hx]);
+          }
+          u1[e] = BPack<T>::pack(pv[0], pv[1]);
+          u2[e] = BPack<T>::pack(ds[0], ds[1]);
+        }
+        if (kDKV) ptx::tmem_st16(tmem + lane_base + kColT1 + 64 * grp + 16 * ch, u1);
+        ptx::tmem_st16(tmem + lane_base + kColT2 + 64 * grp + 16 * ch, u2);
+        if (!kDKV && dbias && mine < p.maxq) {
+          // this tile of d_bias = dS (already rounded), zeros where nothing is visible
+          const int j0 = srow0 + col;
+          T* dst = dbias + static_cast<long long>(b) * p.bias_bstride +
+                   (static_cast<long long>(qh) * p.maxq + mine) * p.maxk + j0;
+          if (dbias_vec && j0 + 32 <= p.maxk) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+              reinterpret_cast<uint4*>(dst)[q4] = make_uint4(u2[4 * q4], u2[4 * q4 + 1], u2[4 * q4 + 2], u2[4 * q4 + 3]);
+          } else {
+            unsigned short* d16 = reinterpret_cast<unsigned short*>(dst);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              if (j0 + 2 * e < p.maxk) d16[2 * e] = static_cast<unsigned short>(u2[e] & 0xffffu);
+              if (j0 + 2 * e + 1 < p.maxk) d16[2 * e + 1] = static_cast<unsigned short>(u2[e] >> 16);
+            }
+          }
+        }
+      }
+      ptx::tmem_wait_st();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(ptx::smem_u32(&bars->u_full));
+      ++cnt;
+    });
+    // accumulators -> global (this group's half of the columns); rows past the sequence end are not written
+    if (cnt > 0) {
+      w.wait(ptx::smem_u32(&bars->acc_full), 0);
+      ptx::tc_fence_after();
+    }
+    const int col0 = grp * (D / 2);
+    const long long tok = (kDKV ? s.k0 : s.q0) + mine;
+    const int heads = kDKV ? p.hk : p.hq;
+    T* out2 = static_cast<T*>(kDKV ? bp.dk : bp.dq) + (tok * heads + head) * D + col0;
+    T* out1 = kDKV ? static_cast<T*>(bp.dv) + (tok * heads + head) * D + col0 : nullptr;
+#pragma unroll 1
+    for (int ch = 0; ch < D / 64; ++ch) {
+#pragma unroll 1
+      for (int which = kDKV ? 0 : 1; which < 2; ++which) {
+        uint32_t acc[32];
+        if (cnt > 0) {
+          ptx::tmem_ld32(tmem + lane_base + (which == 0 ? kColAcc1 : kColAcc2) + col0 + ch * 32, acc);
+          ptx::tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) acc[e] = 0u;   // nothing visible: zero gradient
+        }
+        if (mine_ok) {
+          uint4* dst = reinterpret_cast<uint4*>((which == 0 ? out1 : out2) + ch * 32);
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 u;
+            u.x = BPack<T>::pack(__uint_as_float(acc[q4 * 8 + 0]), __uint_as_float(acc[q4 * 8 + 1]));
+            u.y = BPack<T>::pack(__uint_as_float(acc[q4 * 8 + 2]), __uint_as_float(acc[q4 * 8 + 3]));
+            u.z = BPack<T>::pack(__uint_as_float(acc[q4 * 8 + 4]), __uint_as_float(acc[q4 * 8 + 5]));
+            u.w = BPack<T>::pack(__uint_as_float(acc[q4 * 8 + 6]), __uint_as_float(acc[q4 * 8 + 7]));
+            dst[q4] = u;
+          }
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, 512);
+  }
+}
+
+template <int D, typename T>
+cudaError_t launch_bwd_tc_t(const BwdParams& bp, int dtype, cudaStream_t stream) {
+  const KParams& p = bp.f;
+  CUtensorMap mq, mg, mk, mv;
+  if (!make_tile_map(&mq, p.q, p.total_q, p.hq, p.dqk, dtype) ||
+      !make_tile_map(&mg, bp.dout, p.total_q, p.hq, p.dv, dtype) ||
+      !make_tile_map(&mk, p.k, p.total_k, p.hk, p.dqk, dtype) || !make_tile_map(&mv, p.v, p.total_k, p.hk, p.dv, dtype))
+    return cudaErrorNotSupported;
+  constexpr int smem = 1024 + 6 * (D / 64) * kTileM * 128 + 256;
+  static_assert(sizeof(BwdBars) <= 256, "barrier block too large");
+  auto kq = hstu_bwd_tc_kernel<D, T, false>;
+  auto kkv = hstu_bwd_tc_kernel<D, T, true>;
+  cudaError_t e = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  if (p.total_q > 0) {
+    dim3 grid(static_cast<unsigned>(p.batch) * p.hq, (p.maxq + kTileM - 1) / kTileM, 1);
+    kq<<<grid, kBwdThreads, smem, stream>>>(bp, mq, mg, mk, mv);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  if (p.total_k > 0) {
+    dim3 grid(static_cast<unsigned>(p.batch) * p.hk, (p.maxk + kTileN - 1) / kTileN, 1);
+    kkv<<<grid, kBwdThreads, smem, stream>>>(bp, mk, mv, mq, mg);
+    e = cudaGetLastError();
+  }
+  return e;
+}
+
+}  // namespace
+
+bool bwd_tc_supported(const BwdParams& bp, int dtype) {
+  const KParams& p = bp.f;
+  if (dtype != HSTU_DTYPE_BF16 && dtype != HSTU_DTYPE_FP16) return false;
+  if (p.dqk != p.dv || (p.dqk != 64 && p.dqk != 128)) return false;
+  if (p.mask_type != HSTU_MASK_TRIL && p.mask_type != HSTU_MASK_NONE) return false;
+  if (p.flags & (HSTU_FLAG_ALPHA_BEFORE_BIAS | HSTU_FLAG_FORCE_GENERIC)) return false;
+  if (p.total_q > 0x7fffff00ll || p.total_k > 0x7fffff00ll) return false;
+  const uintptr_t align = reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) |
+                          reinterpret_cast<uintptr_t>(p.v) | reinterpret_cast<uintptr_t>(bp.dout) |
+                          reinterpret_cast<uintptr_t>(bp.dq) | reinterpret_cast<uintptr_t>(bp.dk) |
+                          reinterpret_cast<uintptr_t>(bp.dv);
+  return (align & 15u) == 0;
+}
+
+// Returns cudaSuccess, a CUDA error, or cudaErrorNotSupported when the tensor maps could not be encoded.
+cudaError_t launch_bwd_tc(const BwdParams& bp, int dtype, cudaStream_t stream) {
+  const KParams& p = bp.f;
+  if (dtype == HSTU_DTYPE_BF16)
+    return p.dqk == 128 ? launch_bwd_tc_t<128, __nv_bfloat16>(bp, dtype, stream)
+                        : launch_bwd_tc_t<64, __nv_bfloat16>(bp, dtype, stream);
+  return p.dqk == 128 ? launch_bwd_tc_t<128, __half>(bp, dtype, stream) : launch_bwd_tc_t<64, __half>(bp, dtype, stream);
+}
+
+}  // namespace hstu

@@ -929,6 +929,11 @@ extern "C" __attribute__((visibility("default"))) int hstu_debug_read_prof(unsig
 namespace hstu {
 #endif
 
+// The q / k / v tile map for other translation units (the backward kernels).
+bool make_tile_map(CUtensorMap* m, const void* base, long long tokens, int heads, int dim, int dtype) {
+  return make_map(m, base, tokens, heads, dim, dtype);
+}
+
 bool tc_supported(const KParams& p, int dtype) {
   if (dtype != HSTU_DTYPE_BF16 && dtype != HSTU_DTYPE_FP16) return false;
   if (p.dqk != p.dv || (p.dqk != 64 && p.dqk != 128)) return false;

@@ -221,3 +221,54 @@ def test_inconsistent_inputs_set_the_status_word():
     bad = dict(args, max_seq_len=5, max_seq_len_k=5, attn_bias=None)
     _, status = run_bwd(grad, bad)
     assert status & cabi.ST_LEN_GT_MAX
+
+
+# ------------------------------------------------------------------------------------ tensor-core kernels
+# bf16 / fp16 with Dqk = Dv in {64, 128} and mask tril / none run on hstu_bwd_tc.cu; FLAG_FORCE_GENERIC keeps the
+# CUDA-core kernels, which gives an independent GPU result to compare with.
+
+@pytest.mark.parametrize("D,dtype", [(128, BF16), (64, BF16), (128, FP16), (64, FP16)])
+@pytest.mark.parametrize("case", [
+    dict(B=3, Hq=2, Hk=2, maxL=130, bias=False),
+    dict(B=4, Hq=4, Hk=2, maxL=700, bias=True),
+    dict(B=3, Hq=4, Hk=1, maxL=400, bias=True, ctx=5, tgt=40, g=3),
+    dict(B=3, Hq=2, Hk=2, maxL=300, bias=False, ctx=0, tgt=64, g=1),
+    dict(B=3, Hq=2, Hk=1, maxL=520, bias=True, delta=True),
+    dict(B=2, Hq=2, Hk=2, maxL=260, bias=True, mask_type=2),
+])
+def test_tensor_core_backward(D, dtype, case):
+    c = dict(case)
+    B, Hq, Hk, maxL, bias = c.pop("B"), c.pop("Hq"), c.pop("Hk"), c.pop("maxL"), c.pop("bias")
+    grad, args = make_bwd_case(B, Hq, Hk, D, D, maxL, dtype, seed=maxL + D, bias=bias, alpha=1.0 / D, **c)
+    got, status = run_bwd(grad, args)
+    assert status == 0
+    assert_bwd_parity(got, grad, args, label=f"tc D{D} {dtype} {case}")
+    gen, status = run_bwd(grad, args, flags=cabi.FLAG_FORCE_GENERIC)
+    assert status == 0
+    for a, b_, name in zip(got, gen, NAMES):
+        if a is None:
+            assert b_ is None
+            continue
+        scale = max(b_.float().abs().max().item(), 1e-30)
+        assert (a.float() - b_.float()).abs().max().item() <= 3e-2 * scale, name
+
+
+def test_tensor_core_backward_long_sequences_and_bias_padding():
+    # several 128-row tiles per sequence, odd max_seq_len (unaligned d_bias rows), d_bias fully written
+    grad, args = make_bwd_case(2, 2, 2, 128, 128, 1031, BF16, seed=77, bias=True, alpha=1.0 / 128)
+    (dq, dk, dv, dbias), status = run_bwd(grad, args)
+    assert status == 0
+    assert_bwd_parity([dq, dk, dv, dbias], grad, args, label="long")
+    off = args["seq_offset"].tolist()
+    for b in range(2):
+        L = off[b + 1] - off[b]
+        assert (dbias[b, :, L:, :] == 0).all() and (dbias[b, :, :, L:] == 0).all()
+        assert (torch.triu(dbias[b, 0, :L, :L].float(), diagonal=1) == 0).all()
+
+
+def test_tensor_core_backward_bitwise_reproducible():
+    grad, args = make_bwd_case(4, 4, 2, 64, 64, 500, BF16, seed=31, alpha=1.0 / 64)
+    a, _ = run_bwd(grad, args)
+    b, _ = run_bwd(grad, args)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
