@@ -105,6 +105,14 @@ __device__ __forceinline__ void for_each_step(const KParams& p, const SeqInfo& s
   }
 }
 
+// Bit e set <=> column j0 + e is visible to the row described by rb (columns j0 .. j0 + 31).
+__device__ __forceinline__ uint32_t low_bits(int n) {  // n lowest bits set, n clamped to [0, 32]
+  return n <= 0 ? 0u : (n >= 32 ? 0xffffffffu : ((1u << n) - 1u));
+}
+__device__ __forceinline__ uint32_t visible_bits(const RowBounds& rb, int j0) {
+  return low_bits(rb.lim1 - j0) | (low_bits(rb.hi2 + 1 - j0) & ~low_bits(rb.lo2 - j0));
+}
+
 // P and dS of one element from s = q.k and dp = dO.v (vector_score.h:175-197), zero where not visible.
 template <typename T>
 __device__ __forceinline__ void score_grad(float s, float dp, float bias, float alpha, float scale, bool visible,
@@ -289,6 +297,9 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
     const RowBounds rb_mine = row_bounds(s, (mine_ok || kDKV) ? mine : s.lq - 1, p.mask_type, p.group);  // dQ pass
     T* dbias = static_cast<T*>(bp.dbias);
     const bool dbias_vec = dbias && (p.maxk % 8 == 0) && (reinterpret_cast<uintptr_t>(bp.dbias) & 15u) == 0;
+    // the dK/dV pass holds the score tile transposed (thread = key): a closed form for the visible queries of a key
+    // exists for the plain causal / no-mask cases; context rows and grouped targets take the per-element rule
+    const bool simple_mask = p.mask_type != HSTU_MASK_TRIL || (s.ctx == 0 && (s.tgt == 0 || p.group == 0));
     uint32_t cnt = 0;
     for_each_step<kDKV>(p, s, tile0, head, [&](int, int srow0, int qh) {
       w.wait(ptx::smem_u32(&bars->t_full), cnt & 1u);
@@ -305,25 +316,55 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         ptx::tmem_ld32(tmem + lane_base + kColT1 + col, t1);
         ptx::tmem_ld32(tmem + lane_base + kColT2 + col, t2);
         ptx::tmem_wait_ld();
-        uint32_t u1[16], u2[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float pv[2], ds[2];
-#pragma unroll
-          for (int hx = 0; hx < 2; ++hx) {
-            const int c = col + 2 * e + hx;
-            const int i = kDKV ? srow0 + c : mine;
-            const int j = kDKV ? mine : srow0 + c;
-            const bool inside = i < s.lq && j < s.lk;
-            bool vis = inside;
-            if (!full && inside) vis = allowed(kDKV ? row_bounds(s, i, p.mask_type, p.group) : rb_mine, j);
-            float bias = 0.f;
-            if (p.bias && inside) bias = BPack<T>::one(p.bias, bias_bh + static_cast<long long>(i) * p.maxk + j);
-            score_grad<T>(__uint_as_float(t1[2 * e + hx]), __uint_as_float(t2[2 * e + hx]), bias, p.alpha, p.scale,
-                          vis, pv[hx], ds[hx]);
+        // bit e of `bits`: element (this row, column col + e) of the tile is visible
+        uint32_t bits;
+        if (!kDKV) {
+          bits = !mine_ok ? 0u : (full ? 0xffffffffu : visible_bits(rb_mine, srow0 + col));
+        } else if (full) {
+          bits = 0xffffffffu;
+        } else if (mine >= s.lk) {
+          bits = 0u;
+        } else if (simple_mask) {
+          // causal: query i sees key j iff i + (lk - lq) >= j; no mask: every query of the sequence sees it
+          const int i0 = srow0 + col;
+          bits = low_bits(s.lq - i0);
+          if (p.mask_type == HSTU_MASK_TRIL) bits &= ~low_bits(mine - (s.lk - s.lq) - i0);
+        } else {
+          bits = 0u;   // context rows / grouped targets: evaluate the reference rule element by element
+          for (int e = 0; e < 32; ++e) {
+            const int i = srow0 + col + e;
+            if (i < s.lq && allowed(row_bounds(s, i, p.mask_type, p.group), mine)) bits |= 1u << e;
           }
-          u1[e] = BPack<T>::pack(pv[0], pv[1]);
-          u2[e] = BPack<T>::pack(ds[0], ds[1]);
+        }
+        uint32_t u1[16], u2[16];
+        if (p.bias) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            float pv[2], ds[2];
+#pragma unroll
+            for (int hx = 0; hx < 2; ++hx) {
+              const int c = col + 2 * e + hx;
+              const bool vis = (bits >> (2 * e + hx)) & 1u;
+              const long long at = kDKV ? static_cast<long long>(srow0 + c) * p.maxk + mine
+                                        : static_cast<long long>(mine) * p.maxk + srow0 + c;
+              const float bias = vis ? BPack<T>::one(p.bias, bias_bh + at) : 0.f;
+              score_grad<T>(__uint_as_float(t1[2 * e + hx]), __uint_as_float(t2[2 * e + hx]), bias, p.alpha, p.scale,
+                            vis, pv[hx], ds[hx]);
+            }
+            u1[e] = BPack<T>::pack(pv[0], pv[1]);
+            u2[e] = BPack<T>::pack(ds[0], ds[1]);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            float pv[2], ds[2];
+#pragma unroll
+            for (int hx = 0; hx < 2; ++hx)
+              score_grad<T>(__uint_as_float(t1[2 * e + hx]), __uint_as_float(t2[2 * e + hx]), 0.f, p.alpha, p.scale,
+                            (bits >> (2 * e + hx)) & 1u, pv[hx], ds[hx]);
+            u1[e] = BPack<T>::pack(pv[0], pv[1]);
+            u2[e] = BPack<T>::pack(ds[0], ds[1]);
+          }
         }
         if (kDKV) ptx::tmem_st16(tmem + lane_base + kColT1 + 64 * grp + 16 * ch, u1);
         ptx::tmem_st16(tmem + lane_base + kColT2 + 64 * grp + 16 * ch, u2);
