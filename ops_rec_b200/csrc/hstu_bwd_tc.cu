@@ -113,22 +113,38 @@ __device__ __forceinline__ uint32_t visible_bits(const RowBounds& rb, int j0) {
   return low_bits(rb.lim1 - j0) | (low_bits(rb.hi2 + 1 - j0) & ~low_bits(rb.lo2 - j0));
 }
 
-// P and dS of one element from s = q.k and dp = dO.v (vector_score.h:175-197), zero where not visible.
-template <typename T>
-__device__ __forceinline__ void score_grad(float s, float dp, float bias, float alpha, float scale, bool visible,
-                                           float& p_out, float& ds_out) {
-  const float x = (s + bias) * alpha;
-  float sg;
+// P and dS of two neighbouring elements from s = q.k and dp = dO.v (vector_score.h:175-197) on the packed f32x2
+// pipe:  x = alpha (s + bias),  sg = sigmoid(x),  P = x sg scale,  dS = dp scale alpha sg (1 + x - x sg).
+// kSelect: zero the elements whose bit in `vis` (bits 0 and 1) is clear - a select, never a multiply: scores of
+// rows past a sequence end may be Inf or NaN.
+template <typename T, bool kBiasOn, bool kSelect>
+__device__ __forceinline__ void score_grad2(float2 s, float2 dp, float2 bias, float alpha, float scale, uint32_t vis,
+                                            uint32_t& p_out, uint32_t& ds_out) {
+  const float2 al = make_float2(alpha, alpha);
+  float2 x = kBiasOn ? __fmul2_rn(__fadd2_rn(s, bias), al) : __fmul2_rn(s, al);
+  float2 sg;
   if (BPack<T>::kFormat == 0) {
-    sg = ptx::rcp_approx(1.f + ptx::ex2_approx(-1.4426950408889634f * x));
+    const float2 ny = __fmul2_rn(x, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+    const float2 d = __fadd2_rn(make_float2(ptx::ex2_approx(ny.x), ptx::ex2_approx(ny.y)), make_float2(1.f, 1.f));
+    sg = make_float2(ptx::rcp_approx(d.x), ptx::rcp_approx(d.y));
   } else {
-    sg = fmaf(0.5f, ptx::tanh_approx(0.5f * x), 0.5f);
+    const float2 hx = __fmul2_rn(x, make_float2(0.5f, 0.5f));
+    sg = __ffma2_rn(make_float2(ptx::tanh_approx(hx.x), ptx::tanh_approx(hx.y)), make_float2(0.5f, 0.5f),
+                    make_float2(0.5f, 0.5f));
   }
-  const float xs = x * sg;
-  const float pv = xs * scale;
-  const float ds = dp * (scale * alpha) * sg * (1.f + x - xs);
-  p_out = visible ? pv : 0.f;    // selects: scores of rows past a sequence end may be Inf or NaN
-  ds_out = visible ? ds : 0.f;
+  const float2 xs = __fmul2_rn(x, sg);
+  float2 pv = __fmul2_rn(xs, make_float2(scale, scale));
+  const float2 wgt = __ffma2_rn(xs, make_float2(-1.f, -1.f), __fadd2_rn(x, make_float2(1.f, 1.f)));
+  const float sa = scale * alpha;
+  float2 ds = __fmul2_rn(__fmul2_rn(__fmul2_rn(dp, make_float2(sa, sa)), sg), wgt);
+  if (kSelect) {
+    pv.x = (vis & 1u) ? pv.x : 0.f;
+    pv.y = (vis & 2u) ? pv.y : 0.f;
+    ds.x = (vis & 1u) ? ds.x : 0.f;
+    ds.y = (vis & 2u) ? ds.y : 0.f;
+  }
+  p_out = BPack<T>::pack(pv.x, pv.y);
+  ds_out = BPack<T>::pack(ds.x, ds.y);
 }
 
 template <int D, typename T, bool kDKV>
@@ -337,34 +353,43 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
           }
         }
         uint32_t u1[16], u2[16];
-        if (p.bias) {
+        // per warp: every element visible -> no selects; nothing visible -> zeros without arithmetic; else selects
+        const bool all_on = __all_sync(0xffffffffu, bits == 0xffffffffu);
+        const bool all_off = __all_sync(0xffffffffu, bits == 0u);
+        if (all_off) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) u1[e] = u2[e] = 0u;
+        } else if (p.bias) {
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
-            float pv[2], ds[2];
-#pragma unroll
-            for (int hx = 0; hx < 2; ++hx) {
-              const int c = col + 2 * e + hx;
-              const bool vis = (bits >> (2 * e + hx)) & 1u;
-              const long long at = kDKV ? static_cast<long long>(srow0 + c) * p.maxk + mine
-                                        : static_cast<long long>(mine) * p.maxk + srow0 + c;
-              const float bias = vis ? BPack<T>::one(p.bias, bias_bh + at) : 0.f;
-              score_grad<T>(__uint_as_float(t1[2 * e + hx]), __uint_as_float(t2[2 * e + hx]), bias, p.alpha, p.scale,
-                            vis, pv[hx], ds[hx]);
+            const uint32_t v2 = (bits >> (2 * e)) & 3u;
+            const int c = col + 2 * e;
+            float2 bias;
+            if (kDKV) {
+              const long long at = bias_bh + static_cast<long long>(srow0 + c) * p.maxk + mine;
+              bias.x = (v2 & 1u) ? BPack<T>::one(p.bias, at) : 0.f;
+              bias.y = (v2 & 2u) ? BPack<T>::one(p.bias, at + p.maxk) : 0.f;
+            } else {
+              const long long at = bias_bh + static_cast<long long>(mine) * p.maxk + srow0 + c;
+              bias.x = (v2 & 1u) ? BPack<T>::one(p.bias, at) : 0.f;
+              bias.y = (v2 & 2u) ? BPack<T>::one(p.bias, at + 1) : 0.f;
             }
-            u1[e] = BPack<T>::pack(pv[0], pv[1]);
-            u2[e] = BPack<T>::pack(ds[0], ds[1]);
+            score_grad2<T, true, true>(make_float2(__uint_as_float(t1[2 * e]), __uint_as_float(t1[2 * e + 1])),
+                                       make_float2(__uint_as_float(t2[2 * e]), __uint_as_float(t2[2 * e + 1])), bias,
+                                       p.alpha, p.scale, v2, u1[e], u2[e]);
           }
+        } else if (all_on) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e)
+            score_grad2<T, false, false>(make_float2(__uint_as_float(t1[2 * e]), __uint_as_float(t1[2 * e + 1])),
+                                         make_float2(__uint_as_float(t2[2 * e]), __uint_as_float(t2[2 * e + 1])),
+                                         make_float2(0.f, 0.f), p.alpha, p.scale, 3u, u1[e], u2[e]);
         } else {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            float pv[2], ds[2];
-#pragma unroll
-            for (int hx = 0; hx < 2; ++hx)
-              score_grad<T>(__uint_as_float(t1[2 * e + hx]), __uint_as_float(t2[2 * e + hx]), 0.f, p.alpha, p.scale,
-                            (bits >> (2 * e + hx)) & 1u, pv[hx], ds[hx]);
-            u1[e] = BPack<T>::pack(pv[0], pv[1]);
-            u2[e] = BPack<T>::pack(ds[0], ds[1]);
-          }
+          for (int e = 0; e < 16; ++e)
+            score_grad2<T, false, true>(make_float2(__uint_as_float(t1[2 * e]), __uint_as_float(t1[2 * e + 1])),
+                                        make_float2(__uint_as_float(t2[2 * e]), __uint_as_float(t2[2 * e + 1])),
+                                        make_float2(0.f, 0.f), p.alpha, p.scale, (bits >> (2 * e)) & 3u, u1[e], u2[e]);
         }
         if (kDKV) ptx::tmem_st16(tmem + lane_base + kColT1 + 64 * grp + 16 * ch, u1);
         ptx::tmem_st16(tmem + lane_base + kColT2 + 64 * grp + 16 * ch, u2);
