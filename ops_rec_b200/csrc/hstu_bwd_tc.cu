@@ -62,7 +62,7 @@ struct BwdBars {
   uint64_t a_full;             // the resident pair has landed
   uint64_t b_full[2], b_free[2];
   uint64_t t_full;             // T1 and T2 of the current step are complete
-  uint64_t u_full;             // their 16-bit replacements are written (256 arrivals)
+  uint64_t u_full[2];          // their 16-bit replacements are written: first / second 32 values of each 64 (256 arrivals)
   uint64_t acc_full;           // every accumulate MMA is complete
   uint32_t tmem_base;
   int abort_flag;
@@ -198,7 +198,8 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
       ptx::mbar_init(ptx::smem_u32(&bars->b_free[i]), 1);
     }
     ptx::mbar_init(ptx::smem_u32(&bars->t_full), 1);
-    ptx::mbar_init(ptx::smem_u32(&bars->u_full), 2 * kTileM);
+    ptx::mbar_init(ptx::smem_u32(&bars->u_full[0]), 2 * kTileM);
+    ptx::mbar_init(ptx::smem_u32(&bars->u_full[1]), 2 * kTileM);
     ptx::mbar_init(ptx::smem_u32(&bars->acc_full), 1);
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
@@ -259,19 +260,30 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
       const uint64_t a1 = kDescK | static_cast<uint64_t>(sm_a >> 4);
       const uint64_t a2 = kDescK | static_cast<uint64_t>((sm_a + kTileBytes) >> 4);
       // accumulate products of step c (its U1 / U2 are written): Acc1 += U1.B2, Acc2 += U2.B1
+      // The element-wise groups hand their results over in two parts (values 0..31 and 64..95 of a tile row, then
+      // the rest), so the first half of these MMAs runs while the second part is still being computed.
       auto accumulate = [&](uint32_t c) {
-        w.wait(ptx::smem_u32(&bars->u_full), c & 1u);
-        ptx::tc_fence_after();
         const uint32_t stage = c & 1u;
         const uint64_t b1n = kDescN | static_cast<uint64_t>((sm_b + stage * 2 * kTileBytes) >> 4);
         const uint64_t b2n = kDescN | static_cast<uint64_t>((sm_b + stage * 2 * kTileBytes + kTileBytes) >> 4);
-#pragma unroll
-        for (int ks = 0; ks < kTileN / 16; ++ks) {
+        auto part = [&](int ks, uint32_t acc) {
           const uint32_t ucol = (ks >> 2) * 64 + (ks & 3) * 8;
           const uint64_t off = static_cast<uint64_t>((ks * 2048) >> 4);
-          if (kDKV) ptx::mma_ts(tmem + kColAcc1, tmem + kColT1 + ucol, b2n + off, idesc_acc, (c > 0 || ks > 0) ? 1u : 0u);
-          ptx::mma_ts(tmem + kColAcc2, tmem + kColT2 + ucol, b1n + off, idesc_acc, (c > 0 || ks > 0) ? 1u : 0u);
-        }
+          if (kDKV) ptx::mma_ts(tmem + kColAcc1, tmem + kColT1 + ucol, b2n + off, idesc_acc, acc);
+          ptx::mma_ts(tmem + kColAcc2, tmem + kColT2 + ucol, b1n + off, idesc_acc, acc);
+        };
+        w.wait(ptx::smem_u32(&bars->u_full[0]), c & 1u);
+        ptx::tc_fence_after();
+        part(0, c > 0 ? 1u : 0u);
+        part(1, 1u);
+        part(4, 1u);
+        part(5, 1u);
+        w.wait(ptx::smem_u32(&bars->u_full[1]), c & 1u);
+        ptx::tc_fence_after();
+        part(2, 1u);
+        part(3, 1u);
+        part(6, 1u);
+        part(7, 1u);
         ptx::mma_commit(ptx::smem_u32(&bars->b_free[stage]));
       };
       uint32_t cnt = 0;
@@ -393,6 +405,9 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         }
         if (kDKV) ptx::tmem_st16(tmem + lane_base + kColT1 + 64 * grp + 16 * ch, u1);
         ptx::tmem_st16(tmem + lane_base + kColT2 + 64 * grp + 16 * ch, u2);
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(ptx::smem_u32(&bars->u_full[ch]));
         if (!kDKV && dbias && mine < p.maxq) {
           // this tile of d_bias = dS (already rounded), zeros where nothing is visible
           const int j0 = srow0 + col;
@@ -412,9 +427,6 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
           }
         }
       }
-      ptx::tmem_wait_st();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(ptx::smem_u32(&bars->u_full));
       ++cnt;
     });
     // accumulators -> global (this group's half of the columns); rows past the sequence end are not written
