@@ -225,7 +225,7 @@ def run_backward(args, ops_rec, W, full, mine, kw, dev, rank, world, local_rank,
             "config": {"workload": WORKLOAD_DESC[args.workload], "op": "hstu_jagged_backward"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops_burst"], "traffic": None,
-                         "kernel": "hstu_bwd_dq_kernel + hstu_bwd_dkv_kernel (fp32 CUDA cores)"},
+                         "kernel": "hstu_bwd_tc_kernel (dQ pass + dK/dV pass)"},
             "gpu_launches": 3 * args.steps, "clocks": clocks.summary()}), flush=True)
     if world > 1:
         dist.barrier()
