@@ -19,7 +19,7 @@ bool tc_supported(const KParams& p, int dtype);
 cudaError_t launch_tc(const KParams& p, int dtype, int num_sms, cudaStream_t stream);
 cudaError_t launch_bwd_generic(const BwdParams& bp, int dtype, cudaStream_t stream);
 bool bwd_tc_supported(const BwdParams& bp, int dtype);
-cudaError_t launch_bwd_tc(const BwdParams& bp, int dtype, cudaStream_t stream);
+cudaError_t launch_bwd_tc(const BwdParams& bp, int dtype, int num_sms, cudaStream_t stream);
 }  // namespace hstu
 
 namespace {
@@ -266,7 +266,7 @@ int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t wor
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "pre-pass launch: %s", cudaGetErrorString(e));
   if (f->total_q == 0 && f->total_k == 0 && !bp.dbias) return HSTU_OK;
   if (hstu::bwd_tc_supported(bp, f->dtype)) {
-    e = hstu::launch_bwd_tc(bp, f->dtype, stream);
+    e = hstu::launch_bwd_tc(bp, f->dtype, dev.sms, stream);
     if (e == cudaErrorNotSupported) return fail(HSTU_E_CUDA, "cuTensorMapEncodeTiled failed or is unavailable");
   } else {
     e = hstu::launch_bwd_generic(bp, f->dtype, stream);

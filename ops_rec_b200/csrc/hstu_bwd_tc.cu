@@ -1,13 +1,14 @@
 // HSTU jagged backward on Blackwell tensor cores (tcgen05 + TMEM + TMA), bf16 / fp16, Dqk = Dv in {64, 128},
 // mask tril / none, the reference's order x = alpha (S + bias).  Everything else runs on hstu_bwd_generic.cu.
 //
-// One kernel template, launched twice, no atomics (bitwise reproducible):
+// One kernel template, launched twice with one persistent CTA per SM (tiles are handed out by a counter in the
+// workspace), no atomics on the data (bitwise reproducible):
 //
-//   dQ pass   (kDKV = false)  one CTA per (sequence, query head, 128-row q-tile).  Resident: Q tile, dO tile.
+//   dQ pass   (kDKV = false)  one tile of work per (sequence, query head, 128-row q-tile).  Resident: Q tile, dO tile.
 //             Streamed over the visible K tiles j: K_j, V_j.   S = Q.K_j^T, dP = dO.V_j^T  ->  dS  ->  dQ += dS.K_j.
 //             dS (rounded to the input type) is also this tile of d_bias; the CTA writes the zeros of its d_bias
 //             rows right of the visited tiles, so d_bias needs no clearing.
-//   dK/dV pass (kDKV = true)  one CTA per (sequence, kv head, 128-key tile).  Resident: K tile, V tile.
+//   dK/dV pass (kDKV = true)  one tile of work per (sequence, kv head, 128-key tile).  Resident: K tile, V tile.
 //             Streamed over the query heads of the group and the q-tiles i that see the keys: Q_i, dO_i.
 //             S^T = K.Q_i^T, dP^T = V.dO_i^T  ->  P^T, dS^T  ->  dV += P^T.dO_i, dK += dS^T.Q_i.
 //
@@ -66,6 +67,7 @@ struct BwdBars {
   uint64_t acc_full;           // every accumulate MMA is complete
   uint32_t tmem_base;
   int abort_flag;
+  int item;                    // the tile every thread of the CTA works on next (-1: none left)
 };
 
 struct BwdWaiter {
@@ -157,26 +159,7 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   constexpr int kTileBytes = kHalves * kHalfBytes;
   constexpr uint32_t kColT1 = 0, kColT2 = 128, kColAcc1 = 256, kColAcc2 = 256 + D;
   const KParams& p = bp.f;
-  const int head = blockIdx.x % (kDKV ? p.hk : p.hq);   // dQ pass: query head; dK/dV pass: kv head
-  const int b = blockIdx.x / (kDKV ? p.hk : p.hq);
-  const int tile0 = blockIdx.y * kTileM;                // first query row (dQ pass) / first key (dK/dV pass)
-  const SeqInfo s = load_seq(p, b);
-  const int len = kDKV ? s.lk : s.lq;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-
-  if (!kDKV && bp.dbias) {
-    // zeros of this CTA's d_bias rows right of the visited K tiles (all columns when nothing is visited)
-    const int first = kv_tiles_for_rows(s, tile0, kTileM, p.mask_type, kTileN) * kTileN;
-    const int width = p.maxk - first;
-    T* dbias = static_cast<T*>(bp.dbias);
-    const long long brow0 = (static_cast<long long>(b) * p.hq + head) * p.maxq;
-    if (width > 0)
-      for (int idx = tid; idx < kTileM * width; idx += kBwdThreads) {
-        const int r = idx / width, c = idx - r * width;
-        if (tile0 + r < p.maxq) dbias[(brow0 + tile0 + r) * p.maxk + first + c] = T(0.f);
-      }
-  }
-  if (tile0 >= len) return;   // uniform over the CTA
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -213,6 +196,62 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   ptx::tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
+  // Persistent CTAs take tiles from a counter in the workspace (zeroed by the pre-pass).  Tile order: all tiles of a
+  // (sequence, head) are neighbours, so the CTAs that run together stream the same K/V (Q/dO) rows out of L2, and
+  // the tiles with the most steps of a sequence come first (dQ pass: its last q-tile; dK/dV pass: its first keys).
+  const int heads = kDKV ? p.hk : p.hq;
+  const int ntiles = ((kDKV ? p.maxk : p.maxq) + kTileM - 1) / kTileM;
+  const unsigned total = static_cast<unsigned>(p.batch) * heads * ntiles;
+  uint32_t* counter = p.ws_header + (kDKV ? 3 : 2);
+  uint32_t cnt = 0;          // steps so far (every role counts them alike): barrier phases run on across tiles
+  uint32_t tiles_done = 0;   // tiles so far: phase of a_full / acc_full
+  for (;;) {
+  if (tid == 0) {
+    int found = -1;
+    if (!*reinterpret_cast<volatile int*>(&bars->abort_flag)) {
+      for (;;) {
+        const unsigned idx = atomicAdd(counter, 1u);
+        if (idx >= total) break;
+        const int bh = idx / ntiles, tpos = idx - bh * ntiles;
+        const int t0 = (kDKV ? tpos : ntiles - 1 - tpos) * kTileM;
+        const SeqInfo cs = load_seq(p, bh / heads);
+        // (a q-tile past the sequence end still has its d_bias rows to clear)
+        if (t0 < (kDKV ? cs.lk : cs.lq) || (!kDKV && bp.dbias && t0 < p.maxq)) {
+          found = static_cast<int>(idx);
+          break;
+        }
+      }
+    }
+    bars->item = found;
+  }
+  __syncthreads();
+  const int item = *reinterpret_cast<volatile int*>(&bars->item);
+  if (item < 0) break;
+  const int bh = item / ntiles, tpos = item - bh * ntiles;
+  const int b = bh / heads;
+  const int head = bh - b * heads;                       // dQ pass: query head; dK/dV pass: kv head
+  const int tile0 = (kDKV ? tpos : ntiles - 1 - tpos) * kTileM;   // first query row (dQ) / first key (dK/dV)
+  const SeqInfo s = load_seq(p, b);
+  const int len = kDKV ? s.lk : s.lq;
+  const uint32_t first = cnt;
+
+  if (!kDKV && bp.dbias) {
+    // zeros of this tile's d_bias rows right of the visited K tiles (all columns when nothing is visited)
+    const int first_col = kv_tiles_for_rows(s, tile0, kTileM, p.mask_type, kTileN) * kTileN;
+    const int width = p.maxk - first_col;
+    T* dbias = static_cast<T*>(bp.dbias);
+    const long long brow0 = (static_cast<long long>(b) * p.hq + head) * p.maxq;
+    if (width > 0)
+      for (int idx = tid; idx < kTileM * width; idx += kBwdThreads) {
+        const int r = idx / width, c = idx - r * width;
+        if (tile0 + r < p.maxq) dbias[(brow0 + tile0 + r) * p.maxk + first_col + c] = T(0.f);
+      }
+  }
+  if (tile0 >= len) {   // uniform over the CTA
+    __syncthreads();
+    continue;
+  }
+
   // token row of the resident tiles and of the streamed ones, heads of both
   const long long a_row = (kDKV ? s.k0 : s.q0) + tile0;
   const long long b_row0 = kDKV ? s.q0 : s.k0;
@@ -228,7 +267,6 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         ptx::tma_load_3d(sm_a + hf * kHalfBytes, &tm_a1, afull, hf * 64, a_head, static_cast<int>(a_row));
         ptx::tma_load_3d(sm_a + kTileBytes + hf * kHalfBytes, &tm_a2, afull, hf * 64, a_head, static_cast<int>(a_row));
       }
-      uint32_t cnt = 0;
       for_each_step<kDKV>(p, s, tile0, head, [&](int sh, int srow0, int) {
         const uint32_t stage = cnt & 1u;
         const uint32_t full = ptx::smem_u32(&bars->b_full[stage]);
@@ -242,13 +280,6 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         }
         ++cnt;
       });
-      // drain (matters only after an abort: otherwise the consumers have waited for every load)
-      for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(ptx::smem_u32(&bars->a_full), 0); ++spin) {}
-      for (uint32_t back = 0; back < 2 && back < cnt; ++back) {
-        const uint32_t c = cnt - 1 - back;
-        const uint32_t bar = ptx::smem_u32(&bars->b_full[c & 1u]);
-        for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (c >> 1) & 1u); ++spin) {}
-      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -274,7 +305,7 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         };
         w.wait(ptx::smem_u32(&bars->u_full[0]), c & 1u);
         ptx::tc_fence_after();
-        part(0, c > 0 ? 1u : 0u);
+        part(0, c > first ? 1u : 0u);
         part(1, 1u);
         part(4, 1u);
         part(5, 1u);
@@ -286,10 +317,9 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         part(7, 1u);
         ptx::mma_commit(ptx::smem_u32(&bars->b_free[stage]));
       };
-      uint32_t cnt = 0;
-      w.wait(ptx::smem_u32(&bars->a_full), 0);
+      w.wait(ptx::smem_u32(&bars->a_full), tiles_done & 1u);
       for_each_step<kDKV>(p, s, tile0, head, [&](int, int, int) {
-        if (cnt > 0) accumulate(cnt - 1);   // must precede this step's T products: they overwrite U1 / U2
+        if (cnt > first) accumulate(cnt - 1);   // must precede this step's T products: they overwrite U1 / U2
         const uint32_t stage = cnt & 1u;
         w.wait(ptx::smem_u32(&bars->b_full[stage]), (cnt >> 1) & 1u);
         ptx::tc_fence_after();
@@ -308,9 +338,9 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         ptx::mma_commit(ptx::smem_u32(&bars->t_full));
         ++cnt;
       });
-      if (cnt > 0) accumulate(cnt - 1);
+      if (cnt > first) accumulate(cnt - 1);
       ptx::mma_commit(ptx::smem_u32(&bars->acc_full));
-      w.wait(ptx::smem_u32(&bars->acc_full), 0);   // all MMAs and their barrier arrivals are done before teardown
+      w.wait(ptx::smem_u32(&bars->acc_full), tiles_done & 1u);   // all MMAs and their barrier arrivals are done before teardown
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ element-wise groups (thread = row)
@@ -328,7 +358,6 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
     // the dK/dV pass holds the score tile transposed (thread = key): a closed form for the visible queries of a key
     // exists for the plain causal / no-mask cases; context rows and grouped targets take the per-element rule
     const bool simple_mask = p.mask_type != HSTU_MASK_TRIL || (s.ctx == 0 && (s.tgt == 0 || p.group == 0));
-    uint32_t cnt = 0;
     for_each_step<kDKV>(p, s, tile0, head, [&](int, int srow0, int qh) {
       w.wait(ptx::smem_u32(&bars->t_full), cnt & 1u);
       ptx::tc_fence_after();
@@ -430,13 +459,12 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
       ++cnt;
     });
     // accumulators -> global (this group's half of the columns); rows past the sequence end are not written
-    if (cnt > 0) {
-      w.wait(ptx::smem_u32(&bars->acc_full), 0);
+    if (cnt > first) {
+      w.wait(ptx::smem_u32(&bars->acc_full), tiles_done & 1u);
       ptx::tc_fence_after();
     }
     const int col0 = grp * (D / 2);
     const long long tok = (kDKV ? s.k0 : s.q0) + mine;
-    const int heads = kDKV ? p.hk : p.hq;
     T* out2 = static_cast<T*>(kDKV ? bp.dk : bp.dq) + (tok * heads + head) * D + col0;
     T* out1 = kDKV ? static_cast<T*>(bp.dv) + (tok * heads + head) * D + col0 : nullptr;
 #pragma unroll 1
@@ -444,7 +472,7 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
 #pragma unroll 1
       for (int which = kDKV ? 0 : 1; which < 2; ++which) {
         uint32_t acc[32];
-        if (cnt > 0) {
+        if (cnt > first) {
           ptx::tmem_ld32(tmem + lane_base + (which == 0 ? kColAcc1 : kColAcc2) + col0 + ch * 32, acc);
           ptx::tmem_wait_ld();
         } else {
@@ -467,6 +495,22 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
     }
   }
 
+  // everything of this tile is complete (MMAs, TMEM reads, loads) before the next one reuses the buffers
+  ++tiles_done;
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  }  // tiles
+
+  if (warp == 0 && lane == 0 && tiles_done > 0) {
+    // drain (matters only after an abort: otherwise the consumers have waited for every load)
+    for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(ptx::smem_u32(&bars->a_full), (tiles_done - 1) & 1u); ++spin) {}
+    for (uint32_t back = 0; back < 2 && back < cnt; ++back) {
+      const uint32_t c = cnt - 1 - back;
+      const uint32_t bar = ptx::smem_u32(&bars->b_full[c & 1u]);
+      for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (c >> 1) & 1u); ++spin) {}
+    }
+  }
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 2) {
@@ -476,7 +520,7 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
 }
 
 template <int D, typename T>
-cudaError_t launch_bwd_tc_t(const BwdParams& bp, int dtype, cudaStream_t stream) {
+cudaError_t launch_bwd_tc_t(const BwdParams& bp, int dtype, int num_sms, cudaStream_t stream) {
   const KParams& p = bp.f;
   CUtensorMap mq, mg, mk, mv;
   if (!make_tile_map(&mq, p.q, p.total_q, p.hq, p.dqk, dtype) ||
@@ -491,14 +535,14 @@ cudaError_t launch_bwd_tc_t(const BwdParams& bp, int dtype, cudaStream_t stream)
   if (e == cudaSuccess) e = cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   if (p.total_q > 0) {
-    dim3 grid(static_cast<unsigned>(p.batch) * p.hq, (p.maxq + kTileM - 1) / kTileM, 1);
-    kq<<<grid, kBwdThreads, smem, stream>>>(bp, mq, mg, mk, mv);
+    const long long tiles = static_cast<long long>(p.batch) * p.hq * ((p.maxq + kTileM - 1) / kTileM);
+    kq<<<static_cast<unsigned>(tiles < num_sms ? tiles : num_sms), kBwdThreads, smem, stream>>>(bp, mq, mg, mk, mv);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
   if (p.total_k > 0) {
-    dim3 grid(static_cast<unsigned>(p.batch) * p.hk, (p.maxk + kTileN - 1) / kTileN, 1);
-    kkv<<<grid, kBwdThreads, smem, stream>>>(bp, mk, mv, mq, mg);
+    const long long tiles = static_cast<long long>(p.batch) * p.hk * ((p.maxk + kTileN - 1) / kTileN);
+    kkv<<<static_cast<unsigned>(tiles < num_sms ? tiles : num_sms), kBwdThreads, smem, stream>>>(bp, mk, mv, mq, mg);
     e = cudaGetLastError();
   }
   return e;
@@ -521,12 +565,12 @@ bool bwd_tc_supported(const BwdParams& bp, int dtype) {
 }
 
 // Returns cudaSuccess, a CUDA error, or cudaErrorNotSupported when the tensor maps could not be encoded.
-cudaError_t launch_bwd_tc(const BwdParams& bp, int dtype, cudaStream_t stream) {
+cudaError_t launch_bwd_tc(const BwdParams& bp, int dtype, int num_sms, cudaStream_t stream) {
   const KParams& p = bp.f;
   if (dtype == HSTU_DTYPE_BF16)
-    return p.dqk == 128 ? launch_bwd_tc_t<128, __nv_bfloat16>(bp, dtype, stream)
-                        : launch_bwd_tc_t<64, __nv_bfloat16>(bp, dtype, stream);
-  return p.dqk == 128 ? launch_bwd_tc_t<128, __half>(bp, dtype, stream) : launch_bwd_tc_t<64, __half>(bp, dtype, stream);
+    return p.dqk == 128 ? launch_bwd_tc_t<128, __nv_bfloat16>(bp, dtype, num_sms, stream)
+                        : launch_bwd_tc_t<64, __nv_bfloat16>(bp, dtype, num_sms, stream);
+  return p.dqk == 128 ? launch_bwd_tc_t<128, __half>(bp, dtype, num_sms, stream) : launch_bwd_tc_t<64, __half>(bp, dtype, num_sms, stream);
 }
 
 }  // namespace hstu

@@ -23,7 +23,8 @@ constexpr int kTileN = 128;
 // Workspace layout (all offsets in bytes from the 256-byte aligned base).
 //   [0]   uint32 status bits (HSTU_ST_*)
 //   [4]   uint32 number of work items
-//   [8]   uint32 dynamic work counter (reserved)
+//   [8]   uint32 work counter (forward kernel; backward dQ pass)
+//   [12]  uint32 work counter (backward dK/dV pass)
 //   [256] uint32 items[2 * capacity]   {sequence, head << 16 | q_pair}
 constexpr uint64_t kWsHeaderBytes = 256;
 

@@ -51,7 +51,8 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
   __syncthreads();
   if (tid == 0) {
     p.ws_header[0] = s_status;
-    p.ws_header[2] = 0;
+    p.ws_header[2] = 0;   // work counters (forward; backward dQ pass)
+    p.ws_header[3] = 0;   // (backward dK/dV pass)
     unsigned run = 0;
     for (int key = kMaxPairs; key >= 1; --key) {
       s_start[key] = run;
