@@ -91,3 +91,52 @@ def test_cfg5_sampled_sequences_shared_bias_and_targets():
     _check_sample(w, kw, out, picks, heads=[0, 3])
     out2, _ = _run(kw)
     assert torch.equal(out, out2)
+
+
+# ---------------------------------------------------------------------------------------------------- backward
+def _bwd(kw, grad, **extra):
+    ctx = None if kw["num_target"] is None else torch.zeros_like(kw["num_target"])
+    res, status = cabi.hstu_jagged_backward(
+        grad, kw["q"], kw["k"], kw["v"], None, kw["attn_bias"], 0, kw["max_seq_len"], kw["max_seq_len"], 0.0,
+        kw["seq_offset"], kw["seq_offset"], ctx, kw["num_target"], kw["target_group_size"], kw["alpha"], **extra,
+        return_status=True)
+    torch.cuda.synchronize()
+    return res, status
+
+
+@pytest.mark.parametrize("name", ["cfg2", "cfg3"])
+def test_backward_whole_batch(name):
+    """The tensor-core backward at the workload's full size (more tiles than SMs: every persistent CTA walks several)
+    against the CPU oracle, and against the CUDA-core kernels as an independent GPU result."""
+    from tests.test_gpu_backward import assert_bwd_parity
+    w = W.make_workload(name)
+    kw = W.materialize(w, "cuda")
+    grad = (torch.randn(kw["q"].shape, generator=torch.Generator().manual_seed(5)) * 0.1).to(kw["q"].dtype).cuda()
+    got, status = _bwd(kw, grad)
+    assert status == 0
+    gen, status = _bwd(kw, grad, flags=cabi.FLAG_FORCE_GENERIC)
+    assert status == 0
+    for a, b_ in zip(got, gen):
+        if a is None:
+            assert b_ is None
+            continue
+        scale = b_.float().abs().max().item()
+        assert (a.float() - b_.float()).abs().max().item() <= 3e-2 * scale
+    args = _cpu(kw)
+    args["num_context"] = None if kw["num_target"] is None else torch.zeros_like(args["num_target"])
+    assert_bwd_parity([g.cpu() if g is not None else None for g in got], grad.cpu(), args, label=name)
+
+
+def test_backward_cfg4_properties():
+    """cfg4 is too large for the oracle: linearity of every gradient in dO, bitwise reproducibility, status word."""
+    w = W.make_workload("cfg4").subset(np.arange(64))
+    kw = W.materialize(w, "cuda")
+    g1 = (torch.randn(kw["q"].shape, generator=torch.Generator().manual_seed(6)) * 0.1).to(kw["q"].dtype).cuda()
+    a, status = _bwd(kw, g1)
+    assert status == 0
+    b_, _ = _bwd(kw, g1)
+    for x, y in zip(a[:3], b_[:3]):
+        assert torch.equal(x, y) and torch.isfinite(x.float()).all()
+    c, _ = _bwd(kw, g1 * 2)           # exact in bf16: a power of two
+    for x, y in zip(a[:3], c[:3]):
+        torch.testing.assert_close(2 * x.float(), y.float(), rtol=2e-2, atol=1e-2 * y.float().abs().max().item())
