@@ -182,6 +182,45 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_ln_mul(args, local_rank):
+    """--op ln_mul: (LayerNorm(x) * gamma + beta) * u on fp32 [A, 1024], A = 262 144 rows (x, u, out: 1 GiB each, far
+    beyond L2).  HBM-bound: algorithmic bytes = 12 per element; peak = the measured copy bandwidth."""
+    import statistics
+    import torch
+    import ops_rec_b200 as ops_rec
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    a, r = 262144, 1024
+    gen = torch.Generator(device=dev).manual_seed(1)
+    x = torch.randn(a, r, device=dev, generator=gen)
+    u = torch.randn(a, r, device=dev, generator=gen)
+    gamma, beta = torch.randn(r, device=dev, generator=gen), torch.randn(r, device=dev, generator=gen)
+    op = ops_rec.ascendc.activation.ln_mul
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        op(x, u, gamma, beta)
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    with ClockSampler(local_rank) as clocks:
+        for i in range(args.steps):
+            starts[i].record()
+            op(x, u, gamma, beta)
+            ends[i].record()
+        torch.cuda.synchronize()
+    ms = statistics.mean(s.elapsed_time(e) for s, e in zip(starts, ends))
+    nbytes = 12.0 * a * r + 8.0 * r
+    peaks = load_peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "ln_mul_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": f"ln_mul fp32 [{a}, {r}]", "l2": "3 GiB per step: no flush"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
+                     "traffic": None, "kernel": "ln_mul_rows_kernel<32, true>", "algorithmic_bytes_per_launch": nbytes},
+        "gpu_launches": args.steps, "clocks": clocks.summary()}), flush=True)
+
+
 def run_backward(args, ops_rec, W, full, mine, kw, dev, rank, world, local_rank, warmup, barrier):
     """--op backward: hstu_jagged_backward on the same workload, inputs resident in HBM.  FLOPs: the five products
     of the backward (S, dP, dV, dK, dQ) = 2.5 x the forward's two; the kernels recompute S and dP in both passes,
@@ -239,8 +278,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="cfg4", choices=sorted(WORKLOAD_DESC))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--op", default="forward", choices=["forward", "backward"],
-                    help="backward: time hstu_jagged_backward (device-resident only) instead of the forward")
+    ap.add_argument("--op", default="forward", choices=["forward", "backward", "ln_mul"],
+                    help="backward: time hstu_jagged_backward (device-resident only) instead of the forward; "
+                         "ln_mul: time ops_rec::ln_mul on [tokens/2, 1024] fp32 (HBM roofline)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunks", type=int, default=8,
                     help="the end-to-end run sends the batch through in this many chunks of whole sequences")
@@ -255,6 +295,10 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.op == "ln_mul":
+        if rank == 0:
+            run_ln_mul(args, local_rank)
         return
 
     import numpy as np

@@ -167,6 +167,14 @@ typedef struct HstuJaggedBwdArgs {
 HSTU_API int hstu_jagged_bwd_get_workspace_size(const HstuJaggedBwdArgs* args, uint64_t* workspace_bytes);
 HSTU_API int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------------------------------------------------------------ ln_mul
+ * The step that consumes the attention output in an HSTU layer: out = (LayerNorm(x) * gamma + beta) * u over the
+ * rows of fp32 [rows, cols] matrices, eps = 1e-5 (fixed by the reference's host code, ln_mul/op_host/ln_mul.cpp:73).
+ * Replaces the aclnnLnMul call of ascendc/activation/ln_mul/torch_extension/ln_mul_plugin.cpp:51.  x, u, out:
+ * contiguous [rows, cols]; gamma, beta: [cols]; all fp32 device pointers.  Asynchronous on `stream`; no workspace. */
+HSTU_API int ops_rec_ln_mul_f32(const void* x, const void* u, const void* gamma, const void* beta, void* out,
+                                int64_t rows, int64_t cols, void* stream);
+
 /* Optional: wait for `stream` and fetch the device status word of the last launch that used `workspace`
  * (0 = inputs were consistent).  The reference reads out of bounds on such inputs without noticing. */
 HSTU_API int hstu_jagged_fwd_status(const void* workspace, void* stream, uint32_t* status);

@@ -55,6 +55,7 @@ def install_as_ops_rec():
     sys.modules.setdefault("ops_rec", sys.modules[__name__])
     sys.modules.setdefault("ops_rec.ascendc", ascendc)
     sys.modules.setdefault("ops_rec.ascendc.attention", attention)
+    sys.modules.setdefault("ops_rec.ascendc.activation", ascendc.activation)
     return sys.modules["ops_rec"]
 
 

@@ -24,7 +24,7 @@ EXPORTS = (
     "hstu_jagged_fwd_get_workspace_size", "hstu_jagged_fwd", "hstu_jagged_fwd_status",
     "hstu_jagged_fwd_kernel_kind", "hstu_plan_host", "hstu_debug_mask_host", "hstu_debug_tiles_host",
     "hstu_last_error", "hstu_b200_version", "hstu_jagged_fwd_static",
-    "hstu_jagged_bwd_get_workspace_size", "hstu_jagged_bwd",
+    "hstu_jagged_bwd_get_workspace_size", "hstu_jagged_bwd", "ops_rec_ln_mul_f32",
 )
 STATIC_SCRATCH_BYTES = 1 << 20
 E_SCRATCH_LIMIT = -6
@@ -97,6 +97,8 @@ def load():
     lib.hstu_jagged_bwd_get_workspace_size.restype = C.c_int
     lib.hstu_jagged_bwd.argtypes = [B, C.c_void_p, C.c_uint64, C.c_void_p]
     lib.hstu_jagged_bwd.restype = C.c_int
+    lib.ops_rec_ln_mul_f32.argtypes = [C.c_void_p] * 5 + [C.c_int64, C.c_int64, C.c_void_p]
+    lib.ops_rec_ln_mul_f32.restype = C.c_int
     lib.hstu_last_error.restype = C.c_char_p
     lib.hstu_b200_version.restype = C.c_int
     _lib = lib
@@ -240,6 +242,25 @@ def hstu_jagged_backward(grad, q, k, v, mask=None, attn_bias=None, mask_type=0, 
             return (dq, dk, dv, dbias), st.value
     del keep
     return dq, dk, dv, dbias
+
+
+def ln_mul(x, u, gamma, beta):
+    """(LayerNorm(x) * gamma + beta) * u through ops_rec_ln_mul_f32 on fp32 CUDA tensors (argument order of
+    ops_rec::ln_mul, ascendc/activation/ln_mul/torch_extension/ln_mul_plugin.cpp:28-55)."""
+    import torch
+    if x.dim() != 2 or u.dim() != 2:
+        raise HstuError(-2, "The x should be 2D")
+    if not x.is_cuda:
+        raise HstuError(-2, "tensors must live on a CUDA device; there is no CPU implementation")
+    if x.dtype != torch.float32:
+        raise HstuError(-2, "ln_mul supports float32 only")
+    x, u, gamma, beta = x.contiguous(), u.contiguous(), gamma.contiguous(), beta.contiguous()
+    out = torch.empty_like(x)
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    with torch.cuda.device(x.device):
+        check(load().ops_rec_ln_mul_f32(x.data_ptr(), u.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(),
+                                        x.shape[0], x.shape[1], stream))
+    return out
 
 
 def hstu_jagged_forward_static(q, k, v, out, mask=None, attn_bias=None, mask_type=0, max_seq_len=0, silu_scale=0.0,

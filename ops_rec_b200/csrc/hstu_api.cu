@@ -20,6 +20,8 @@ cudaError_t launch_tc(const KParams& p, int dtype, int num_sms, cudaStream_t str
 cudaError_t launch_bwd_generic(const BwdParams& bp, int dtype, cudaStream_t stream);
 bool bwd_tc_supported(const BwdParams& bp, int dtype);
 cudaError_t launch_bwd_tc(const BwdParams& bp, int dtype, int num_sms, cudaStream_t stream);
+cudaError_t launch_ln_mul(const float* x, const float* u, const float* gamma, const float* beta, float* out,
+                          long long rows, int cols, float eps, int num_sms, cudaStream_t stream);
 }  // namespace hstu
 
 namespace {
@@ -272,6 +274,24 @@ int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t wor
     e = hstu::launch_bwd_generic(bp, f->dtype, stream);
   }
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+  return HSTU_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ ln_mul
+int ops_rec_ln_mul_f32(const void* x, const void* u, const void* gamma, const void* beta, void* out, int64_t rows,
+                       int64_t cols, void* stream_v) {
+  g_err[0] = 0;
+  if (rows < 0 || cols < 0 || cols > 0x7fffffffll) return fail(HSTU_E_PARAM, "ln_mul: bad shape [%lld, %lld]", (long long)rows, (long long)cols);
+  if (rows > 0 && cols > 0 && (!x || !u || !gamma || !beta || !out)) return fail(HSTU_E_NULL, "ln_mul: null pointer");
+  DeviceInfo dev;
+  int rc = device_info(&dev);
+  if (rc) return rc;
+  if (dev.major != 10) return fail(HSTU_E_ARCH, "this library is built for sm_100a only; device has compute capability %d.x", dev.major);
+  const cudaError_t e = hstu::launch_ln_mul(static_cast<const float*>(x), static_cast<const float*>(u),
+                                            static_cast<const float*>(gamma), static_cast<const float*>(beta),
+                                            static_cast<float*>(out), rows, static_cast<int>(cols), 1e-5f, dev.sms,
+                                            static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(HSTU_E_CUDA, "ln_mul launch: %s", cudaGetErrorString(e));
   return HSTU_OK;
 }
 

@@ -268,6 +268,39 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> hstu_jagged_backward_
   return backward_meta_out(q, k, v, attn_bias);
 }
 
+// ln_mul (ascendc/activation/ln_mul/torch_extension/ln_mul_plugin.cpp:28-55): same checks and messages, fp32 only.
+at::Tensor ln_mul(const at::Tensor& x, const at::Tensor& u, const at::Tensor& gamma, const at::Tensor& beta) {
+  for (const auto* t : {&x, &u, &gamma, &beta}) TORCH_CHECK(t->defined() && t->numel() > 0, "ln_mul: input tensor is empty");
+  TORCH_CHECK(x.is_cuda() && u.is_cuda() && gamma.is_cuda() && beta.is_cuda() && u.device() == x.device() &&
+                  gamma.device() == x.device() && beta.device() == x.device(),
+              "ln_mul: all tensors must be on the same CUDA device");
+  TORCH_CHECK(x.dim() == 2, "The x should be 2D");
+  TORCH_CHECK(u.dim() == 2, "The u should be 2D");
+  TORCH_CHECK(gamma.dim() == 1, "The gamma should be 1D");
+  TORCH_CHECK(beta.dim() == 1, "The beta should be 1D");
+  TORCH_CHECK(x.sizes() == u.sizes(), "x and u must have identical shape");
+  TORCH_CHECK(gamma.size(0) == x.size(1) && beta.size(0) == x.size(1), "gamma and beta must have x.size(1) elements");
+  TORCH_CHECK(x.scalar_type() == at::kFloat && u.scalar_type() == at::kFloat && gamma.scalar_type() == at::kFloat &&
+                  beta.scalar_type() == at::kFloat,
+              "ln_mul supports float32 only");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto xc = x.contiguous(), uc = u.contiguous(), gc = gamma.contiguous(), bc = beta.contiguous();
+  auto y = at::empty_like(xc);
+  const int rc = ops_rec_ln_mul_f32(xc.data_ptr(), uc.data_ptr(), gc.data_ptr(), bc.data_ptr(), y.data_ptr(), xc.size(0),
+                                    xc.size(1), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "ln_mul: ", hstu_last_error());
+  return y;
+}
+
+at::Tensor ln_mul_meta(const at::Tensor& x, const at::Tensor& u, const at::Tensor& gamma, const at::Tensor& beta) {
+  TORCH_CHECK(x.dim() == 2, "x must be 2D");
+  TORCH_CHECK(u.dim() == 2, "u must be 2D");
+  TORCH_CHECK(gamma.dim() == 1, "gamma must be 1D");
+  TORCH_CHECK(beta.dim() == 1, "beta must be 1D");
+  TORCH_CHECK(x.sizes() == u.sizes(), "x and u must share the same shape");
+  return at::empty_like(x, x.options());
+}
+
 // hstu_dense: [B, S, N, D] layout, every batch row one sequence of S tokens
 // (ascendc/attention/hstu_v1/torch_extension/hstu_dense_plugin.cpp:19-40).  It is the jagged forward over equal
 // lengths: the tensors are viewed as [B*S, N, D] and the offsets 0, S, 2S, ... are generated on the device.
@@ -339,6 +372,7 @@ TORCH_LIBRARY_FRAGMENT(ops_rec, m) {
         "Tensor? attn_bias=None, int mask_type=0, int max_seq_len=0, int max_seq_len_k=0, float silu_scale=0.0, "
         "Tensor seq_offset=None, Tensor seq_offset_k=None, Tensor? num_context=None, Tensor? num_target=None, "
         "int? target_group_size=0, float? alpha=1.0) -> (Tensor, Tensor, Tensor, Tensor)");
+  m.def("ln_mul(Tensor x, Tensor u, Tensor gamma, Tensor beta) -> Tensor");
   m.def("hstu_dense(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
         "int max_seq_len=0, float silu_scale=0.0) -> Tensor");
 }
@@ -348,6 +382,7 @@ TORCH_LIBRARY_IMPL(ops_rec, CUDA, m) {
   m.impl("hstu_jagged.delta", TORCH_FN(hstu_jagged_delta));
   m.impl("hstu_jagged_backward.equal", TORCH_FN(hstu_jagged_backward_equal));
   m.impl("hstu_jagged_backward.delta", TORCH_FN(hstu_jagged_backward_delta));
+  m.impl("ln_mul", TORCH_FN(ln_mul));
   m.impl("hstu_dense", TORCH_FN(hstu_dense));
 }
 
@@ -356,5 +391,6 @@ TORCH_LIBRARY_IMPL(ops_rec, Meta, m) {
   m.impl("hstu_jagged.delta", TORCH_FN(hstu_jagged_delta_meta));
   m.impl("hstu_jagged_backward.equal", TORCH_FN(hstu_jagged_backward_equal_meta));
   m.impl("hstu_jagged_backward.delta", TORCH_FN(hstu_jagged_backward_delta_meta));
+  m.impl("ln_mul", TORCH_FN(ln_mul_meta));
   m.impl("hstu_dense", TORCH_FN(hstu_dense_meta));
 }

@@ -253,13 +253,43 @@ def main_backward(ref_root, v1c):
         print(f"{case['name']:28s} tokens_q={arrays['q'].shape[0]:5d} {os.path.getsize(path) / 1024:8.1f} KiB")
 
 
+LNMUL_SHAPES = [(1, 1), (8, 64), (33, 100), (4, 1024), (2, 2048), (3, 4100), (1, 9000)]
+
+
+def main_ln_mul(ref_root):
+    """ln_mul fixtures from the reference's numpy golden, ascendc/activation/ln_mul/test/pytest/test_ln_mul.py:37-50
+    (`get_golden`).  The test module imports the NPU package and touches torch.npu at import time; stand-ins
+    satisfy that, the golden itself is pure numpy."""
+    d = os.path.join(ref_root, "ascendc/activation/ln_mul/test/pytest")
+    sys.modules.setdefault("ops_rec", types.ModuleType("ops_rec"))
+    if not hasattr(torch, "npu"):
+        torch.npu = types.SimpleNamespace(config=types.SimpleNamespace())
+    spec = importlib.util.spec_from_file_location("ref_ln_mul_test", os.path.join(d, "test_ln_mul.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    for a, r in LNMUL_SHAPES:
+        rng = np.random.default_rng(1000 * a + r)
+        x, u = rng.standard_normal((a, r), dtype=np.float32), rng.standard_normal((a, r), dtype=np.float32)
+        gamma, beta = rng.standard_normal(r, dtype=np.float32), rng.standard_normal(r, dtype=np.float32)
+        if r > 1:
+            x[0] += 30.0   # a row with a large mean: the two-pass variance matters
+        y = mod.get_golden(x, u, gamma, beta)
+        path = os.path.join(HERE, f"lnmul_{a}x{r}.npz")
+        np.savez_compressed(path, x=x, u=u, gamma=gamma, beta=beta, y=y)
+        print(f"lnmul_{a}x{r:<6d} {os.path.getsize(path) / 1024:8.1f} KiB")
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) > 2 and sys.argv[2] == "ln_mul":   # only the ln_mul fixtures
+        main_ln_mul(ref_root)
+        return
     v1c, v2b = _load_reference(ref_root)
     if len(sys.argv) > 2 and sys.argv[2] == "backward":   # only the backward fixtures
         main_backward(ref_root, v1c)
         return
     main_backward(ref_root, v1c)
+    main_ln_mul(ref_root)
     for case in CASES:
         arrays = build_case(case, v1c, v2b)
         path = os.path.join(HERE, case["name"] + ".npz")

@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def _declared_functions():
     text = open(os.path.join(ROOT, "include", "hstu_b200.h")).read()
-    return sorted(set(re.findall(r"HSTU_API\s+[\w\s\*]+?\b(hstu_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"HSTU_API\s+[\w\s\*]+?\b((?:hstu|ops_rec)_\w+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol():
