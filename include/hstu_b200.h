@@ -175,6 +175,32 @@ HSTU_API int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uin
 HSTU_API int ops_rec_ln_mul_f32(const void* x, const void* u, const void* gamma, const void* beta, void* out,
                                 int64_t rows, int64_t cols, void* stream);
 
+/* ---------------------------------------------------------------------------------------------- in_linear_silu
+ * The step that produces the attention's inputs in an HSTU layer (forward): mixed = x . weight^T + bias;
+ * linear_output = mixed (rounded to the input type); (user, value, query, key) = split(silu(linear_output)) along
+ * the last dimension.  Replaces the aclnnInLinearSilu call of
+ * ascendc/activation/in_linear_silu/torch_extension/in_linear_silu_plugin.cpp:91-93; shape rules of :36-66
+ * (k in [16, 8192] and n in [64, 32768] multiples of 16, n a multiple of 4 k, four split sizes in [16, 8192] multiples
+ * of 16 that add up to n).  x [m, k], weight [n, k]: bf16 or fp16, contiguous, 16-byte aligned; bias [n] fp32 or null;
+ * outputs in the input type, contiguous, 16-byte aligned.  Asynchronous on `stream`; no workspace. */
+typedef struct OpsRecInLinearSiluArgs {
+  uint32_t struct_bytes;  /* sizeof(OpsRecInLinearSiluArgs) */
+  int32_t dtype;          /* HSTU_DTYPE_BF16 or HSTU_DTYPE_FP16 */
+  const void* x;
+  const void* weight;
+  const void* bias;
+  void* user;             /* [m, split[0]] */
+  void* value;            /* [m, split[1]] */
+  void* query;            /* [m, split[2]] */
+  void* key;              /* [m, split[3]] */
+  void* linear_output;    /* [m, n] */
+  int64_t m;
+  int32_t n;
+  int32_t k;
+  int32_t split[4];
+} OpsRecInLinearSiluArgs;
+HSTU_API int ops_rec_in_linear_silu_fwd(const OpsRecInLinearSiluArgs* args, void* stream);
+
 /* Optional: wait for `stream` and fetch the device status word of the last launch that used `workspace`
  * (0 = inputs were consistent).  The reference reads out of bounds on such inputs without noticing. */
 HSTU_API int hstu_jagged_fwd_status(const void* workspace, void* stream, uint32_t* status);

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-_OPS = ("ln_mul",)
+_OPS = ("ln_mul", "distance_in_linear_silu")
 
 
 def _available():

@@ -24,7 +24,7 @@ EXPORTS = (
     "hstu_jagged_fwd_get_workspace_size", "hstu_jagged_fwd", "hstu_jagged_fwd_status",
     "hstu_jagged_fwd_kernel_kind", "hstu_plan_host", "hstu_debug_mask_host", "hstu_debug_tiles_host",
     "hstu_last_error", "hstu_b200_version", "hstu_jagged_fwd_static",
-    "hstu_jagged_bwd_get_workspace_size", "hstu_jagged_bwd", "ops_rec_ln_mul_f32",
+    "hstu_jagged_bwd_get_workspace_size", "hstu_jagged_bwd", "ops_rec_ln_mul_f32", "ops_rec_in_linear_silu_fwd",
 )
 STATIC_SCRATCH_BYTES = 1 << 20
 E_SCRATCH_LIMIT = -6
@@ -50,6 +50,14 @@ class HstuJaggedBwdArgs(C.Structure):
         ("struct_bytes", C.c_uint32), ("reserved", C.c_uint32), ("fwd", HstuJaggedArgs),
         ("grad_out", C.c_void_p), ("grad_q", C.c_void_p), ("grad_k", C.c_void_p), ("grad_v", C.c_void_p),
         ("grad_bias", C.c_void_p),
+    ]
+
+
+class OpsRecInLinearSiluArgs(C.Structure):
+    _fields_ = [
+        ("struct_bytes", C.c_uint32), ("dtype", C.c_int32), ("x", C.c_void_p), ("weight", C.c_void_p),
+        ("bias", C.c_void_p), ("user", C.c_void_p), ("value", C.c_void_p), ("query", C.c_void_p), ("key", C.c_void_p),
+        ("linear_output", C.c_void_p), ("m", C.c_int64), ("n", C.c_int32), ("k", C.c_int32), ("split", C.c_int32 * 4),
     ]
 
 
@@ -99,6 +107,8 @@ def load():
     lib.hstu_jagged_bwd.restype = C.c_int
     lib.ops_rec_ln_mul_f32.argtypes = [C.c_void_p] * 5 + [C.c_int64, C.c_int64, C.c_void_p]
     lib.ops_rec_ln_mul_f32.restype = C.c_int
+    lib.ops_rec_in_linear_silu_fwd.argtypes = [C.POINTER(OpsRecInLinearSiluArgs), C.c_void_p]
+    lib.ops_rec_in_linear_silu_fwd.restype = C.c_int
     lib.hstu_last_error.restype = C.c_char_p
     lib.hstu_b200_version.restype = C.c_int
     _lib = lib
@@ -242,6 +252,40 @@ def hstu_jagged_backward(grad, q, k, v, mask=None, attn_bias=None, mask_type=0, 
             return (dq, dk, dv, dbias), st.value
     del keep
     return dq, dk, dv, dbias
+
+
+def in_linear_silu(x, weight, bias, split):
+    """(user, value, query, key, linear_output) through ops_rec_in_linear_silu_fwd on CUDA tensors (argument order of
+    ops_rec::distance_in_linear_silu, in_linear_silu/torch_extension/in_linear_silu_plugin.cpp:70-98)."""
+    import torch
+    if x.dim() != 2 or weight.dim() != 2:
+        raise HstuError(-2, "x and weight must be 2D")
+    if not x.is_cuda:
+        raise HstuError(-2, "tensors must live on a CUDA device; there is no CPU implementation")
+    x, weight = x.contiguous(), weight.contiguous()
+    bias = bias.float().contiguous() if bias is not None else None
+    a = OpsRecInLinearSiluArgs()
+    a.struct_bytes = C.sizeof(OpsRecInLinearSiluArgs)
+    a.dtype = _dtype_code(x.dtype)
+    m, k, n = x.shape[0], x.shape[1], weight.shape[0]
+    if weight.shape[1] != k:
+        raise HstuError(-2, "weight dim[1] must equal to x dim[1].")
+    split = [int(v) for v in split]
+    if len(split) != 4:
+        raise HstuError(-2, "splitList must have 4 elements.")
+    outs = [torch.empty(m, w, dtype=x.dtype, device=x.device) for w in split]
+    lin = torch.empty(m, n, dtype=x.dtype, device=x.device)
+    a.x, a.weight = x.data_ptr(), weight.data_ptr()
+    a.bias = bias.data_ptr() if bias is not None else None
+    a.user, a.value, a.query, a.key = (o.data_ptr() for o in outs)
+    a.linear_output = lin.data_ptr()
+    a.m, a.n, a.k = m, n, k
+    for i in range(4):
+        a.split[i] = split[i]
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    with torch.cuda.device(x.device):
+        check(load().ops_rec_in_linear_silu_fwd(C.byref(a), stream))
+    return (*outs, lin)
 
 
 def ln_mul(x, u, gamma, beta):

@@ -22,6 +22,18 @@ bool bwd_tc_supported(const BwdParams& bp, int dtype);
 cudaError_t launch_bwd_tc(const BwdParams& bp, int dtype, int num_sms, cudaStream_t stream);
 cudaError_t launch_ln_mul(const float* x, const float* u, const float* gamma, const float* beta, float* out,
                           long long rows, int cols, float eps, int num_sms, cudaStream_t stream);
+struct LinSiluParams {
+  const float* bias;
+  void* out[4];
+  void* linear;
+  int width[4];
+  int start[5];
+  long long m;
+  int n, k;
+  uint32_t* status;
+};
+cudaError_t launch_in_linear_silu(const LinSiluParams& p, const void* x, const void* weight, int dtype,
+                                  cudaStream_t stream);
 }  // namespace hstu
 
 namespace {
@@ -274,6 +286,61 @@ int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t wor
     e = hstu::launch_bwd_generic(bp, f->dtype, stream);
   }
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+  return HSTU_OK;
+}
+
+// ---------------------------------------------------------------------------------------- in_linear_silu
+int ops_rec_in_linear_silu_fwd(const OpsRecInLinearSiluArgs* a, void* stream_v) {
+  g_err[0] = 0;
+  if (!a) return fail(HSTU_E_NULL, "args is null");
+  if (a->struct_bytes != sizeof(OpsRecInLinearSiluArgs))
+    return fail(HSTU_E_PARAM, "struct_bytes is %u, this library expects %zu", a->struct_bytes, sizeof(OpsRecInLinearSiluArgs));
+  if (a->dtype != HSTU_DTYPE_BF16 && a->dtype != HSTU_DTYPE_FP16)
+    return fail(HSTU_E_PARAM, "in_linear_silu: x and weight must be bf16 or fp16");
+  long long total = 0;
+  for (int i = 0; i < 4; ++i) {
+    if (a->split[i] < 16 || a->split[i] > 8192 || a->split[i] % 16 != 0)
+      return fail(HSTU_E_PARAM, "uvqk dim must in range[16, 8192] and multiples of 16.");
+    total += a->split[i];
+  }
+  if (a->k < 16 || a->k > 8192 || a->k % 16 != 0)
+    return fail(HSTU_E_PARAM, "x dim[1] must in range[16, 8192] and multiples of 16.");
+  if (a->n < 64 || a->n > 32768 || a->n % 16 != 0)
+    return fail(HSTU_E_PARAM, "weight dim[0] must in range[64, 32768] and multiples of 16.");
+  if (total != a->n) return fail(HSTU_E_PARAM, "weight_dim[0] must equal to sum(splitList).");
+  if (a->n % (4 * a->k) != 0) return fail(HSTU_E_PARAM, "weight dim[0] must be a multiple of 4 x dim[1]");
+  if (a->m < 0 || a->m > 0x7fffff00ll) return fail(HSTU_E_PARAM, "in_linear_silu: bad row count");
+  if (a->m == 0) return HSTU_OK;
+  if (!a->x || !a->weight || !a->user || !a->value || !a->query || !a->key || !a->linear_output)
+    return fail(HSTU_E_NULL, "in_linear_silu: null pointer");
+  const uintptr_t align = reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->weight) |
+                          reinterpret_cast<uintptr_t>(a->bias) | reinterpret_cast<uintptr_t>(a->user) |
+                          reinterpret_cast<uintptr_t>(a->value) | reinterpret_cast<uintptr_t>(a->query) |
+                          reinterpret_cast<uintptr_t>(a->key) | reinterpret_cast<uintptr_t>(a->linear_output);
+  if (align & 15u) return fail(HSTU_E_PARAM, "in_linear_silu: every tensor must be 16-byte aligned");
+  DeviceInfo dev;
+  int rc = device_info(&dev);
+  if (rc) return rc;
+  if (dev.major != 10) return fail(HSTU_E_ARCH, "this library is built for sm_100a only; device has compute capability %d.x", dev.major);
+  hstu::LinSiluParams p;
+  memset(&p, 0, sizeof(p));
+  p.bias = static_cast<const float*>(a->bias);
+  p.out[0] = a->user, p.out[1] = a->value, p.out[2] = a->query, p.out[3] = a->key;
+  p.linear = a->linear_output;
+  int at = 0;
+  for (int i = 0; i < 4; ++i) {
+    p.width[i] = a->split[i];
+    p.start[i] = at;
+    at += a->split[i];
+  }
+  p.start[4] = at;
+  p.m = a->m;
+  p.n = a->n;
+  p.k = a->k;
+  p.status = nullptr;
+  const cudaError_t e = hstu::launch_in_linear_silu(p, a->x, a->weight, a->dtype, static_cast<cudaStream_t>(stream_v));
+  if (e == cudaErrorNotSupported) return fail(HSTU_E_CUDA, "cuTensorMapEncodeTiled failed or is unavailable");
+  if (e != cudaSuccess) return fail(HSTU_E_CUDA, "in_linear_silu launch: %s", cudaGetErrorString(e));
   return HSTU_OK;
 }
 

@@ -929,6 +929,22 @@ extern "C" __attribute__((visibility("default"))) int hstu_debug_read_prof(unsig
 namespace hstu {
 #endif
 
+// 2-D view (cols, rows) of a contiguous 16-bit [rows, cols] matrix; box = 64 x 128, 128-byte swizzle (a K-major
+// operand tile of 64 K values).  Reads past either edge give zeros.
+bool make_matrix_map(CUtensorMap* m, const void* base, long long rows, long long cols, int dtype) {
+  auto fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows > 0 ? rows : 1)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kTileM)};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = dtype == HSTU_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // The q / k / v tile map for other translation units (the backward kernels).
 bool make_tile_map(CUtensorMap* m, const void* base, long long tokens, int heads, int dim, int dtype) {
   return make_map(m, base, tokens, heads, dim, dtype);

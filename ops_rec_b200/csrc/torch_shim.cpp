@@ -301,6 +301,65 @@ at::Tensor ln_mul_meta(const at::Tensor& x, const at::Tensor& u, const at::Tenso
   return at::empty_like(x, x.options());
 }
 
+// distance_in_linear_silu (in_linear_silu/torch_extension/in_linear_silu_plugin.cpp:36-98): forward only.
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> in_linear_silu_fwd(
+    const at::Tensor& x, const at::Tensor& weight, const at::Tensor& bias, at::IntArrayRef split) {
+  TORCH_CHECK(x.defined() && x.numel() > 0, "x is empty");
+  TORCH_CHECK(weight.defined() && weight.numel() > 0, "weight is empty");
+  TORCH_CHECK(x.dim() == 2, "x must be 2D");
+  TORCH_CHECK(weight.dim() == 2, "weight must be 2D");
+  TORCH_CHECK(split.size() == 4, "splitList must have 4 elements.");
+  TORCH_CHECK(x.is_cuda() && weight.is_cuda(), "in_linear_silu: tensors must be CUDA tensors");
+  TORCH_CHECK(weight.scalar_type() == x.scalar_type(), "weight must have the dtype of x");
+  TORCH_CHECK(weight.size(1) == x.size(1), "weight dim[1] must equal to x dim[1].");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto xc = x.contiguous(), wc = weight.contiguous();
+  at::Tensor bc;
+  if (bias.defined()) {
+    TORCH_CHECK(bias.dim() == 1 && bias.numel() > 0, "bias must be 1D and not empty");
+    TORCH_CHECK(bias.size(0) == weight.size(0), "bias dim[0] must equal to weight dim[0].");
+    bc = bias.to(at::kFloat).contiguous();
+  }
+  const int64_t m = xc.size(0), n = wc.size(0);
+  OpsRecInLinearSiluArgs a;
+  memset(&a, 0, sizeof(a));
+  a.struct_bytes = sizeof(a);
+  a.dtype = dtype_code(x.scalar_type());
+  TORCH_CHECK(a.dtype != HSTU_DTYPE_FP32, "in_linear_silu: x and weight must be bf16 or fp16");
+  at::Tensor outs[4];
+  for (int i = 0; i < 4; ++i) {
+    TORCH_CHECK(split[i] >= 16 && split[i] <= 8192 && split[i] % 16 == 0,
+                "uvqk dim must in range[16, 8192] and multiples of 16.");
+    outs[i] = at::empty({m, split[i]}, xc.options());
+    a.split[i] = static_cast<int32_t>(split[i]);
+  }
+  auto lin = at::empty({m, n}, xc.options());
+  a.x = xc.data_ptr();
+  a.weight = wc.data_ptr();
+  a.bias = bc.defined() ? bc.data_ptr() : nullptr;
+  a.user = outs[0].data_ptr();
+  a.value = outs[1].data_ptr();
+  a.query = outs[2].data_ptr();
+  a.key = outs[3].data_ptr();
+  a.linear_output = lin.data_ptr();
+  a.m = m;
+  TORCH_CHECK(n <= 32768 && xc.size(1) <= 8192, "weight dim[0] must in range[64, 32768] and multiples of 16.");
+  a.n = static_cast<int32_t>(n);
+  a.k = static_cast<int32_t>(xc.size(1));
+  const int rc = ops_rec_in_linear_silu_fwd(&a, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, hstu_last_error());
+  return std::make_tuple(outs[0], outs[1], outs[2], outs[3], lin);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> in_linear_silu_fwd_meta(
+    const at::Tensor& x, const at::Tensor& weight, const at::Tensor&, at::IntArrayRef split) {
+  TORCH_CHECK(split.size() == 4, "splitList must have 4 elements.");
+  const auto m = x.size(0);
+  auto o = x.options();
+  return std::make_tuple(at::empty({m, split[0]}, o), at::empty({m, split[1]}, o), at::empty({m, split[2]}, o),
+                         at::empty({m, split[3]}, o), at::empty({m, weight.size(0)}, o));
+}
+
 // hstu_dense: [B, S, N, D] layout, every batch row one sequence of S tokens
 // (ascendc/attention/hstu_v1/torch_extension/hstu_dense_plugin.cpp:19-40).  It is the jagged forward over equal
 // lengths: the tensors are viewed as [B*S, N, D] and the offsets 0, S, 2S, ... are generated on the device.
@@ -373,6 +432,8 @@ TORCH_LIBRARY_FRAGMENT(ops_rec, m) {
         "Tensor seq_offset=None, Tensor seq_offset_k=None, Tensor? num_context=None, Tensor? num_target=None, "
         "int? target_group_size=0, float? alpha=1.0) -> (Tensor, Tensor, Tensor, Tensor)");
   m.def("ln_mul(Tensor x, Tensor u, Tensor gamma, Tensor beta) -> Tensor");
+  m.def("distance_in_linear_silu(Tensor x, Tensor weight, Tensor bias, int[] attr_dict) -> "
+        "(Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("hstu_dense(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
         "int max_seq_len=0, float silu_scale=0.0) -> Tensor");
 }
@@ -383,6 +444,7 @@ TORCH_LIBRARY_IMPL(ops_rec, CUDA, m) {
   m.impl("hstu_jagged_backward.equal", TORCH_FN(hstu_jagged_backward_equal));
   m.impl("hstu_jagged_backward.delta", TORCH_FN(hstu_jagged_backward_delta));
   m.impl("ln_mul", TORCH_FN(ln_mul));
+  m.impl("distance_in_linear_silu", TORCH_FN(in_linear_silu_fwd));
   m.impl("hstu_dense", TORCH_FN(hstu_dense));
 }
 
@@ -392,5 +454,6 @@ TORCH_LIBRARY_IMPL(ops_rec, Meta, m) {
   m.impl("hstu_jagged_backward.equal", TORCH_FN(hstu_jagged_backward_equal_meta));
   m.impl("hstu_jagged_backward.delta", TORCH_FN(hstu_jagged_backward_delta_meta));
   m.impl("ln_mul", TORCH_FN(ln_mul_meta));
+  m.impl("distance_in_linear_silu", TORCH_FN(in_linear_silu_fwd_meta));
   m.impl("hstu_dense", TORCH_FN(hstu_dense_meta));
 }

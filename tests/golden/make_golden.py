@@ -279,8 +279,53 @@ def main_ln_mul(ref_root):
         print(f"lnmul_{a}x{r:<6d} {os.path.getsize(path) / 1024:8.1f} KiB")
 
 
+# m, n, k, dtype, split (None: the reference's uneven split of its diff-dim test)
+LINSILU_CASES = [(100, 64, 16, "fp16", [16, 16, 16, 16]), (37, 256, 64, "bf16", None), (130, 512, 128, "bf16", None),
+                 (64, 384, 96, "fp16", [96, 96, 96, 96])]
+
+
+def main_in_linear_silu(ref_root):
+    """in_linear_silu fixtures from the reference's torch golden, in_linear_silu_forward/test/pytest/
+    test_in_linear_silu.py:36-50 (`get_user_value_query_key_tensors_uniattn`), with its input recipe (:93-97: integer
+    x in [-100, 100], xavier-uniform weight, bias of ones).  Stand-ins satisfy the module-level NPU imports."""
+    d = os.path.join(ref_root, "ascendc/activation/in_linear_silu/in_linear_silu_forward/test/pytest")
+    sys.modules.setdefault("ops_rec", types.ModuleType("ops_rec"))
+    if not hasattr(torch, "npu"):
+        torch.npu = types.SimpleNamespace(config=types.SimpleNamespace())
+    spec = importlib.util.spec_from_file_location("ref_in_linear_silu_test", os.path.join(d, "test_in_linear_silu.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    for m, n, k, dt, split in LINSILU_CASES:
+        torch.manual_seed(m + n + k)
+        dtype = torch.float16 if dt == "fp16" else torch.bfloat16
+        q = n // 4
+        split = split or [q - 16, q - 16, q + 16, q + 16]
+        x = torch.randint(low=-100, high=101, size=(m, k)).to(dtype)
+        w = torch.nn.init.xavier_uniform_(torch.empty(n, k)).to(dtype)
+        bias = torch.ones(n, dtype=dtype)
+        # the golden runs in fp32 on the 16-bit values and is rounded like an addmm in the input dtype
+        outs = mod.get_user_value_query_key_tensors_uniattn(x, w, bias, split)
+        arrays = dict(x=x, weight=w, bias=bias.float(), split=np.array(split, dtype=np.int64))
+        for name, t in zip(("user", "value", "query", "key", "linear_output"), outs):
+            arrays[name] = t
+        path = os.path.join(HERE, f"linsilu_{m}x{n}x{k}_{dt}.npz")
+        out = {}
+        for key, val in arrays.items():
+            if isinstance(val, torch.Tensor):
+                if val.dtype == torch.bfloat16:
+                    out[key + "__bf16"] = val.contiguous().view(torch.int16).numpy().view(np.uint16)
+                    continue
+                val = val.contiguous().numpy()
+            out[key] = np.asarray(val)
+        np.savez_compressed(path, **out)
+        print(f"{os.path.basename(path):32s} {os.path.getsize(path) / 1024:8.1f} KiB")
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) > 2 and sys.argv[2] == "in_linear_silu":   # only the in_linear_silu fixtures
+        main_in_linear_silu(ref_root)
+        return
     if len(sys.argv) > 2 and sys.argv[2] == "ln_mul":   # only the ln_mul fixtures
         main_ln_mul(ref_root)
         return
@@ -290,6 +335,7 @@ def main():
         return
     main_backward(ref_root, v1c)
     main_ln_mul(ref_root)
+    main_in_linear_silu(ref_root)
     for case in CASES:
         arrays = build_case(case, v1c, v2b)
         path = os.path.join(HERE, case["name"] + ".npz")
