@@ -221,6 +221,48 @@ def run_ln_mul(args, local_rank):
         "gpu_launches": args.steps, "clocks": clocks.summary()}), flush=True)
 
 
+def run_in_linear_silu(args, local_rank):
+    """--op in_linear_silu: x [65536, 1024] . weight [4096, 1024]^T + bias -> linear_output and the four SiLU outputs
+    (bf16).  Tensor-bound: 2 m n k = 550 GFLOP per launch; it also writes 2 x m x n x 2 bytes = 1.07 GB."""
+    import statistics
+    import torch
+    import ops_rec_b200 as ops_rec
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    m, k, n = 65536, 1024, 4096
+    gen = torch.Generator(device=dev).manual_seed(1)
+    x = (torch.randn(m, k, device=dev, generator=gen)).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=dev, generator=gen) * (6.0 / (n + k)) ** 0.5).to(torch.bfloat16)
+    bias = torch.ones(n, device=dev)
+    split = [n // 4] * 4
+    op = ops_rec.ascendc.activation.distance_in_linear_silu
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        op(x, w, bias, split)
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    with ClockSampler(local_rank) as clocks:
+        for i in range(args.steps):
+            starts[i].record()
+            op(x, w, bias, split)
+            ends[i].record()
+        torch.cuda.synchronize()
+    ms = statistics.mean(s.elapsed_time(e) for s, e in zip(starts, ends))
+    flops = 2.0 * m * n * k
+    peaks = load_peaks()
+    tf = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "in_linear_silu_tflops", "value": tf, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"in_linear_silu bf16 m={m} k={k} n={n}, even split", "l2": "1.2 GB per step: no flush"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
+                     "frac": tf / peaks["tflops_burst"], "traffic": None, "kernel": "in_linear_silu_kernel",
+                     "algorithmic_flops_per_launch": flops},
+        "gpu_launches": args.steps, "clocks": clocks.summary()}), flush=True)
+
+
 def run_backward(args, ops_rec, W, full, mine, kw, dev, rank, world, local_rank, warmup, barrier):
     """--op backward: hstu_jagged_backward on the same workload, inputs resident in HBM.  FLOPs: the five products
     of the backward (S, dP, dV, dK, dQ) = 2.5 x the forward's two; the kernels recompute S and dP in both passes,
@@ -278,9 +320,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="cfg4", choices=sorted(WORKLOAD_DESC))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--op", default="forward", choices=["forward", "backward", "ln_mul"],
+    ap.add_argument("--op", default="forward", choices=["forward", "backward", "ln_mul", "in_linear_silu"],
                     help="backward: time hstu_jagged_backward (device-resident only) instead of the forward; "
-                         "ln_mul: time ops_rec::ln_mul on [tokens/2, 1024] fp32 (HBM roofline)")
+                         "ln_mul: time ops_rec::ln_mul on [262144, 1024] fp32 (HBM roofline); "
+                         "in_linear_silu: time ops_rec::distance_in_linear_silu, m=65536 k=1024 n=4096 bf16")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunks", type=int, default=8,
                     help="the end-to-end run sends the batch through in this many chunks of whole sequences")
@@ -299,6 +342,10 @@ def main():
     if args.op == "ln_mul":
         if rank == 0:
             run_ln_mul(args, local_rank)
+        return
+    if args.op == "in_linear_silu":
+        if rank == 0:
+            run_in_linear_silu(args, local_rank)
         return
 
     import numpy as np

@@ -929,14 +929,14 @@ extern "C" __attribute__((visibility("default"))) int hstu_debug_read_prof(unsig
 namespace hstu {
 #endif
 
-// 2-D view (cols, rows) of a contiguous 16-bit [rows, cols] matrix; box = 64 x 128, 128-byte swizzle (a K-major
-// operand tile of 64 K values).  Reads past either edge give zeros.
-bool make_matrix_map(CUtensorMap* m, const void* base, long long rows, long long cols, int dtype) {
+// 2-D view (cols, rows) of a contiguous 16-bit [rows, cols] matrix; box = 64 x box_rows (<= 256), 128-byte swizzle
+// (a K-major operand tile of 64 K values).  Reads past either edge give zeros.
+bool make_matrix_map(CUtensorMap* m, const void* base, long long rows, long long cols, int dtype, int box_rows) {
   auto fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows > 0 ? rows : 1)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kTileM)};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   const CUtensorMapDataType dt = dtype == HSTU_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;

@@ -6,13 +6,17 @@
 // in_linear_silu_forward/test/pytest/test_in_linear_silu.py:36-50: addmm in the input type, SiLU of that ROUNDED
 // value, split along the last dimension).  x [m, k] and weight [n, k] are bf16 / fp16, bias [n] fp32.
 //
-// One CTA per 128 x 128 tile of mixed (n-tiles fastest, so the CTAs that run together share their x rows; the weight
-// stays in L2), two CTAs per SM so that one tile's epilogue overlaps the other's main loop:
-//   warp 0   TMA producer: 64-wide K chunks of the x tile and the weight tile (both K-major) into a 3-stage ring
-//   warp 1   MMA issuer: tcgen05.mma SS, M128 N128 K16, fp32 accumulator in TMEM (128 columns)
+// One CTA per 256 x 256 tile of mixed (n-tiles fastest, so the CTAs that run together share their x rows; the weight
+// stays in L2).  The tile size is set by the L2 -> shared-memory traffic: a 128 x 128 tile needs 1 byte per 64 FLOPs
+// (measured: 531 TFLOP/s, the L2 limit), a 256 x 256 tile half of that.
+//   warp 0   TMA producer: 64-wide K chunks of the x tile and the weight tile (both K-major, 256 rows each) into a
+//            3-stage ring
+//   warp 1   MMA issuer: tcgen05.mma SS, M128 N256 K16, two fp32 accumulators in TMEM (rows 0..127 and 128..255 of
+//            the tile, 256 columns each)
 //   warp 2   TMEM allocation
-//   warps 4-7 epilogue (thread = row): TMEM -> + bias -> round -> linear_output; SiLU of the rounded value -> the output
-//            its 16-column group belongs to (the split sizes are multiples of 16)
+//   warps 4-7 / 8-11 epilogue of the first / second accumulator (thread = row): TMEM -> + bias -> round ->
+//            linear_output; SiLU of the rounded value -> the output its 16-column group belongs to (the split sizes
+//            are multiples of 16)
 // Rows / columns / K past the matrix edges are zero-filled by TMA and never stored.  Tensor bound: 2 m n k FLOPs.
 // Every mbarrier wait is bounded (then: status bit in the caller's status word, CTA-wide abort flag).
 #include <cuda.h>
@@ -24,7 +28,7 @@
 
 namespace hstu {
 
-bool make_matrix_map(CUtensorMap* m, const void* base, long long rows, long long cols, int dtype);
+bool make_matrix_map(CUtensorMap* m, const void* base, long long rows, long long cols, int dtype, int box_rows);
 
 struct LinSiluParams {
   const float* bias;       // [n] or null
@@ -39,10 +43,10 @@ struct LinSiluParams {
 
 namespace {
 
-constexpr int kLsThreads = 256;
-constexpr int kLsTile = 128;
+constexpr int kLsThreads = 384;
+constexpr int kLsTile = 256;                    // tile edge (rows of x and rows of the weight per CTA)
 constexpr int kLsStages = 3;
-constexpr int kLsChunkBytes = kLsTile * 128;   // 128 rows x 64 16-bit values
+constexpr int kLsChunkBytes = kLsTile * 128;   // 256 rows x 64 16-bit values
 constexpr long long kLsWaitLimit = 2000000000ll;
 
 struct LsBars {
@@ -88,7 +92,7 @@ __device__ __forceinline__ void ls_wait(LsBars* bars, uint32_t* status, uint32_t
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kLsThreads, 2)
+__global__ void __launch_bounds__(kLsThreads, 1)
 in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap tm_x,
                       const __grid_constant__ CUtensorMap tm_w) {
   extern __shared__ uint8_t smem_raw[];
@@ -112,8 +116,11 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
   }
+  // the bias values of this tile's columns (zeros without a bias / past the last column), read by every epilogue thread
+  float* s_bias = reinterpret_cast<float*>(base_ptr + kLsStages * 2 * kLsChunkBytes + 256);
+  if (tid < kLsTile) s_bias[tid] = (p.bias && n0 + tid < p.n) ? p.bias[n0 + tid] : 0.f;
   if (warp == 2) {
-    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), kLsTile);
+    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), 512);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before();
@@ -140,7 +147,7 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::umma_idesc_f16(LsPack<T>::kFormat, kLsTile, kLsTile, 0);
+      constexpr uint32_t idesc = ptx::umma_idesc_f16(LsPack<T>::kFormat, 128, kLsTile, 0);
       constexpr uint64_t kDescK = ptx::umma_desc_sw128_hi(16, 1024);
       for (int c = 0; c < chunks; ++c) {
         const int s = c % kLsStages;
@@ -149,22 +156,29 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
         const uint64_t a = kDescK | static_cast<uint64_t>((base + s * 2 * kLsChunkBytes) >> 4);
         const uint64_t b = kDescK | static_cast<uint64_t>((base + s * 2 * kLsChunkBytes + kLsChunkBytes) >> 4);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          ptx::mma_ss(tmem, a + static_cast<uint64_t>((ks * 32) >> 4), b + static_cast<uint64_t>((ks * 32) >> 4), idesc,
-                      (c > 0 || ks > 0) ? 1u : 0u);
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t off = static_cast<uint64_t>((ks * 32) >> 4);
+          const uint32_t acc = (c > 0 || ks > 0) ? 1u : 0u;
+          ptx::mma_ss(tmem, a + off, b + off, idesc, acc);                                          // rows 0..127
+          ptx::mma_ss(tmem + kLsTile, a + static_cast<uint64_t>((128 * 128) >> 4) + off, b + off, idesc, acc);  // 128..255
+        }
         ptx::mma_commit(ptx::smem_u32(&bars->empty[s]));
       }
       ptx::mma_commit(ptx::smem_u32(&bars->acc_full));
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ epilogue (thread = row of the tile)
-    const int row = tid - 128;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const long long gr = m0 + row;
-    const bool row_ok = gr < p.m;
-    ls_wait(bars, p.status, ptx::smem_u32(&bars->acc_full), 0);
+    // Each warp turns 32 rows x 32 columns at a time: TMEM -> registers -> (+ bias, round, SiLU) -> a private staging
+    // block in the (now idle) operand ring -> global, four lanes per row, so that every store instruction writes whole
+    // 64-byte row pieces instead of 32 scattered 16-byte ones.
+    const int half = (warp - 4) >> 2;          // which accumulator: rows [128 half, 128 half + 128) of the tile
+    const uint32_t lane_base = (static_cast<uint32_t>((warp & 3) * 32) << 16) + half * kLsTile;
+    const long long row0 = m0 + half * 128 + (warp & 3) * 32;   // first row of this warp
+    constexpr int kPitch = 80;                                   // bytes per staged row (64 + 16: fewer bank conflicts)
+    uint8_t* stage = base_ptr + (warp - 4) * (2 * 32 * kPitch);  // [lin | silu] x 32 rows
+    ls_wait(bars, p.status, ptx::smem_u32(&bars->acc_full), 0);  // all MMAs are done: the ring is free
     ptx::tc_fence_after();
-    T* lin_row = static_cast<T*>(p.linear) + gr * p.n;
+    const int sub_row = lane >> 2, part = lane & 3;              // store phase: 8 rows per instruction, 4 lanes per row
 #pragma unroll 1
     for (int ch = 0; ch < kLsTile / 32; ++ch) {
       const int c0 = n0 + ch * 32;
@@ -172,38 +186,42 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
       uint32_t acc[32];
       ptx::tmem_ld32(tmem + lane_base + ch * 32, acc);
       ptx::tmem_wait_ld();
-      if (!row_ok) continue;
+      uint32_t lin[16], act[16];
 #pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        const int cg = c0 + 16 * g;
-        if (cg >= p.n) break;   // n is a multiple of 16
-        float v[16];
+      for (int e = 0; e < 16; ++e) {
+        const float b0 = s_bias[ch * 32 + 2 * e], b1 = s_bias[ch * 32 + 2 * e + 1];
+        const float v0 = LsPack<T>::round(__uint_as_float(acc[2 * e]) + b0);
+        const float v1 = LsPack<T>::round(__uint_as_float(acc[2 * e + 1]) + b1);
+        lin[e] = LsPack<T>::pack(v0, v1);
+        // SiLU of the rounded value
+        act[e] = LsPack<T>::pack(__fdividef(v0, 1.f + __expf(-v0)), __fdividef(v1, 1.f + __expf(-v1)));
+      }
+      __syncwarp();   // the previous chunk's staged rows have been read
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          float4 bb = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (p.bias) bb = __ldg(reinterpret_cast<const float4*>(p.bias + cg) + q4);
-          v[4 * q4 + 0] = LsPack<T>::round(__uint_as_float(acc[16 * g + 4 * q4 + 0]) + bb.x);
-          v[4 * q4 + 1] = LsPack<T>::round(__uint_as_float(acc[16 * g + 4 * q4 + 1]) + bb.y);
-          v[4 * q4 + 2] = LsPack<T>::round(__uint_as_float(acc[16 * g + 4 * q4 + 2]) + bb.z);
-          v[4 * q4 + 3] = LsPack<T>::round(__uint_as_float(acc[16 * g + 4 * q4 + 3]) + bb.w);
+      for (int q4 = 0; q4 < 4; ++q4) {
+        *reinterpret_cast<uint4*>(stage + lane * kPitch + q4 * 16) =
+            make_uint4(lin[4 * q4], lin[4 * q4 + 1], lin[4 * q4 + 2], lin[4 * q4 + 3]);
+        *reinterpret_cast<uint4*>(stage + 32 * kPitch + lane * kPitch + q4 * 16) =
+            make_uint4(act[4 * q4], act[4 * q4 + 1], act[4 * q4 + 2], act[4 * q4 + 3]);
+      }
+      __syncwarp();
+      // this lane's 8 columns: c0 + 8 part .. ; their 16-column group decides the SiLU output tensor
+      const int cg = c0 + 16 * (part >> 1);
+      const bool col_ok = cg < p.n;   // n is a multiple of 16
+      const int which = (cg >= p.start[1]) + (cg >= p.start[2]) + (cg >= p.start[3]);
+      T* obase = static_cast<T*>(which == 0 ? p.out[0] : which == 1 ? p.out[1] : which == 2 ? p.out[2] : p.out[3]);
+      const int owidth = which == 0 ? p.width[0] : which == 1 ? p.width[1] : which == 2 ? p.width[2] : p.width[3];
+      const int ostart = which == 0 ? p.start[0] : which == 1 ? p.start[1] : which == 2 ? p.start[2] : p.start[3];
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int r = it * 8 + sub_row;
+        const long long gr = row0 + r;
+        if (gr < p.m && col_ok) {
+          const uint4 l = *reinterpret_cast<const uint4*>(stage + r * kPitch + part * 16);
+          const uint4 a = *reinterpret_cast<const uint4*>(stage + 32 * kPitch + r * kPitch + part * 16);
+          *reinterpret_cast<uint4*>(static_cast<T*>(p.linear) + gr * p.n + c0 + part * 8) = l;
+          *reinterpret_cast<uint4*>(obase + gr * owidth + (cg - ostart) + (part & 1) * 8) = a;
         }
-        uint4* lin = reinterpret_cast<uint4*>(lin_row + cg);
-        lin[0] = make_uint4(LsPack<T>::pack(v[0], v[1]), LsPack<T>::pack(v[2], v[3]), LsPack<T>::pack(v[4], v[5]),
-                            LsPack<T>::pack(v[6], v[7]));
-        lin[1] = make_uint4(LsPack<T>::pack(v[8], v[9]), LsPack<T>::pack(v[10], v[11]), LsPack<T>::pack(v[12], v[13]),
-                            LsPack<T>::pack(v[14], v[15]));
-        // SiLU of the rounded value, into the output this 16-column group belongs to
-        const int which = (cg >= p.start[1]) + (cg >= p.start[2]) + (cg >= p.start[3]);
-#pragma unroll
-        for (int e = 0; e < 16; ++e) v[e] = v[e] / (1.f + __expf(-v[e]));
-        void* obase = which == 0 ? p.out[0] : which == 1 ? p.out[1] : which == 2 ? p.out[2] : p.out[3];
-        const int owidth = which == 0 ? p.width[0] : which == 1 ? p.width[1] : which == 2 ? p.width[2] : p.width[3];
-        const int ostart = which == 0 ? p.start[0] : which == 1 ? p.start[1] : which == 2 ? p.start[2] : p.start[3];
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(obase) + gr * owidth + (cg - ostart));
-        dst[0] = make_uint4(LsPack<T>::pack(v[0], v[1]), LsPack<T>::pack(v[2], v[3]), LsPack<T>::pack(v[4], v[5]),
-                            LsPack<T>::pack(v[6], v[7]));
-        dst[1] = make_uint4(LsPack<T>::pack(v[8], v[9]), LsPack<T>::pack(v[10], v[11]), LsPack<T>::pack(v[12], v[13]),
-                            LsPack<T>::pack(v[14], v[15]));
       }
     }
   }
@@ -212,13 +230,13 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
   __syncthreads();
   if (warp == 2) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem, kLsTile);
+    ptx::tmem_dealloc(tmem, 512);
   }
 }
 
 template <typename T>
 cudaError_t launch_t(const LinSiluParams& p, const CUtensorMap& mx, const CUtensorMap& mw, cudaStream_t stream) {
-  constexpr int smem = 1024 + kLsStages * 2 * kLsChunkBytes + 256;
+  constexpr int smem = 1024 + kLsStages * 2 * kLsChunkBytes + 256 + kLsTile * 4;
   static_assert(sizeof(LsBars) <= 256, "barrier block too large");
   auto kern = in_linear_silu_kernel<T>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -235,7 +253,7 @@ cudaError_t launch_in_linear_silu(const LinSiluParams& p, const void* x, const v
                                   cudaStream_t stream) {
   if (p.m == 0) return cudaSuccess;
   CUtensorMap mx, mw;
-  if (!make_matrix_map(&mx, x, p.m, p.k, dtype) || !make_matrix_map(&mw, weight, p.n, p.k, dtype))
+  if (!make_matrix_map(&mx, x, p.m, p.k, dtype, kLsTile) || !make_matrix_map(&mw, weight, p.n, p.k, dtype, kLsTile))
     return cudaErrorNotSupported;
   return dtype == HSTU_DTYPE_BF16 ? launch_t<__nv_bfloat16>(p, mx, mw, stream) : launch_t<__half>(p, mx, mw, stream);
 }
