@@ -22,16 +22,6 @@ bool bwd_tc_supported(const BwdParams& bp, int dtype);
 cudaError_t launch_bwd_tc(const BwdParams& bp, int dtype, int num_sms, cudaStream_t stream);
 cudaError_t launch_ln_mul(const float* x, const float* u, const float* gamma, const float* beta, float* out,
                           long long rows, int cols, float eps, int num_sms, cudaStream_t stream);
-struct LinSiluParams {
-  const float* bias;
-  void* out[4];
-  void* linear;
-  int width[4];
-  int start[5];
-  long long m;
-  int n, k;
-  uint32_t* status;
-};
 cudaError_t launch_in_linear_silu(const LinSiluParams& p, const void* x, const void* weight, int dtype,
                                   cudaStream_t stream);
 }  // namespace hstu

@@ -66,6 +66,18 @@ struct BwdParams {
   void* dbias;        // [batch, hq, maxq, maxk] or null
 };
 
+// in_linear_silu call: the output tensors and the column ranges of mixed that go to each of them.
+struct LinSiluParams {
+  const float* bias;       // [n] or null
+  void* out[4];            // user, value, query, key: [m, width[i]]
+  void* linear;            // [m, n]
+  int width[4];
+  int start[5];            // first column of each output in mixed; start[4] = n
+  long long m;
+  int n, k;
+  uint32_t* status;        // optional: HSTU_ST_PIPE_TIMEOUT is or-ed into it when a wait gives up
+};
+
 struct SeqInfo {
   long long q0, k0;  // first token of the sequence in q / k,v
   int lq, lk;        // lengths

@@ -23,23 +23,12 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include "../../include/hstu_b200.h"
+#include "hstu_common.cuh"
 #include "ptx_sm100.cuh"
 
 namespace hstu {
 
 bool make_matrix_map(CUtensorMap* m, const void* base, long long rows, long long cols, int dtype, int box_rows);
-
-struct LinSiluParams {
-  const float* bias;       // [n] or null
-  void* out[4];            // user, value, query, key: [m, width[i]]
-  void* linear;            // [m, n]
-  int width[4];
-  int start[5];            // first column of each output in mixed; start[4] = n
-  long long m;
-  int n, k;
-  uint32_t* status;        // optional: HSTU_ST_PIPE_TIMEOUT is or-ed into it when a wait gives up
-};
 
 namespace {
 
