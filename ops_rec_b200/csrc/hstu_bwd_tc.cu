@@ -47,6 +47,9 @@ template <> struct BPack<__nv_bfloat16> {
   static __device__ __forceinline__ float one(const void* p, long long i) {
     return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
   }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+  }
 };
 template <> struct BPack<__half> {
   static constexpr int kFormat = 0;
@@ -56,6 +59,9 @@ template <> struct BPack<__half> {
   }
   static __device__ __forceinline__ float one(const void* p, long long i) {
     return __half2float(static_cast<const __half*>(p)[i]);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
   }
 };
 
@@ -355,6 +361,8 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
     const RowBounds rb_mine = row_bounds(s, (mine_ok || kDKV) ? mine : s.lq - 1, p.mask_type, p.group);  // dQ pass
     T* dbias = static_cast<T*>(bp.dbias);
     const bool dbias_vec = dbias && (p.maxk % 8 == 0) && (reinterpret_cast<uintptr_t>(bp.dbias) & 15u) == 0;
+    const bool bias_vec = p.bias && (p.maxk % 8 == 0) && (p.bias_bstride % 8 == 0) &&
+                          (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;
     // the dK/dV pass holds the score tile transposed (thread = key): a closed form for the visible queries of a key
     // exists for the plain causal / no-mask cases; context rows and grouped targets take the per-element rule
     const bool simple_mask = p.mask_type != HSTU_MASK_TRIL || (s.ctx == 0 && (s.tgt == 0 || p.group == 0));
@@ -400,6 +408,21 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         if (all_off) {
 #pragma unroll
           for (int e = 0; e < 16; ++e) u1[e] = u2[e] = 0u;
+        } else if (!kDKV && bias_vec && mine_ok && srow0 + col + 32 <= p.maxk) {
+          // dQ pass: the 32 bias values of this row and chunk are contiguous - four 16-byte loads
+          const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + bias_bh +
+                                                            static_cast<long long>(mine) * p.maxk + srow0 + col);
+          uint32_t bw[16];
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const uint4 v4 = __ldg(src + q4);
+            bw[4 * q4] = v4.x, bw[4 * q4 + 1] = v4.y, bw[4 * q4 + 2] = v4.z, bw[4 * q4 + 3] = v4.w;
+          }
+#pragma unroll
+          for (int e = 0; e < 16; ++e)
+            score_grad2<T, true, true>(make_float2(__uint_as_float(t1[2 * e]), __uint_as_float(t1[2 * e + 1])),
+                                       make_float2(__uint_as_float(t2[2 * e]), __uint_as_float(t2[2 * e + 1])),
+                                       BPack<T>::unpack(bw[e]), p.alpha, p.scale, (bits >> (2 * e)) & 3u, u1[e], u2[e]);
         } else if (p.bias) {
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
