@@ -322,7 +322,9 @@ def main_in_linear_silu(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path to the ops-rec tree> [backward | ln_mul | in_linear_silu]")
+    ref_root = sys.argv[1]
     if len(sys.argv) > 2 and sys.argv[2] == "in_linear_silu":   # only the in_linear_silu fixtures
         main_in_linear_silu(ref_root)
         return
