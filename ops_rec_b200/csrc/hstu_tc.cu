@@ -42,10 +42,15 @@ constexpr int kColS0 = 0, kColS1 = 128, kColO0 = 256;
 constexpr long long kWaitLimitCycles = 2000000000ll;  // ~1 s
 constexpr int kSchedStages = 8;                       // depth of the work-item ring between scheduler and roles
 constexpr int kSchedReaders = 3 + 2 * 128;            // producer lane + two MMA lanes + every thread of both P/O groups
+                                                      // (+ the two bias cursors of the scheduler thread, kBias == 2)
 
-// kBias: 0 = no attn_bias, 1 = bias read by plain loads (fallback when its rows are not 16-byte aligned),
+// kBias: 0 = no attn_bias, 1 = bias read by plain loads and added in registers (fallback when its rows are not
+// 16-byte aligned, or with HSTU_FLAG_ALPHA_BEFORE_BIAS),
 // 3 = no bias, but a custom mask (mask_type 3) read by plain loads through the same operand path: P *= mask,
-// 2 = bias tiles staged in shared memory by TMA.
+// 2 = bias tiles staged in shared memory by TMA and added to S on the tensor cores: after S = Q.K^T the issuer
+//     runs eight M128 N16 K16 products  S[:, 16s .. 16s+16) += bias[:, 16s .. 16s+16) . I16  (the staged tile is the
+//     K-major A operand, a 16 x 16 identity the B operand), so the P/O groups never touch the bias and the
+//     staging buffer is free again as soon as these products complete.
 template <int D, int kBias = 0>
 struct Cfg {
   static constexpr int kHalves = D / 64;                 // 128-byte swizzle atoms along the head dim
@@ -55,7 +60,7 @@ struct Cfg {
   static constexpr int kStages = D == 128 ? (kBias == 2 ? 3 : 4) : 8;          // K/V ring slots (one tile each)
   static constexpr int kQBytes = 2 * kTileBytes;
   static constexpr int kRingBytes = kStages * kTileBytes;
-  static constexpr int kBarBytes = 1024;
+  static constexpr int kBarBytes = 2048;
   // output staging for TMA stores: per P/O group two buffers of 128 rows x 32 columns (16 bit); not available
   // when the staged bias tiles already fill the shared memory
   static constexpr int kOutWarpBytes = 32 * 32 * 2;   // output staging: 32 rows x 32 columns per warp and buffer
@@ -95,8 +100,11 @@ struct Barriers {
   Item sched_item[kSchedStages];
   uint32_t tmem_base;
   int abort_flag;
+  // kBias == 2: the 16 x 16 identity the bias products multiply by, in the element type, as a K-major operand
+  // without swizzle: four 8 x 8 core matrices of 128 bytes, element (n, k) at (n/8)*256 + (k/8)*128 + (n%8)*16 + (k%8)*2
+  alignas(16) uint16_t ident[256];
 };
-static_assert(sizeof(Barriers) <= 1024, "barrier block too large");
+static_assert(sizeof(Barriers) <= 2048, "barrier block too large");
 
 struct Waiter {
   int* abort_flag;
@@ -137,13 +145,6 @@ struct ItemFeed {
     if (*reinterpret_cast<volatile int*>(w->abort_flag)) it.valid = 0;  // a wait gave up: stop taking work
     ptx::mbar_arrive(ptx::smem_u32(&bars->sched_free[slot]));
     ++n;
-    return it.valid != 0;
-  }
-  // Look at the next item without taking it; false when the scheduler has not published it yet.
-  __device__ __forceinline__ bool peek(Item& it) const {
-    const uint32_t slot = n % kSchedStages;
-    if (!ptx::mbar_try_wait(ptx::smem_u32(&bars->sched_full[slot]), (n / kSchedStages) & 1u)) return false;
-    it = bars->sched_item[slot];
     return it.valid != 0;
   }
 };
@@ -211,23 +212,7 @@ struct BiasRow {
   bool row_ok;          // row i exists in the sequence
   bool vec_ok;          // 16-byte loads are aligned
   int maxk, lk;
-  uint32_t smem_row;    // kBias == 2: shared-memory address of this row in the staged tile (first 64-column half)
-  uint32_t swz;         // row & 7: the 16-byte-chunk XOR of the 128-byte swizzle
 };
-
-// 32 consecutive bias values of this thread's row from the TMA-staged tile (two 64-column halves of 128 rows x
-// 128 bytes, 128-byte swizzle), columns ch*32 .. ch*32+31 of the tile.
-// Result: 16 words, two 16-bit values each (converted to fp32 only where they are consumed).
-__device__ __forceinline__ void load_bias32_smem(const BiasRow& br, int ch, uint32_t (&bv)[16]) {
-  const uint32_t half = br.smem_row + (ch >> 1) * (kTileM * 128);
-#pragma unroll
-  for (int q4 = 0; q4 < 4; ++q4) {
-    const uint32_t chunk = static_cast<uint32_t>((ch & 1) * 4 + q4) ^ br.swz;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(bv[q4 * 4]), "=r"(bv[q4 * 4 + 1]), "=r"(bv[q4 * 4 + 2]), "=r"(bv[q4 * 4 + 3])
-                 : "r"(half + chunk * 16));
-  }
-}
 
 // 32 consecutive bias values of one row, starting at column jb, as 16 packed words (0 beyond the sequence).
 template <typename T>
@@ -269,7 +254,7 @@ __device__ __forceinline__ void silu_chunk(const uint32_t (&sr)[32], const uint3
 #pragma unroll
   for (int e = 0; e < 16; ++e) {
     float2 x = make_float2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1]));
-    if (kBias == 1 || kBias == 2)
+    if (kBias == 1)
       x = __ffma2_rn(x, cin2, __fmul2_rn(Pack<T>::unpack(bv[e]), cb2));
     else
       x = __fmul2_rn(x, cin2);
@@ -307,9 +292,16 @@ __device__ __forceinline__ uint32_t visible_bits(const RowBounds& rb, int j0) {
 // read.  The TMEM load of the second 32 columns is in flight while the first 32 are computed.  In a tile the mask
 // cuts through (kMasked) every warp classifies each 32 x 32 chunk of its rows: all visible -> plain path, nothing
 // visible -> zeros without any arithmetic, mixed -> per-element select.
+//
+// kBias == 2: the bias is already inside S (added by the tensor cores) except for the one 16-column slice of a
+// sequence's last K tile that contains the sequence end - the issuer leaves that slice out, because whatever lies
+// in the bias buffer beyond column lk would reach the visible columns of the slice through the identity product
+// (0 x NaN).  fix_n > 0 names that slice (tile columns [fix_col, fix_col + 16), of which the first fix_n are inside
+// the sequence); its owner adds those few bias values from global memory.
 template <typename T, int kBias, bool kMasked>
 __device__ __forceinline__ void p_half(uint32_t t_s, int grp, int c0, const BiasRow& br, const RowBounds& rb,
-                                       float c_in, float c_bias, float scale, uint32_t bar_p0) {
+                                       float c_in, float c_bias, float scale, uint32_t bar_p0, int fix_col,
+                                       int fix_n) {
   uint32_t sbuf[2][32];
   uint32_t bv[16];
   uint32_t pr[16];
@@ -327,9 +319,21 @@ __device__ __forceinline__ void p_half(uint32_t t_s, int grp, int c0, const Bias
       all_off = __all_sync(0xffffffffu, vis == 0u);
     }
     if ((kBias == 1 || kBias == 3) && !all_off) load_bias32<T>(br, j0 + ch * 32, bv);
-    if (kBias == 2 && !all_off) load_bias32_smem(br, 2 * grp + ch, bv);
     ptx::tmem_wait_ld_dep(sbuf[ch]);
     if (ch == 0) ptx::tmem_ld32(s_col + 32, sbuf[1]);
+    if (kBias == 2 && fix_n > 0 && (fix_col & ~16) == 64 * grp + 32 * ch && br.row_ok) {
+      const long long at = br.row + c0 + fix_col;
+      if ((fix_col & 16) == 0) {
+#pragma unroll
+        for (int e = 0; e < 15; ++e)
+          if (e < fix_n) sbuf[ch][e] = __float_as_uint(__uint_as_float(sbuf[ch][e]) + Pack<T>::one(br.base, at + e));
+      } else {
+#pragma unroll
+        for (int e = 0; e < 15; ++e)
+          if (e < fix_n)
+            sbuf[ch][16 + e] = __float_as_uint(__uint_as_float(sbuf[ch][16 + e]) + Pack<T>::one(br.base, at + e));
+      }
+    }
     if (all_on) {
       silu_chunk<T, kBias, false>(sbuf[ch], bv, pr, c_in, c_bias, scale, 0u);
     } else if (all_off) {
@@ -384,7 +388,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     ptx::mbar_init(ptx::smem_u32(&bars->done[1]), 1);
     for (int t = 0; t < 2; ++t) {
       ptx::mbar_init(ptx::smem_u32(&bars->bias_full[t]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->bias_free[t]), 2 * kTileM);
+      ptx::mbar_init(ptx::smem_u32(&bars->bias_free[t]), 1);  // the commit of the bias products
     }
     for (int s = 0; s < C::kStages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&bars->kv_full[s]), 1);
@@ -392,10 +396,17 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     }
     for (int s = 0; s < kSchedStages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&bars->sched_full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->sched_free[s]), kSchedReaders);
+      ptx::mbar_init(ptx::smem_u32(&bars->sched_free[s]), kSchedReaders + (kBias == 2 ? 2 : 0));
     }
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
+  }
+  if (kBias == 2 && threadIdx.x >= 128) {
+    // the identity operand of the bias products (1.0 in the element type on the diagonal)
+    const int e = threadIdx.x - 128, n = e >> 4, k = e & 15;
+    const uint16_t one = Pack<T>::kFormat == 1 ? 0x3F80 : 0x3C00;
+    bars->ident[((n >> 3) * 256 + (k >> 3) * 128 + (n & 7) * 16 + (k & 7) * 2) >> 1] = n == k ? one : 0;
+    ptx::fence_proxy_async();  // generic-proxy writes, read by the tensor cores through the async proxy
   }
   if (warp == 2) {
     ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), kTmemCols);
@@ -481,7 +492,16 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       const uint32_t bar_s_full = ptx::smem_u32(&bars->s_full[t]);
       const uint32_t bar_p_full = ptx::smem_u32(&bars->p_full[t][0]), bar_p_half1 = ptx::smem_u32(&bars->p_full[t][1]);
       const uint32_t bar_o_full = ptx::smem_u32(&bars->o_full[t]), bar_o_free = ptx::smem_u32(&bars->o_free[t]);
-      uint32_t q_uses = 0, p_uses = 0, o_uses = 0;
+      // kBias == 2: the staged bias tile of this Q tile as K-major A operand, the identity as B operand (no swizzle:
+      // 128 bytes between the core matrices along K, 256 along N), 16 score columns per product
+      constexpr uint32_t idesc_bias = ptx::umma_idesc_f16(Pack<T>::kFormat, kTileM, 16, 0);
+      const uint64_t bias_base = kDescK | static_cast<uint64_t>((sm_bias + t * (kTileM * kTileN * 2)) >> 4);
+      const uint64_t ident_desc = static_cast<uint64_t>((ptx::smem_u32(bars->ident) & 0x3FFFFu) >> 4) |
+                                  (static_cast<uint64_t>(128 >> 4) << 16) | (static_cast<uint64_t>(256 >> 4) << 32) |
+                                  (static_cast<uint64_t>(1) << 46);
+      const uint32_t bar_bias_full = ptx::smem_u32(&bars->bias_full[t]);
+      const uint32_t bar_bias_free = ptx::smem_u32(&bars->bias_free[t]);
+      uint32_t q_uses = 0, p_uses = 0, o_uses = 0, b_uses = 0;
       uint32_t ring_base = 0;
 #ifdef HSTU_PROF
       unsigned long long prof_acc[6] = {0, 0, 0, 0, 0, 0};
@@ -505,8 +525,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           const bool ok_v = has_v ? ptx::mbar_try_wait(bar_vf, par_vf) : true;
           const bool ok_k = has_k ? ptx::mbar_try_wait(bar_kf, par_kf) : true;
           const bool ok_p = do_pv ? ptx::mbar_try_wait(bar_p_full, p_uses & 1u) : true;
+          const bool ok_b = (kBias == 2 && do_qk) ? ptx::mbar_try_wait(bar_bias_full, b_uses & 1u) : true;
           w.wait_polled(ok_v, bar_vf, par_vf);
           w.wait_polled(ok_k, bar_kf, par_kf);
+          if (kBias == 2 && do_qk) w.wait_polled(ok_b, bar_bias_full, b_uses & 1u);
           PROF_ADD(0, t_kv);
           PROF_T0(t_p);
           w.wait_polled(ok_p, bar_p_full, p_uses & 1u);
@@ -554,6 +576,23 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
               const uint64_t off = static_cast<uint64_t>(((ks >> 2) * C::kHalfBytes + (ks & 3) * 32) >> 4);
               ptx::mma_ss(col_s, qbase + off, kbase + off, idesc_qk, ks > 0 ? 1u : 0u);
             }
+            if (kBias == 2) {
+              // S_t += bias tile, 16 columns per product; only the slices that lie wholly inside the sequence
+              // (the slice that contains the sequence end is added by the P/O groups)
+              const int inside = (it.s.lk - step * kTileN) >> 4;
+              auto add_bias = [&](int sl) {
+                const uint64_t off = static_cast<uint64_t>(((sl >> 2) * (kTileM * 128) + (sl & 3) * 32) >> 4);
+                ptx::mma_ss(col_s + 16 * sl, bias_base + off, ident_desc, idesc_bias, 1u);
+              };
+              if (inside >= 8) {
+#pragma unroll
+                for (int sl = 0; sl < 8; ++sl) add_bias(sl);
+              } else {
+                for (int sl = 0; sl < inside; ++sl) add_bias(sl);
+              }
+              ptx::mma_commit(bar_bias_free);
+              ++b_uses;
+            }
             PROF_ADD(5, t_iqk);
             ptx::mma_commit(bar_s_full);
             if (step == n - 1) {
@@ -596,18 +635,91 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       // the scheduling pre-pass.  Only this thread reads what the pre-pass wrote (item count, work list, and the
       // offsets it validated), so only it has to wait for that grid to complete.
       asm volatile("griddepcontrol.wait;" ::: "memory");
-      const long long num_items = p.ws_header[1];
-      for (uint32_t n = 0;; ++n) {
-        const uint32_t slot = n % kSchedStages;
-        w.wait(ptx::smem_u32(&bars->sched_free[slot]), ((n / kSchedStages) & 1u) ^ 1u);
+      long long num_items = p.ws_header[1];
+      if (num_items > p.item_capacity) num_items = p.item_capacity;  // never read past the list (inconsistent offsets)
+      // Draw the next item from the global counter and publish it in ring slot n % kSchedStages.
+      auto publish = [&](uint32_t n) -> bool {
         const long long idx = static_cast<long long>(atomicAdd(&p.ws_header[2], 1u));
         const bool more = idx < num_items && !*reinterpret_cast<volatile int*>(&bars->abort_flag);
         Item it;
         if (more) it = load_item(p, idx);
         else it.valid = 0;
-        bars->sched_item[slot] = it;
-        ptx::mbar_arrive(ptx::smem_u32(&bars->sched_full[slot]));
-        if (!more) break;
+        bars->sched_item[n % kSchedStages] = it;
+        ptx::mbar_arrive(ptx::smem_u32(&bars->sched_full[n % kSchedStages]));
+        return more;
+      };
+      if (kBias != 2) {
+        for (uint32_t n = 0;; ++n) {
+          w.wait(ptx::smem_u32(&bars->sched_free[n % kSchedStages]), ((n / kSchedStages) & 1u) ^ 1u);
+          if (!publish(n)) break;
+        }
+      } else {
+        // With staged bias tiles this thread is also their TMA producer.  It polls instead of waiting: whenever a
+        // ring slot is free it publishes the next item, and whenever the bias buffer of Q tile t is free (its bias
+        // products have completed, early in the step) it requests that tile's next bias tile - so a bias tile has
+        // a whole step to arrive, whatever the other loads are waiting for.  A cursor holds its item's ring slot
+        // (it counts as one reader) until the item's last bias tile is requested.
+        uint32_t n_pub = 0;
+        bool sched_done = false;
+        uint32_t cur_item[2] = {0, 0}, loads[2] = {0, 0};
+        int cur_j[2] = {0, 0};
+        bool cur_done[2] = {false, false};
+        long long t_progress = clock64();
+        unsigned spins = 0;
+        while (!(sched_done && cur_done[0] && cur_done[1])) {
+          bool progress = false;
+          if (!sched_done &&
+              ptx::mbar_try_wait(ptx::smem_u32(&bars->sched_free[n_pub % kSchedStages]),
+                                 ((n_pub / kSchedStages) & 1u) ^ 1u)) {
+            if (!publish(n_pub)) sched_done = true;
+            ++n_pub;
+            progress = true;
+          }
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (cur_done[t] || cur_item[t] >= n_pub) continue;
+            const uint32_t slot = cur_item[t] % kSchedStages;
+            const Item& of = bars->sched_item[slot];
+            if (!of.valid) {
+              cur_done[t] = true;
+              continue;
+            }
+            if (cur_j[t] >= of.n(t)) {  // every bias tile of this item is requested: release the slot
+              ptx::mbar_arrive(ptx::smem_u32(&bars->sched_free[slot]));
+              ++cur_item[t];
+              cur_j[t] = 0;
+              progress = true;
+              continue;
+            }
+            if (!ptx::mbar_try_wait(ptx::smem_u32(&bars->bias_free[t]), (loads[t] & 1u) ^ 1u)) continue;
+            const uint32_t bfull = ptx::smem_u32(&bars->bias_full[t]);
+            ptx::mbar_expect_tx(bfull, kTileM * kTileN * 2);
+            const int brow = of.b * (p.bias_bstride ? p.hq * p.maxq : 0) + of.h * p.maxq + of.r0 + t * kTileM;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf)
+              ptx::tma_load_2d(sm_bias + t * (kTileM * kTileN * 2) + hf * (kTileM * 128), &tm_bias, bfull,
+                               cur_j[t] * kTileN + hf * 64, brow);
+            ++loads[t];
+            ++cur_j[t];
+            progress = true;
+          }
+          if (progress) {
+            t_progress = clock64();
+          } else if ((++spins & 0xffu) == 0) {
+            // a wait gave up somewhere: every reader of the item ring stops by itself when it sees the flag
+            if (*reinterpret_cast<volatile int*>(&bars->abort_flag)) break;
+            if (clock64() - t_progress > kWaitLimitCycles) {
+              *reinterpret_cast<volatile int*>(&bars->abort_flag) = 1;
+              atomicOr(p.ws_header, static_cast<uint32_t>(HSTU_ST_PIPE_TIMEOUT));
+            }
+          }
+        }
+        // the bias tiles this thread requested have landed (already true unless a wait gave up)
+        for (int t = 0; t < 2; ++t) {
+          if (loads[t] == 0) continue;
+          const uint32_t bar = ptx::smem_u32(&bars->bias_full[t]);
+          for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (loads[t] - 1) & 1u); ++spin) {}
+        }
       }
     }
     __syncwarp();
@@ -625,9 +737,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     // bf16 works on a = y / 2 (tanh form), fp16 on y itself;  x = c_in * s + c_bias * bias
     const float c_in = kExact ? p.alpha : 0.5f * p.alpha;
     const float c_bias = alpha_first ? (kExact ? 1.f : 0.5f) : c_in;
-    const bool bias_thread = kBias == 2 && grp == 0 && row == 0;  // fetches the staged bias tiles of both Q tiles
-    uint32_t s_uses[2] = {0, 0}, o_uses[2] = {0, 0}, b_uses[2] = {0, 0}, b_loads[2] = {0, 0};
-    bool bias_ahead[2] = {false, false};  // (bias thread) the next item's first bias tile is already requested
+    uint32_t s_uses[2] = {0, 0}, o_uses[2] = {0, 0};
     uint32_t out_chunks = 0;              // TMA-store chunks issued so far by this warp (selects the staging buffer)
 #ifdef HSTU_PROF
     unsigned long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
@@ -724,23 +834,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         i_row[t] = it.r0 + t * kTileM + row;
         row_ok[t] = i_row[t] < it.s.lq;
         rb[t] = row_bounds(it.s, row_ok[t] ? i_row[t] : it.s.lq - 1, p.mask_type, p.group);
-        bias_row[t] = (kBias == 1 || kBias == 3) ? static_cast<long long>(it.b) * p.bias_bstride +
+        bias_row[t] = kBias != 0 ? static_cast<long long>(it.b) * p.bias_bstride +
                                        (static_cast<long long>(it.h) * p.maxq + i_row[t]) * p.maxk
                                  : 0;
       }
-      // kBias == 2: TMA of the 128 x 128 bias tile (Q tile t, K tile jt) into that Q tile's staging buffer, once
-      // all 256 threads have released its previous contents.  Only the bias thread calls it.
-      auto issue_bias = [&](int t, const Item& of, int jt) {
-        const uint32_t bfull = ptx::smem_u32(&bars->bias_full[t]);
-        w.wait(ptx::smem_u32(&bars->bias_free[t]), (b_loads[t] & 1u) ^ 1u);
-        ++b_loads[t];
-        ptx::mbar_expect_tx(bfull, kTileM * kTileN * 2);
-        const int brow = of.b * (p.bias_bstride ? p.hq * p.maxq : 0) + of.h * p.maxq + of.r0 + t * kTileM;
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf)
-          ptx::tma_load_2d(sm_bias + t * (kTileM * kTileN * 2) + hf * (kTileM * 128), &tm_bias, bfull,
-                           jt * kTileN + hf * 64, brow);
-      };
       // Tile 0 usually ends one K tile before tile 1: its output leaves while tile 1's last S tile is computed.
       // (Keeping tile 1's output back until the next item's first score tile has been served was measured too:
       // slower on every workload.)
@@ -766,37 +863,15 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           if (grp == 0 && row == 0) TRACE(t, 3);
           ++s_uses[t];
           ptx::tc_fence_after();
-          const BiasRow br{p.bias, bias_row[t], row_ok[t], bias_vec_ok != 0, p.maxk, it.s.lk,
-                           sm_bias + t * (kTileM * kTileN * 2) + row * 128, static_cast<uint32_t>(row & 7)};
-          if (kBias == 2) {
-            // the first bias tile of an item is requested as soon as the item is known (unless it was requested
-            // ahead, at the end of the previous item); its latency hides behind the wait for S
-            if (bias_thread && j == 0 && !bias_ahead[t]) issue_bias(t, it, 0);
-            bias_ahead[t] = false;
-            __syncwarp();
-            w.wait(ptx::smem_u32(&bars->bias_full[t]), b_uses[t] & 1u);
-            ++b_uses[t];
-          }
+          const BiasRow br{p.bias, bias_row[t], row_ok[t], bias_vec_ok != 0, p.maxk, it.s.lk};
+          // kBias == 2: the 16-column slice of the sequence's last K tile that holds the sequence end (if any)
+          const int rem = it.s.lk - c0;
+          const int fix_n = (kBias == 2 && rem < kTileN) ? (rem & 15) : 0;
+          const int fix_col = rem & ~15;
           if (full)
-            p_half<T, kBias, false>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p);
+            p_half<T, kBias, false>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p, fix_col, fix_n);
           else
-            p_half<T, kBias, true>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p);
-          if (kBias == 2) {
-            ptx::mbar_arrive(ptx::smem_u32(&bars->bias_free[t]));  // this thread has read its part of the staged tile
-            if (bias_thread) {
-              if (j + 1 < it.n(t)) {
-                issue_bias(t, it, j + 1);
-              } else {
-                // last K tile of this Q tile: start on the first bias tile of the next item if it is known already
-                Item nx;
-                if (feed.peek(nx) && nx.n(t) > 0) {
-                  issue_bias(t, nx, 0);
-                  bias_ahead[t] = true;
-                }
-              }
-            }
-            __syncwarp();
-          }
+            p_half<T, kBias, true>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p, fix_col, fix_n);
           if (grp == 0 && row == 0) TRACE(t, 4);
           PROF_ADD(1, t_silu);
 #ifdef HSTU_PROF
@@ -808,14 +883,6 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       store_o(1, OutTile{it.s.q0, it.s.lq, it.r0 + kTileM, it.h, it.n1});
     }
     if (C::kOutBytes > 0 && lane == 0) ptx::bulk_wait<0>();  // this thread's TMA stores have completed
-    if (bias_thread) {
-      // the last bias tiles this thread requested have landed (already true unless a wait gave up)
-      for (int t = 0; t < 2; ++t) {
-        if (b_loads[t] == 0) continue;
-        const uint32_t bar = ptx::smem_u32(&bars->bias_full[t]);
-        for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (b_loads[t] - 1) & 1u); ++spin) {}
-      }
-    }
 #ifdef HSTU_PROF
     if (row == 0) {
       for (int i = 0; i < 6; ++i) g_prof[blockIdx.x][grp * 6 + i] = prof_acc[i];
@@ -978,11 +1045,12 @@ cudaError_t launch_tc(const KParams& p_in, int dtype, int num_sms, cudaStream_t 
   const int g = static_cast<int>(grid);
   const int vec_ok = p.bias && (p.maxk % 8 == 0) && (p.bias_bstride % 8 == 0) &&
                      (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;
-  // bias staging by TMA needs 16-byte aligned rows and batch blocks laid out back to back (or one shared block)
+  // bias staging by TMA needs 16-byte aligned rows and batch blocks laid out back to back (or one shared block);
+  // the tensor cores then add the tile to S, which gives alpha * (S + bias) only
   int bias_mode = p.bias ? 1 : 0;
   CUtensorMap mb = mq;
   if (custom_mask) bias_mode = 3;
-  if (!custom_mask && p.bias && vec_ok &&
+  if (!custom_mask && p.bias && vec_ok && !(p.flags & HSTU_FLAG_ALPHA_BEFORE_BIAS) &&
       (p.bias_bstride == 0 || p.bias_bstride == static_cast<long long>(p.hq) * p.maxq * p.maxk) &&
       make_bias_map(&mb, p, dtype))
     bias_mode = 2;
