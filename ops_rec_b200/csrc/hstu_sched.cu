@@ -59,6 +59,9 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
       run += s_count[key] * static_cast<unsigned>(key) * static_cast<unsigned>(p.hq);
     }
     s_start[0] = run;
+    // never more than the list holds: offsets that are not monotone can describe more q-pairs than total_q has
+    // rows for (the host sizes the list from total_q); the surplus items are dropped, the status word says why
+    if (static_cast<long long>(run) > p.item_capacity) run = static_cast<unsigned>(p.item_capacity);
     p.ws_header[1] = build_items ? run : 0u;
   }
   if (!build_items) return;

@@ -114,6 +114,7 @@ struct Waiter {
   __device__ __forceinline__ void wait_polled(bool polled, uint32_t bar, uint32_t parity) const {
     if (!polled) wait(bar, parity);
   }
+  __device__ __forceinline__ bool aborted() const { return *reinterpret_cast<volatile int*>(abort_flag) != 0; }
   __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity) const {
     if (ptx::mbar_try_wait(bar, parity)) return;
     if (*reinterpret_cast<volatile int*>(abort_flag)) return;
@@ -168,8 +169,15 @@ __device__ __forceinline__ Item load_item(const KParams& p, long long idx) {
   it.b = static_cast<int>(p.items[2 * idx]);
   const uint32_t hp = p.items[2 * idx + 1];
   it.h = static_cast<int>(hp >> 16);
-  it.hk = it.h / p.gqa_ratio;
   it.r0 = static_cast<int>(hp & 0xffffu) * kPairM;
+  // an entry that does not name a (sequence, head) of this call does nothing (the list is rebuilt by every call,
+  // so this can only happen with inconsistent offsets; it must still never address anything out of range)
+  if (it.b < 0 || it.b >= p.batch || it.h >= p.hq) {
+    it.b = 0;
+    it.h = 0;
+    it.r0 = 0x40000000;
+  }
+  it.hk = it.h / p.gqa_ratio;
   it.s = load_seq(p, it.b);
   it.n0 = kv_tiles_for_rows(it.s, it.r0, kTileM, p.mask_type, kTileN);
   it.n1 = kv_tiles_for_rows(it.s, it.r0 + kTileM, kTileM, p.mask_type, kTileN);
@@ -296,12 +304,13 @@ __device__ __forceinline__ uint32_t visible_bits(const RowBounds& rb, int j0) {
 // kBias == 2: the bias is already inside S (added by the tensor cores) except for the one 16-column slice of a
 // sequence's last K tile that contains the sequence end - the issuer leaves that slice out, because whatever lies
 // in the bias buffer beyond column lk would reach the visible columns of the slice through the identity product
-// (0 x NaN).  fix_n > 0 names that slice (tile columns [fix_col, fix_col + 16), of which the first fix_n are inside
-// the sequence); its owner adds those few bias values from global memory.
+// (0 x NaN).  The thread that owns that slice of its row (fix_ch = the 32-column chunk of this thread that holds
+// it, -1 = none; fix_lo = 0 or 16, its position inside the chunk) adds the fix_n bias values that lie inside the
+// sequence; the caller has fetched the slice into fixv (two values per word) before it waited for the scores.
 template <typename T, int kBias, bool kMasked>
 __device__ __forceinline__ void p_half(uint32_t t_s, int grp, int c0, const BiasRow& br, const RowBounds& rb,
-                                       float c_in, float c_bias, float scale, uint32_t bar_p0, int fix_col,
-                                       int fix_n) {
+                                       float c_in, float c_bias, float scale, uint32_t bar_p0, int fix_ch,
+                                       int fix_lo, int fix_n, const uint32_t (&fixv)[8]) {
   uint32_t sbuf[2][32];
   uint32_t bv[16];
   uint32_t pr[16];
@@ -321,17 +330,20 @@ __device__ __forceinline__ void p_half(uint32_t t_s, int grp, int c0, const Bias
     if ((kBias == 1 || kBias == 3) && !all_off) load_bias32<T>(br, j0 + ch * 32, bv);
     ptx::tmem_wait_ld_dep(sbuf[ch]);
     if (ch == 0) ptx::tmem_ld32(s_col + 32, sbuf[1]);
-    if (kBias == 2 && fix_n > 0 && (fix_col & ~16) == 64 * grp + 32 * ch && br.row_ok) {
-      const long long at = br.row + c0 + fix_col;
-      if ((fix_col & 16) == 0) {
+    if (kBias == 2 && fix_ch == ch) {
+      if (fix_lo == 0) {
 #pragma unroll
-        for (int e = 0; e < 15; ++e)
-          if (e < fix_n) sbuf[ch][e] = __float_as_uint(__uint_as_float(sbuf[ch][e]) + Pack<T>::one(br.base, at + e));
+        for (int e = 0; e < 15; ++e) {
+          const float2 b2 = Pack<T>::unpack(fixv[e >> 1]);
+          if (e < fix_n) sbuf[ch][e] = __float_as_uint(__uint_as_float(sbuf[ch][e]) + ((e & 1) ? b2.y : b2.x));
+        }
       } else {
 #pragma unroll
-        for (int e = 0; e < 15; ++e)
+        for (int e = 0; e < 15; ++e) {
+          const float2 b2 = Pack<T>::unpack(fixv[e >> 1]);
           if (e < fix_n)
-            sbuf[ch][16 + e] = __float_as_uint(__uint_as_float(sbuf[ch][16 + e]) + Pack<T>::one(br.base, at + e));
+            sbuf[ch][16 + e] = __float_as_uint(__uint_as_float(sbuf[ch][16 + e]) + ((e & 1) ? b2.y : b2.x));
+        }
       }
     }
     if (all_on) {
@@ -430,6 +442,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           if (it.n(t) == 0) return;
           const uint32_t full = ptx::smem_u32(&bars->q_full[t]);
           w.wait(ptx::smem_u32(&bars->q_free[t]), (q_uses[t] & 1u) ^ 1u);
+          if (w.aborted()) return;  // a wait gave up somewhere: request nothing more, touch no barrier
           ptx::mbar_expect_tx(full, C::kTileBytes);
           const int row = static_cast<int>(it.s.q0) + it.r0 + t * kTileM;
 #pragma unroll
@@ -448,6 +461,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
             const uint32_t use = ring_pos / C::kStages;
             const uint32_t full = ptx::smem_u32(&bars->kv_full[stage]);
             w.wait(ptx::smem_u32(&bars->kv_free[stage]), (use & 1u) ^ 1u);
+            if (w.aborted()) break;
             ptx::mbar_expect_tx(full, C::kTileBytes);
 #pragma unroll
             for (int hf = 0; hf < C::kHalves; ++hf)
@@ -537,6 +551,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           if (do_pv && step == 1) w.wait(bar_o_free, (o_uses & 1u) ^ 1u);
           if (do_qk && step == 0) w.wait(bar_q_full, q_uses & 1u);
           PROF_ADD(2, t_of);
+          if (w.aborted()) break;  // a wait gave up somewhere: issue nothing more, touch no barrier
           ptx::tc_fence_after();
           TRACE(2 + t, 1);
           if (do_pv) {
@@ -613,6 +628,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
             else ptx::mbar_arrive(ptx::smem_u32(&bars->kv_free[st_k]));
           }
         }
+        if (w.aborted()) break;
         ring_base += 2u * it.nmax;
       }
       // all MMAs (and the mbarrier arrivals of their commits) complete before the CTA tears down
@@ -756,6 +772,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         const uint32_t t_o = tmem + lane_base + (t == 0 ? kColO0 : C::kColO1) + col0;
         PROF_T0(t_wo);
         w.wait(ptx::smem_u32(&bars->o_full[t]), o_uses[t] & 1u);
+        if (w.aborted()) return;  // nothing valid to store; the barriers are left alone
         PROF_ADD(2, t_wo);
         PROF_T0(t_epi);
         if (grp == 0 && row == 0) TRACE(t, 5);
@@ -856,22 +873,44 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           const bool full = tile_is_full(it.s, tile_r0, kTileM, c0, kTileN, p.mask_type, p.group);
           const uint32_t t_s = tmem + lane_base + (t == 0 ? kColS0 : kColS1);
           const uint32_t bar_p = ptx::smem_u32(&bars->p_full[t][0]);
+          // kBias == 2: the 16-column slice of the sequence's last K tile that holds the sequence end (if any) is
+          // added here, not by the tensor cores; its owner fetches it now, before it waits for the scores
+          const int rem = it.s.lk - c0;
+          const int fix_n = (kBias == 2 && rem < kTileN) ? (rem & 15) : 0;
+          const int fix_col = rem & ~15;
+          const bool fix_mine = fix_n > 0 && (fix_col >> 6) == grp && row_ok[t];
+          uint32_t fixv[8];
+          if (kBias == 2 && fix_mine) {
+            const T* src = static_cast<const T*>(p.bias) + bias_row[t] + c0 + fix_col;
+            if (c0 + fix_col + 16 <= p.maxk) {  // 32-byte aligned: the rows are 16-byte aligned and c0 + fix_col is a multiple of 16
+              const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(src));
+              const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+              fixv[0] = u0.x, fixv[1] = u0.y, fixv[2] = u0.z, fixv[3] = u0.w;
+              fixv[4] = u1.x, fixv[5] = u1.y, fixv[6] = u1.z, fixv[7] = u1.w;
+            } else {
+              const unsigned short* s16 = reinterpret_cast<const unsigned short*>(src);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const uint32_t lo = 2 * e < fix_n ? s16[2 * e] : 0u;
+                const uint32_t hi = 2 * e + 1 < fix_n ? s16[2 * e + 1] : 0u;
+                fixv[e] = lo | (hi << 16);
+              }
+            }
+          }
+          const int fix_ch = (kBias == 2 && fix_mine) ? ((fix_col >> 5) & 1) : -1;
           PROF_T0(t_ws);
           w.wait(ptx::smem_u32(&bars->s_full[t]), s_uses[t] & 1u);
+          if (w.aborted()) break;  // (the item feed then ends the outer loops)
           PROF_ADD(0, t_ws);
           PROF_T0(t_silu);
           if (grp == 0 && row == 0) TRACE(t, 3);
           ++s_uses[t];
           ptx::tc_fence_after();
           const BiasRow br{p.bias, bias_row[t], row_ok[t], bias_vec_ok != 0, p.maxk, it.s.lk};
-          // kBias == 2: the 16-column slice of the sequence's last K tile that holds the sequence end (if any)
-          const int rem = it.s.lk - c0;
-          const int fix_n = (kBias == 2 && rem < kTileN) ? (rem & 15) : 0;
-          const int fix_col = rem & ~15;
           if (full)
-            p_half<T, kBias, false>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p, fix_col, fix_n);
+            p_half<T, kBias, false>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p, fix_ch, fix_col & 16, fix_n, fixv);
           else
-            p_half<T, kBias, true>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p, fix_col, fix_n);
+            p_half<T, kBias, true>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p, fix_ch, fix_col & 16, fix_n, fixv);
           if (grp == 0 && row == 0) TRACE(t, 4);
           PROF_ADD(1, t_silu);
 #ifdef HSTU_PROF
