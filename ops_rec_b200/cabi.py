@@ -134,6 +134,12 @@ def make_args(q, k, v, out, seq_offset, *, seq_offset_k=None, mask=None, attn_bi
               target_group_size=0, alpha=1.0, flags=0, ptr=lambda t: t.data_ptr()):
     """Fill an HstuJaggedArgs from tensors (torch tensors by default; `ptr` extracts the address).
     Returns (args, keepalive) - keepalive holds converted temporaries that must outlive the launch."""
+    for name, t in (("k", k), ("v", v), ("out", out), ("seq_offset", seq_offset), ("seq_offset_k", seq_offset_k),
+                    ("mask", mask), ("attn_bias", attn_bias), ("num_context", num_context),
+                    ("num_target", num_target)):
+        # a pointer to another device (or to host memory) would fault inside the kernel instead of failing here
+        if t is not None and hasattr(t, "device") and hasattr(q, "device") and t.device != q.device:
+            raise ValueError(f"{name} is on {t.device} but q is on {q.device}")
     a = HstuJaggedArgs()
     a.struct_bytes = C.sizeof(HstuJaggedArgs)
     a.dtype = _dtype_code(q.dtype)
@@ -330,15 +336,16 @@ def hstu_jagged_forward_static(q, k, v, out, mask=None, attn_bias=None, mask_typ
 
 
 def plan_host(seq_offset, heads_q, *, num_context=None, num_target=None, max_seq_len=20480, dim=128,
-              dtype_code=DTYPE_BF16, mask_type=0):
-    """Run the scheduler's ordering rule on host arrays; returns (items[n,2] uint32, status)."""
+              dtype_code=DTYPE_BF16, mask_type=0, total_q=None, count_only=False):
+    """Run the scheduler's ordering rule on host arrays; returns (items[n,2] uint32, status), or with count_only
+    (number of items the offsets describe, status).  total_q defaults to the last offset."""
     off = np.ascontiguousarray(np.asarray(seq_offset, dtype=np.int64))
     a = HstuJaggedArgs()
     a.struct_bytes = C.sizeof(HstuJaggedArgs)
     a.dtype = dtype_code
     a.index_bytes = 8
     a.batch = len(off) - 1
-    a.total_q = a.total_k = int(off[-1])
+    a.total_q = a.total_k = int(off[-1]) if total_q is None else int(total_q)
     a.heads_q = a.heads_k = heads_q
     a.dim_qk = a.dim_v = dim
     a.mask_type = mask_type
@@ -346,13 +353,15 @@ def plan_host(seq_offset, heads_q, *, num_context=None, num_target=None, max_seq
     a.alpha = 1.0
     ctx = np.ascontiguousarray(np.asarray(num_context, dtype=np.int64)) if num_context is not None else None
     tgt = np.ascontiguousarray(np.asarray(num_target, dtype=np.int64)) if num_target is not None else None
-    cap = heads_q * (int(off[-1]) // 256 + a.batch) + 1
+    cap = heads_q * (int(a.total_q) // 256 + a.batch) + 1
     items = np.zeros((cap, 2), dtype=np.uint32)
     st = C.c_uint32(0)
     n = check(load().hstu_plan_host(
         C.byref(a), off.ctypes.data, None, ctx.ctypes.data if ctx is not None else None,
         tgt.ctypes.data if tgt is not None else None, items.ctypes.data, cap, C.byref(st)))
-    return items[:n], st.value
+    if count_only:
+        return n, st.value
+    return items[:min(n, cap)], st.value
 
 
 def debug_mask(len_q, len_k, ctx, tgt, group, mask_type=0):

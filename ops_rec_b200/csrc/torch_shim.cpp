@@ -27,6 +27,13 @@ int dtype_code(at::ScalarType t) {
   }
 }
 
+// Every tensor whose address reaches a kernel must live on q's device: a CPU tensor, or one on another GPU, would be
+// read through a raw pointer and fault on the device instead of failing here.
+void check_same_device(const at::Tensor& t, const at::Tensor& q, const char* name) {
+  TORCH_CHECK(t.device() == q.device(), "hstu_jagged: ", name, " is on ", t.device(), " but q is on ", q.device(),
+              " (every tensor of a call must be on the same CUDA device)");
+}
+
 // The normalised arguments of one call: the C-ABI argument block plus the tensors that own what it points to.
 struct Prepared {
   HstuJaggedArgs a;
@@ -44,6 +51,12 @@ Prepared prepare(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
   TORCH_CHECK(k.dim() == 3 && v.dim() == 3, "The k and v should be 3D in jagged layout");
   TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda() && seq_offset.is_cuda(),
               "hstu_jagged: tensors must be CUDA tensors (there is no CPU implementation)");
+  check_same_device(k, q, "k");
+  check_same_device(v, q, "v");
+  check_same_device(seq_offset, q, "seq_offset");
+  check_same_device(seq_offset_k, q, "seq_offset_k");
+  if (attn_bias.has_value() && attn_bias->defined()) check_same_device(*attn_bias, q, "attn_bias");
+  if (mask.has_value() && mask->defined()) check_same_device(*mask, q, "mask");
   TORCH_CHECK(seq_offset.scalar_type() == at::kInt || seq_offset.scalar_type() == at::kLong,
               "seq_offset must be int32 or int64");
   Prepared pr;
@@ -191,6 +204,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> backward_impl(
   }
   TORCH_CHECK(grad.dim() == 3 && grad.is_cuda() && grad.scalar_type() == q.scalar_type(),
               "grad must be a 3D CUDA tensor of q's dtype");
+  check_same_device(grad, q, "grad");
   c10::cuda::CUDAGuard guard(q.device());
   Prepared pr = prepare(q, k, v, mask, attn_bias, mask_type, max_seq_len_q, max_seq_len_k, silu_scale, seq_offset,
                         seq_offset_k, num_context, num_target, target_group_size, alpha, false);
@@ -310,6 +324,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> in_linear
   TORCH_CHECK(weight.dim() == 2, "weight must be 2D");
   TORCH_CHECK(split.size() == 4, "splitList must have 4 elements.");
   TORCH_CHECK(x.is_cuda() && weight.is_cuda(), "in_linear_silu: tensors must be CUDA tensors");
+  TORCH_CHECK(weight.device() == x.device() && (!bias.defined() || bias.device() == x.device()),
+              "in_linear_silu: x, weight and bias must be on the same CUDA device");
   TORCH_CHECK(weight.scalar_type() == x.scalar_type(), "weight must have the dtype of x");
   TORCH_CHECK(weight.size(1) == x.size(1), "weight dim[1] must equal to x dim[1].");
   c10::cuda::CUDAGuard guard(x.device());

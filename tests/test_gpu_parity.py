@@ -235,9 +235,44 @@ def test_inconsistent_inputs_set_the_status_word_and_never_fault():
     past[-1] += 1000                                        # points past the end of q
     _, status = run_cabi(dict(args, seq_offset=past, seq_offset_k=past))
     assert status & cabi.ST_BAD_OFFSETS
+    # offsets that run back and forth describe more q-pairs than the work list (sized from total_q) can hold:
+    # the device clamps the list and ignores what does not fit - flagged, never a fault
+    B = off.numel() - 1
+    zig = torch.tensor([int(off[-1]) if i % 2 else 0 for i in range(B + 1)], dtype=off.dtype)
+    _, status = run_cabi(dict(args, seq_offset=zig, seq_offset_k=zig, max_seq_len=int(off[-1]),
+                              max_seq_len_k=int(off[-1]), attn_bias=None))
+    assert status & cabi.ST_BAD_OFFSETS
+    many = make_case(64, 4, 4, 128, 128, 60, 64, BF16, seed=5)
+    T = many["q"].shape[0]
+    zig = torch.tensor([T if i % 2 else 0 for i in range(65)], dtype=many["seq_offset"].dtype)
+    _, status = run_cabi(dict(many, seq_offset=zig, seq_offset_k=zig, max_seq_len=T, max_seq_len_k=T))
+    assert status & cabi.ST_BAD_OFFSETS
     out, status = run_cabi(args)                            # the context is still healthy
     assert status == 0
     assert_parity(out, args, label="after bad inputs")
+
+
+def test_tensors_on_another_device_are_refused_on_the_host():
+    """A CPU (or other-GPU) tensor among CUDA tensors must fail before any pointer reaches a kernel."""
+    import ops_rec_b200 as ops_rec
+    args = to_cuda(make_case(2, 2, 2, 64, 64, 5, 40, BF16, seed=3, rab="batch", tgt=2, g=1))
+    hj = ops_rec.ascendc.attention.hstu_jagged
+
+    def call(**over):
+        a = dict(args, **over)
+        return hj(a["q"], a["k"], a["v"], a["mask"], a["attn_bias"], a["mask_type"], a["max_seq_len"], 0.0,
+                  a["seq_offset"], None, a["num_target"], 1, a["alpha"])
+
+    for name in ("k", "v", "attn_bias", "seq_offset"):
+        with pytest.raises(RuntimeError, match="device|CUDA"):
+            call(**{name: args[name].cpu()})
+    with pytest.raises(RuntimeError, match="device|CUDA"):
+        call(mask=torch.ones(2, 2, args["max_seq_len"], args["max_seq_len"], dtype=BF16), mask_type=3)
+    with pytest.raises(ValueError, match="is on"):
+        cabi.hstu_jagged_forward(**dict(args, attn_bias=args["attn_bias"].cpu()))
+    out = call()                                            # and a consistent call still works
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
 
 
 def test_device_work_list_equals_host_plan():

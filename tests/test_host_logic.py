@@ -104,3 +104,17 @@ def test_work_list_flags_inconsistent_inputs():
     assert status & cabi.ST_BAD_CTX_TARGET
     items, status = cabi.plan_host(off, 2, num_context=[200, 0], num_target=[100, 0])
     assert status == 0 and len(items) == 2 * 2 * 2
+
+
+def test_overlapping_offsets_describe_more_items_than_the_list_is_sized_for():
+    # The workspace is sized from total_q (heads * (total_q / 256 + batch) items).  Offsets that run back and forth
+    # between 0 and T describe far more q-pairs than that; the plan reports them (and flags the offsets), and the
+    # device clamps its work list to the capacity it was given instead of reading past it.
+    T, B, H = 4096, 64, 4
+    off = np.array([T if i % 2 else 0 for i in range(B + 1)], dtype=np.int64)
+    items, status = cabi.plan_host(off, H, total_q=T)
+    assert status & cabi.ST_BAD_OFFSETS
+    bound = H * (T // 256 + B)
+    assert len(items) == bound + 1            # the plan stops one past the bound it was given room for ...
+    n, _ = cabi.plan_host(off, H, total_q=T, count_only=True)
+    assert n > bound                          # ... and counts more than the bound
