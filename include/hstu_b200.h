@@ -15,7 +15,9 @@
  * Rules of the boundary
  *   - plain C, no exceptions: every function returns 0 on success or a negative HSTU_E* code; the text of the last
  *     error of the calling thread is available from hstu_last_error().
- *   - the caller owns every buffer, including the workspace; the library allocates no device memory.
+ *   - the caller owns every buffer, including the workspace; the library allocates no device memory.  (The only
+ *     device memory the library holds is the fixed scratch block of hstu_jagged_fwd_static, below, which is part of
+ *     the library image: HSTU_STATIC_SCRATCH_BYTES per GPU, from load until the process exits.)
  *   - hstu_jagged_fwd is asynchronous on `stream`; it never synchronises and never reads device data on the host.
  *     The sequence offsets are device data, so per-call scheduling happens in a small device pre-pass.
  *   - there is no CPU implementation behind these entry points.
@@ -138,8 +140,15 @@ HSTU_API int hstu_jagged_fwd(const HstuJaggedArgs* args, void* workspace, uint64
  *     current); make that first call during start-up, before any stream capture begins.
  *   - All calls on a device share the one block, which keeps what the previous call left in it.  Each call's
  *     pre-pass re-initialises everything it reads, so calls that run one after another (same stream, or ordered by
- *     events) are safe; two calls that overlap on the GPU race on the block and give undefined results. */
+ *     events) are safe; two calls that overlap on the GPU race on the block and give undefined results.
+ *   - The looked-up address is cached for the life of the process; it does not survive cudaDeviceReset.
+ *   - Every error, HSTU_E_SCRATCH_LIMIT included, leaves its text in hstu_last_error(). */
 HSTU_API int hstu_jagged_fwd_static(const HstuJaggedArgs* args, void* stream);
+
+/* The device status word (HSTU_ST_* bits) of the last hstu_jagged_fwd_static call on the current device: its caller
+ * holds no workspace pointer that hstu_jagged_fwd_status could take.  Waits for `stream`, allocates nothing.  No
+ * counterpart in the reference. */
+HSTU_API int hstu_jagged_fwd_static_status(void* stream, uint32_t* status);
 
 /* ---------------------------------------------------------------------------------------------------- backward
  * Replaces the aclnnHstuJaggedBackward call of the reference adapter
@@ -198,6 +207,9 @@ typedef struct OpsRecInLinearSiluArgs {
   int32_t n;
   int32_t k;
   int32_t split[4];
+  /* optional device uint32, or NULL: HSTU_ST_PIPE_TIMEOUT is or-ed into it if a bounded wait inside the kernel gives up
+   * (the tile concerned is then not stored).  The caller clears it; the library only ever sets bits. */
+  void* status;
 } OpsRecInLinearSiluArgs;
 HSTU_API int ops_rec_in_linear_silu_fwd(const OpsRecInLinearSiluArgs* args, void* stream);
 

@@ -23,7 +23,7 @@ ST_BAD_OFFSETS, ST_LEN_GT_MAX, ST_BAD_CTX_TARGET, ST_PIPE_TIMEOUT = 1, 2, 4, 256
 EXPORTS = (
     "hstu_jagged_fwd_get_workspace_size", "hstu_jagged_fwd", "hstu_jagged_fwd_status",
     "hstu_jagged_fwd_kernel_kind", "hstu_plan_host", "hstu_debug_mask_host", "hstu_debug_tiles_host",
-    "hstu_last_error", "hstu_b200_version", "hstu_jagged_fwd_static",
+    "hstu_last_error", "hstu_b200_version", "hstu_jagged_fwd_static", "hstu_jagged_fwd_static_status",
     "hstu_jagged_bwd_get_workspace_size", "hstu_jagged_bwd", "ops_rec_ln_mul_f32", "ops_rec_in_linear_silu_fwd",
 )
 STATIC_SCRATCH_BYTES = 1 << 20
@@ -58,6 +58,7 @@ class OpsRecInLinearSiluArgs(C.Structure):
         ("struct_bytes", C.c_uint32), ("dtype", C.c_int32), ("x", C.c_void_p), ("weight", C.c_void_p),
         ("bias", C.c_void_p), ("user", C.c_void_p), ("value", C.c_void_p), ("query", C.c_void_p), ("key", C.c_void_p),
         ("linear_output", C.c_void_p), ("m", C.c_int64), ("n", C.c_int32), ("k", C.c_int32), ("split", C.c_int32 * 4),
+        ("status", C.c_void_p),
     ]
 
 
@@ -100,6 +101,8 @@ def load():
     lib.hstu_debug_tiles_host.restype = C.c_int
     lib.hstu_jagged_fwd_static.argtypes = [A, C.c_void_p]
     lib.hstu_jagged_fwd_static.restype = C.c_int
+    lib.hstu_jagged_fwd_static_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
+    lib.hstu_jagged_fwd_static_status.restype = C.c_int
     B = C.POINTER(HstuJaggedBwdArgs)
     lib.hstu_jagged_bwd_get_workspace_size.argtypes = [B, C.POINTER(C.c_uint64)]
     lib.hstu_jagged_bwd_get_workspace_size.restype = C.c_int
@@ -315,10 +318,11 @@ def ln_mul(x, u, gamma, beta):
 
 def hstu_jagged_forward_static(q, k, v, out, mask=None, attn_bias=None, mask_type=0, max_seq_len=0, silu_scale=0.0,
                                seq_offset=None, num_context=None, num_target=None, target_group_size=0, alpha=1.0,
-                               *, max_seq_len_k=None, seq_offset_k=None, flags=0):
+                               *, max_seq_len_k=None, seq_offset_k=None, flags=0, return_status=False):
     """The operator through hstu_jagged_fwd_static: no workspace, nothing allocated by the call.  `out` must be
     preallocated by the caller ([total_q, heads_q, dim_v], q's dtype); inputs must already be contiguous.
-    Raises HstuError(E_SCRATCH_LIMIT) when the work list does not fit the library's built-in scratch block."""
+    Raises HstuError(E_SCRATCH_LIMIT) when the work list does not fit the library's built-in scratch block.
+    With return_status the device status word is read back through hstu_jagged_fwd_static_status (this waits)."""
     import torch
     args, keep = make_args(q, k, v, out, seq_offset, seq_offset_k=seq_offset_k, mask=mask, attn_bias=attn_bias,
                            mask_type=mask_type, max_seq_len=max_seq_len, max_seq_len_k=max_seq_len_k,
@@ -327,10 +331,13 @@ def hstu_jagged_forward_static(q, k, v, out, mask=None, attn_bias=None, mask_typ
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
         rc = load().hstu_jagged_fwd_static(C.byref(args), stream)
-    if rc == E_SCRATCH_LIMIT:
-        raise HstuError(rc, f"the call needs more than the {STATIC_SCRATCH_BYTES} bytes of built-in scratch; "
-                            "use hstu_jagged_fwd with a caller workspace")
     check(rc)
+    if return_status:
+        st = C.c_uint32(0)
+        with torch.cuda.device(q.device):
+            check(load().hstu_jagged_fwd_static_status(stream, C.byref(st)))
+        del keep
+        return out, st.value
     del keep
     return out
 

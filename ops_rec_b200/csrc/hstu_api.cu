@@ -155,7 +155,10 @@ int device_info(DeviceInfo* out) {
 
 extern "C" {
 
-int hstu_b200_version(void) { return 100; }
+// for the other translation units of the library (not exported)
+int hstu_set_last_error(int code, const char* text) { return fail(code, "%s", text); }
+
+int hstu_b200_version(void) { return 101; }
 
 const char* hstu_last_error(void) { return g_err; }
 
@@ -225,6 +228,13 @@ static int validate_bwd(const HstuJaggedBwdArgs* a) {
   if (a->fwd.attn_bias && a->fwd.bias_batch_stride == 0 && a->fwd.batch > 1)
     return fail(HSTU_E_PARAM, "the backward needs a per-sequence attn_bias (a bias shared by the batch has no "
                               "per-sequence gradient slot)");
+  // grad_bias is a contiguous [batch, heads_q, max_seq_len_q, max_seq_len_k] tensor and is addressed like the
+  // bias: a padded batch stride would put the gradients of one and the zeros of the other in different places
+  const long long block = static_cast<long long>(a->fwd.heads_q) * a->fwd.max_seq_len_q * a->fwd.max_seq_len_k;
+  if (a->fwd.attn_bias && a->fwd.bias_batch_stride != 0 && a->fwd.bias_batch_stride != block)
+    return fail(HSTU_E_PARAM, "the backward needs a contiguous attn_bias: bias_batch_stride must be heads_q * "
+                              "max_seq_len_q * max_seq_len_k (%lld), but value is %lld", block,
+                (long long)a->fwd.bias_batch_stride);
   return HSTU_OK;
 }
 
@@ -268,7 +278,16 @@ int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t wor
   bp.dbias = f->attn_bias ? args->grad_bias : nullptr;
   cudaError_t e = hstu::launch_prepass(bp.f, false, stream);  // input consistency -> status word
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "pre-pass launch: %s", cudaGetErrorString(e));
-  if (f->total_q == 0 && f->total_k == 0 && !bp.dbias) return HSTU_OK;
+  if (f->total_q == 0 && bp.dbias) {
+    // no query rows: no kernel visits grad_bias, and every element of it is promised to be written
+    const size_t esize = f->dtype == HSTU_DTYPE_FP32 ? 4 : 2;
+    const size_t bytes = static_cast<size_t>(f->batch) * f->heads_q * f->max_seq_len_q * f->max_seq_len_k * esize;
+    e = cudaMemsetAsync(bp.dbias, 0, bytes, stream);
+    if (e != cudaSuccess) return fail(HSTU_E_CUDA, "clearing grad_bias: %s", cudaGetErrorString(e));
+    bp.dbias = nullptr;
+    bp.f.bias = nullptr;   // (nothing reads the bias either)
+  }
+  if (f->total_q == 0 && f->total_k == 0) return HSTU_OK;
   if (hstu::bwd_tc_supported(bp, f->dtype)) {
     e = hstu::launch_bwd_tc(bp, f->dtype, dev.sms, stream);
     if (e == cudaErrorNotSupported) return fail(HSTU_E_CUDA, "cuTensorMapEncodeTiled failed or is unavailable");
@@ -308,6 +327,7 @@ int ops_rec_in_linear_silu_fwd(const OpsRecInLinearSiluArgs* a, void* stream_v) 
                           reinterpret_cast<uintptr_t>(a->value) | reinterpret_cast<uintptr_t>(a->query) |
                           reinterpret_cast<uintptr_t>(a->key) | reinterpret_cast<uintptr_t>(a->linear_output);
   if (align & 15u) return fail(HSTU_E_PARAM, "in_linear_silu: every tensor must be 16-byte aligned");
+  if (reinterpret_cast<uintptr_t>(a->status) & 3u) return fail(HSTU_E_PARAM, "in_linear_silu: status must be 4-byte aligned");
   DeviceInfo dev;
   int rc = device_info(&dev);
   if (rc) return rc;
@@ -327,7 +347,7 @@ int ops_rec_in_linear_silu_fwd(const OpsRecInLinearSiluArgs* a, void* stream_v) 
   p.m = a->m;
   p.n = a->n;
   p.k = a->k;
-  p.status = nullptr;
+  p.status = static_cast<uint32_t*>(a->status);
   const cudaError_t e = hstu::launch_in_linear_silu(p, a->x, a->weight, a->dtype, static_cast<cudaStream_t>(stream_v));
   if (e == cudaErrorNotSupported) return fail(HSTU_E_CUDA, "cuTensorMapEncodeTiled failed or is unavailable");
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "in_linear_silu launch: %s", cudaGetErrorString(e));

@@ -90,8 +90,11 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
   uint8_t* base_ptr = smem_raw + (base - raw);
   LsBars* bars = reinterpret_cast<LsBars*>(base_ptr + kLsStages * 2 * kLsChunkBytes);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = blockIdx.x * kLsTile;
-  const long long m0 = static_cast<long long>(blockIdx.y) * kLsTile;
+  // tiles are numbered along the grid's x axis, the n tiles of one row block next to each other (so the CTAs that
+  // run together share their rows of x): the row count may be far larger than a grid's y extent allows
+  const int n_tiles = (p.n + kLsTile - 1) / kLsTile;
+  const int n0 = static_cast<int>(blockIdx.x % n_tiles) * kLsTile;
+  const long long m0 = static_cast<long long>(blockIdx.x / n_tiles) * kLsTile;
   const int chunks = (p.k + 63) / 64;
 
   if (tid == 0) {
@@ -167,11 +170,13 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
     uint8_t* stage = base_ptr + (warp - 4) * (2 * 32 * kPitch);  // [lin | silu] x 32 rows
     ls_wait(bars, p.status, ptx::smem_u32(&bars->acc_full), 0);  // all MMAs are done: the ring is free
     ptx::tc_fence_after();
+    // a wait gave up (status word set): the accumulators hold nothing valid, store nothing
+    const bool give_up = *reinterpret_cast<volatile int*>(&bars->abort_flag) != 0;
     const int sub_row = lane >> 2, part = lane & 3;              // store phase: 8 rows per instruction, 4 lanes per row
 #pragma unroll 1
     for (int ch = 0; ch < kLsTile / 32; ++ch) {
       const int c0 = n0 + ch * 32;
-      if (c0 >= p.n) break;   // uniform over the CTA
+      if (c0 >= p.n || give_up) break;   // uniform over the CTA
       uint32_t acc[32];
       ptx::tmem_ld32(tmem + lane_base + ch * 32, acc);
       ptx::tmem_wait_ld();
@@ -230,8 +235,9 @@ cudaError_t launch_t(const LinSiluParams& p, const CUtensorMap& mx, const CUtens
   auto kern = in_linear_silu_kernel<T>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  dim3 grid((p.n + kLsTile - 1) / kLsTile, static_cast<unsigned>((p.m + kLsTile - 1) / kLsTile), 1);
-  kern<<<grid, kLsThreads, smem, stream>>>(p, mx, mw);
+  const long long tiles = static_cast<long long>((p.n + kLsTile - 1) / kLsTile) * ((p.m + kLsTile - 1) / kLsTile);
+  if (tiles > 0x7fffffffll) return cudaErrorInvalidConfiguration;  // (m <= 2^31 - 256 and n <= 32768 never get here)
+  kern<<<dim3(static_cast<unsigned>(tiles)), kLsThreads, smem, stream>>>(p, mx, mw);
   return cudaGetLastError();
 }
 
