@@ -68,6 +68,8 @@ enum {
   HSTU_ST_BAD_OFFSETS = 1u << 0,   /* offsets not monotone */
   HSTU_ST_LEN_GT_MAX = 1u << 1,    /* a sequence is longer than max_seq_len (bias/mask rows would be overrun) */
   HSTU_ST_BAD_CTX_TARGET = 1u << 2,/* num_context + num_target exceeds the sequence length, or negative */
+  HSTU_ST_BAD_PAGES = 1u << 3,     /* hstu_paged: a page table that does not describe len_k - num_target cached rows,
+                                      or a page id outside the cache */
   HSTU_ST_PIPE_TIMEOUT = 1u << 8   /* a bounded wait inside the tensor-core kernel gave up */
 };
 
@@ -149,6 +151,38 @@ HSTU_API int hstu_jagged_fwd_static(const HstuJaggedArgs* args, void* stream);
  * holds no workspace pointer that hstu_jagged_fwd_status could take.  Waits for `stream`, allocates nothing.  No
  * counterpart in the reference. */
 HSTU_API int hstu_jagged_fwd_static_status(void* stream, uint32_t* status);
+
+/* ------------------------------------------------------------------------------------------------------- paged
+ * The forward with the history keys / values in a paged KV cache: replaces the aclnnHstuPagedForward call of the
+ * reference adapter (ascendc/attention/hstu_v1/torch_extension/hstu_paged_plugin.cpp:21-72, the EXEC_NPU_CMD at
+ * :67-69; kernel hstu_forward_v1/op_kernel/atlas950/hstu_paged_forward_kernel.h).  Per sequence b the operator attends
+ * over  K/V = [pages page_ids[page_offsets[b] .. page_offsets[b+1]) of kv_cache, the last cut to last_page_len[b]]
+ * followed by the last num_target[b] rows of the sequence's segment of base.k / base.v, with the composite mask of
+ * the jagged operator (num_target targets, each seeing the cache and itself).
+ *   base            the jagged arguments: q, out [total_q, heads_q, dim]; k, v [total_q, heads_k, dim] (only their
+ *                   target rows are read); seq_offset_q; seq_offset_k (REQUIRED: offsets of cached rows + targets per
+ *                   sequence); num_target; mask / attn_bias / mask_type / lengths / scales as in the jagged call;
+ *                   dim_qk == dim_v; base.total_k is ignored; num_context must be null (the reference passes zeros)
+ *   kv_cache        [num_pages, 2, page_size, heads_k, dim], element type of q; index 0 = keys, 1 = values
+ *   page_offsets    [batch + 1], page_ids [num_page_ids], last_page_len [batch]: device integers of the offsets' width
+ *   seq_offset_t    [batch + 1] offsets of num_target; implied by num_target and not read (may be null)
+ * Workspace (phase 1 sizes it): the forward's work list plus two staging tensors of
+ * (num_page_ids * page_size + total_q + 128) rows into which one gather pass packs the keys and values; the
+ * attention itself is then the jagged forward in its delta form on the same kernels.  batch <= 65535. */
+typedef struct HstuPagedArgs {
+  uint32_t struct_bytes;  /* sizeof(HstuPagedArgs) */
+  int32_t page_size;
+  HstuJaggedArgs base;
+  const void* kv_cache;
+  const void* page_offsets;
+  const void* page_ids;
+  const void* last_page_len;
+  const void* seq_offset_t;
+  int64_t num_pages;
+  int64_t num_page_ids;
+} HstuPagedArgs;
+HSTU_API int hstu_paged_fwd_get_workspace_size(const HstuPagedArgs* args, uint64_t* workspace_bytes);
+HSTU_API int hstu_paged_fwd(const HstuPagedArgs* args, void* workspace, uint64_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------------------- backward
  * Replaces the aclnnHstuJaggedBackward call of the reference adapter

@@ -18,7 +18,7 @@ ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libhstu_b200.so")
 SHIM = os.path.join(PKG, "_torch_shim.so")
 
-CUDA_SOURCES = ["hstu_api.cu", "hstu_sched.cu", "hstu_generic.cu", "hstu_tc.cu", "hstu_static.cu", "hstu_bwd_generic.cu", "hstu_bwd_tc.cu", "ln_mul.cu", "in_linear_silu.cu"]
+CUDA_SOURCES = ["hstu_api.cu", "hstu_sched.cu", "hstu_generic.cu", "hstu_tc.cu", "hstu_static.cu", "hstu_paged.cu", "hstu_bwd_generic.cu", "hstu_bwd_tc.cu", "ln_mul.cu", "in_linear_silu.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -18,13 +18,14 @@ LIB_PATH = os.path.join(_PKG, "libhstu_b200.so")
 DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2
 MASK_TRIL, MASK_TRIU, MASK_NONE, MASK_CUSTOM = 0, 1, 2, 3
 FLAG_DETERMINISTIC, FLAG_ALPHA_BEFORE_BIAS, FLAG_FORCE_GENERIC = 1, 2, 4
-ST_BAD_OFFSETS, ST_LEN_GT_MAX, ST_BAD_CTX_TARGET, ST_PIPE_TIMEOUT = 1, 2, 4, 256
+ST_BAD_OFFSETS, ST_LEN_GT_MAX, ST_BAD_CTX_TARGET, ST_BAD_PAGES, ST_PIPE_TIMEOUT = 1, 2, 4, 8, 256
 
 EXPORTS = (
     "hstu_jagged_fwd_get_workspace_size", "hstu_jagged_fwd", "hstu_jagged_fwd_status",
     "hstu_jagged_fwd_kernel_kind", "hstu_plan_host", "hstu_debug_mask_host", "hstu_debug_tiles_host",
     "hstu_last_error", "hstu_b200_version", "hstu_jagged_fwd_static", "hstu_jagged_fwd_static_status",
     "hstu_jagged_bwd_get_workspace_size", "hstu_jagged_bwd", "ops_rec_ln_mul_f32", "ops_rec_in_linear_silu_fwd",
+    "hstu_paged_fwd_get_workspace_size", "hstu_paged_fwd",
 )
 STATIC_SCRATCH_BYTES = 1 << 20
 E_SCRATCH_LIMIT = -6
@@ -42,6 +43,15 @@ class HstuJaggedArgs(C.Structure):
         ("mask_type", C.c_int32), ("max_seq_len_q", C.c_int32), ("max_seq_len_k", C.c_int32),
         ("target_group_size", C.c_int32), ("silu_scale", C.c_float), ("alpha", C.c_float),
         ("flags", C.c_uint32), ("reserved", C.c_uint32),
+    ]
+
+
+class HstuPagedArgs(C.Structure):
+    _fields_ = [
+        ("struct_bytes", C.c_uint32), ("page_size", C.c_int32), ("base", HstuJaggedArgs),
+        ("kv_cache", C.c_void_p), ("page_offsets", C.c_void_p), ("page_ids", C.c_void_p),
+        ("last_page_len", C.c_void_p), ("seq_offset_t", C.c_void_p), ("num_pages", C.c_int64),
+        ("num_page_ids", C.c_int64),
     ]
 
 
@@ -108,6 +118,11 @@ def load():
     lib.hstu_jagged_bwd_get_workspace_size.restype = C.c_int
     lib.hstu_jagged_bwd.argtypes = [B, C.c_void_p, C.c_uint64, C.c_void_p]
     lib.hstu_jagged_bwd.restype = C.c_int
+    P = C.POINTER(HstuPagedArgs)
+    lib.hstu_paged_fwd_get_workspace_size.argtypes = [P, C.POINTER(C.c_uint64)]
+    lib.hstu_paged_fwd_get_workspace_size.restype = C.c_int
+    lib.hstu_paged_fwd.argtypes = [P, C.c_void_p, C.c_uint64, C.c_void_p]
+    lib.hstu_paged_fwd.restype = C.c_int
     lib.ops_rec_ln_mul_f32.argtypes = [C.c_void_p] * 5 + [C.c_int64, C.c_int64, C.c_void_p]
     lib.ops_rec_ln_mul_f32.restype = C.c_int
     lib.ops_rec_in_linear_silu_fwd.argtypes = [C.POINTER(OpsRecInLinearSiluArgs), C.c_void_p]
@@ -261,6 +276,53 @@ def hstu_jagged_backward(grad, q, k, v, mask=None, attn_bias=None, mask_type=0, 
             return (dq, dk, dv, dbias), st.value
     del keep
     return dq, dk, dv, dbias
+
+
+def hstu_paged_forward(q, k, v, kv_cache, mask=None, attn_bias=None, mask_type=0, max_seq_len=0, max_seq_len_k=0,
+                       silu_scale=0.0, seq_offset=None, seq_offset_k=None, seq_offset_t=None, page_offsets=None,
+                       page_ids=None, last_page_len=None, num_target=None, target_group_size=0, alpha=1.0, *,
+                       flags=0, return_status=False):
+    """ops_rec::hstu_paged through hstu_paged_fwd on CUDA tensors (argument order of the reference schema,
+    hstu_v1/torch_extension/hstu_paged_plugin.cpp:75-98).  The page-table tensors are converted to seq_offset's
+    integer type like the reference adapter does (:33-35)."""
+    import torch
+    if q.dim() != 3:
+        raise HstuError(-2, "The q should be 3D in jagged layout")
+    if not q.is_cuda:
+        raise HstuError(-2, "tensors must live on a CUDA device; there is no CPU implementation")
+    q, k, v, kv_cache = q.contiguous(), k.contiguous(), v.contiguous(), kv_cache.contiguous()
+    it = seq_offset.dtype
+    conv = [t.to(it).contiguous() for t in (seq_offset_k, page_offsets, page_ids, last_page_len)]
+    seq_offset_k, page_offsets, page_ids, last_page_len = conv
+    for name, t in (("kv_cache", kv_cache), ("page_offsets", page_offsets), ("page_ids", page_ids),
+                    ("last_page_len", last_page_len)):
+        if t.device != q.device:
+            raise ValueError(f"{name} is on {t.device} but q is on {q.device}")
+    out = torch.empty(q.shape[0], q.shape[1], v.shape[2], dtype=q.dtype, device=q.device)
+    base, keep = make_args(q, k, v, out, seq_offset, seq_offset_k=seq_offset_k, mask=mask, attn_bias=attn_bias,
+                           mask_type=mask_type, max_seq_len=max_seq_len, max_seq_len_k=max_seq_len_k or None,
+                           silu_scale=silu_scale, num_target=num_target, target_group_size=target_group_size,
+                           alpha=alpha, flags=flags)
+    a = HstuPagedArgs()
+    a.struct_bytes = C.sizeof(HstuPagedArgs)
+    a.page_size = kv_cache.shape[2]
+    a.base = base
+    a.kv_cache, a.page_offsets, a.page_ids = kv_cache.data_ptr(), page_offsets.data_ptr(), page_ids.data_ptr()
+    a.last_page_len = last_page_len.data_ptr()
+    a.seq_offset_t = seq_offset_t.data_ptr() if seq_offset_t is not None else None
+    a.num_pages, a.num_page_ids = kv_cache.shape[0], page_ids.numel()
+    n = C.c_uint64(0)
+    check(load().hstu_paged_fwd_get_workspace_size(C.byref(a), C.byref(n)))
+    ws = torch.empty(n.value, dtype=torch.uint8, device=q.device)
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+        check(load().hstu_paged_fwd(C.byref(a), ws.data_ptr(), n.value, stream))
+        if return_status:
+            st = C.c_uint32(0)
+            check(load().hstu_jagged_fwd_status(ws.data_ptr(), stream, C.byref(st)))
+            return out, st.value
+    del keep, conv
+    return out
 
 
 def in_linear_silu(x, weight, bias, split):

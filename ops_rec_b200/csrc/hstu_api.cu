@@ -24,6 +24,9 @@ cudaError_t launch_ln_mul(const float* x, const float* u, const float* gamma, co
                           long long rows, int cols, float eps, int num_sms, cudaStream_t stream);
 cudaError_t launch_in_linear_silu(const LinSiluParams& p, const void* x, const void* weight, int dtype,
                                   cudaStream_t stream);
+cudaError_t launch_paged_gather(const KParams& p, const void* kv_cache, const void* k_in, const void* v_in,
+                                void* k_out, void* v_out, long long capacity, long long num_pages,
+                                long long num_page_ids, int esize, cudaStream_t stream);
 }  // namespace hstu
 
 namespace {
@@ -182,8 +185,17 @@ int hstu_jagged_fwd_kernel_kind(const HstuJaggedArgs* args) {
   return wants_tc(args, p) ? 1 : 0;
 }
 
+// `paged` (hstu_paged only): parameters that carry the page table, for the pre-pass's consistency check.
+static int jagged_fwd_impl(const HstuJaggedArgs* args, void* workspace, uint64_t workspace_bytes, void* stream_v,
+                           const hstu::KParams* paged);
+
 int hstu_jagged_fwd(const HstuJaggedArgs* args, void* workspace, uint64_t workspace_bytes, void* stream_v) {
   g_err[0] = 0;
+  return jagged_fwd_impl(args, workspace, workspace_bytes, stream_v, nullptr);
+}
+
+static int jagged_fwd_impl(const HstuJaggedArgs* args, void* workspace, uint64_t workspace_bytes, void* stream_v,
+                           const hstu::KParams* paged) {
   int rc = validate(args);
   if (rc) return rc;
   rc = validate_pointers(args);
@@ -203,6 +215,14 @@ int hstu_jagged_fwd(const HstuJaggedArgs* args, void* workspace, uint64_t worksp
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   hstu::KParams p = to_params(args, workspace, need);
+  if (paged) {
+    p.page_offsets = paged->page_offsets;
+    p.page_ids = paged->page_ids;
+    p.last_page_len = paged->last_page_len;
+    p.page_size = paged->page_size;
+    p.num_pages = paged->num_pages;
+    p.num_page_ids = paged->num_page_ids;
+  }
   const bool tc = wants_tc(args, p);
   cudaError_t e = hstu::launch_prepass(p, tc, stream);
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "pre-pass launch: %s", cudaGetErrorString(e));
@@ -215,6 +235,97 @@ int hstu_jagged_fwd(const HstuJaggedArgs* args, void* workspace, uint64_t worksp
   }
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "kernel launch: %s", cudaGetErrorString(e));
   return HSTU_OK;
+}
+
+// --------------------------------------------------------------------------------------------------- paged
+namespace {
+struct PagedPlan {
+  HstuJaggedArgs fwd;        // the jagged call on the staging tensors
+  uint64_t fwd_bytes;        // its workspace
+  uint64_t stage_bytes;      // one staging tensor (256-byte multiple)
+  long long capacity;        // rows of a staging tensor
+  int esize;
+};
+
+int plan_paged(const HstuPagedArgs* a, PagedPlan* pl) {
+  if (!a) return fail(HSTU_E_NULL, "args is null");
+  if (a->struct_bytes != sizeof(HstuPagedArgs))
+    return fail(HSTU_E_PARAM, "struct_bytes is %u, this library expects %zu", a->struct_bytes, sizeof(HstuPagedArgs));
+  int rc = validate(&a->base);
+  if (rc) return rc;
+  if (a->base.dim_qk != a->base.dim_v)
+    return fail(HSTU_E_PARAM, "hstu_paged: keys and values share the cache layout, dim_qk (%d) must equal dim_v (%d)",
+                a->base.dim_qk, a->base.dim_v);
+  if (a->page_size < 1) return fail(HSTU_E_PARAM, "hstu_paged: page_size must be positive, but value is %d", a->page_size);
+  if (a->num_pages < 1 || a->num_page_ids < 1) return fail(HSTU_E_PARAM, "kv_cache / page_ids must not be empty");
+  if (a->base.batch > 65535) return fail(HSTU_E_PARAM, "hstu_paged: batch expect in [1, 65535], but value is %d", a->base.batch);
+  if (a->base.num_context) return fail(HSTU_E_PARAM, "hstu_paged takes no num_context");
+  if (a->base.num_target && a->base.target_group_size <= 0)
+    return fail(HSTU_E_PARAM, "targetGroupSize must be greater than 0 when numTarget is defined");
+  const __int128 cap = static_cast<__int128>(a->num_page_ids) * a->page_size + a->base.total_q + hstu::kTileN;
+  if (cap > 0x7fffff00ll) return fail(HSTU_E_PARAM, "hstu_paged: page table too large (%lld page slots of %d rows)",
+                                      (long long)a->num_page_ids, a->page_size);
+  pl->capacity = static_cast<long long>(cap);
+  pl->esize = a->base.dtype == HSTU_DTYPE_FP32 ? 4 : 2;
+  pl->stage_bytes = (static_cast<uint64_t>(pl->capacity) * a->base.heads_k * a->base.dim_qk * pl->esize + 255) &
+                    ~static_cast<uint64_t>(255);
+  pl->fwd = a->base;
+  pl->fwd.total_k = pl->capacity;
+  pl->fwd.num_context = nullptr;
+  // k / v are filled in by the caller of this plan once the workspace is known; a 256-byte aligned stand-in keeps
+  // the kernel choice (which looks at alignment) the same in both phases
+  pl->fwd.k = pl->fwd.v = reinterpret_cast<const void*>(static_cast<uintptr_t>(256));
+  if (!pl->fwd.out) pl->fwd.out = reinterpret_cast<void*>(static_cast<uintptr_t>(256));
+  if (!pl->fwd.q) pl->fwd.q = reinterpret_cast<const void*>(static_cast<uintptr_t>(256));
+  return hstu_jagged_fwd_get_workspace_size(&pl->fwd, &pl->fwd_bytes);
+}
+}  // namespace
+
+int hstu_paged_fwd_get_workspace_size(const HstuPagedArgs* args, uint64_t* workspace_bytes) {
+  g_err[0] = 0;
+  if (!workspace_bytes) return fail(HSTU_E_NULL, "workspace_bytes is null");
+  PagedPlan pl;
+  int rc = plan_paged(args, &pl);
+  if (rc) return rc;
+  *workspace_bytes = pl.fwd_bytes + 2 * pl.stage_bytes;
+  return HSTU_OK;
+}
+
+int hstu_paged_fwd(const HstuPagedArgs* args, void* workspace, uint64_t workspace_bytes, void* stream_v) {
+  g_err[0] = 0;
+  PagedPlan pl;
+  int rc = plan_paged(args, &pl);
+  if (rc) return rc;
+  const HstuJaggedArgs* b = &args->base;
+  if (!b->seq_offset_q || !b->seq_offset_k) return fail(HSTU_E_NULL, "seq_offset / seq_offset_k is null");
+  if (!args->kv_cache || !args->page_offsets || !args->page_ids || !args->last_page_len)
+    return fail(HSTU_E_NULL, "kv_cache / page_offsets / page_ids / last_page_len is null");
+  if (b->total_q > 0 && (!b->q || !b->out || !b->k || !b->v)) return fail(HSTU_E_NULL, "q / k / v / out is null");
+  const uint64_t need = pl.fwd_bytes + 2 * pl.stage_bytes;
+  if (!workspace) return fail(HSTU_E_WORKSPACE, "workspace is null (%llu bytes needed)", (unsigned long long)need);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(HSTU_E_WORKSPACE, "workspace must be 256-byte aligned");
+  if (workspace_bytes < need)
+    return fail(HSTU_E_WORKSPACE, "workspace has %llu bytes, %llu needed", (unsigned long long)workspace_bytes,
+                (unsigned long long)need);
+  char* base = static_cast<char*>(workspace);
+  void* k_stage = base + pl.fwd_bytes;
+  void* v_stage = base + pl.fwd_bytes + pl.stage_bytes;
+  pl.fwd.q = b->q;
+  pl.fwd.out = b->out;
+  pl.fwd.k = k_stage;
+  pl.fwd.v = v_stage;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  hstu::KParams p = to_params(&pl.fwd, nullptr, 0);
+  p.page_offsets = args->page_offsets;
+  p.page_ids = args->page_ids;
+  p.last_page_len = args->last_page_len;
+  p.page_size = args->page_size;
+  p.num_pages = args->num_pages;
+  p.num_page_ids = args->num_page_ids;
+  const cudaError_t e = hstu::launch_paged_gather(p, args->kv_cache, b->k, b->v, k_stage, v_stage, pl.capacity,
+                                                  args->num_pages, args->num_page_ids, pl.esize, stream);
+  if (e != cudaSuccess) return fail(HSTU_E_CUDA, "gather launch: %s", cudaGetErrorString(e));
+  return jagged_fwd_impl(&pl.fwd, workspace, pl.fwd_bytes, stream_v, &p);
 }
 
 // ------------------------------------------------------------------------------------------------ backward

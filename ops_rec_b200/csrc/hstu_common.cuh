@@ -54,6 +54,13 @@ struct KParams {
   uint32_t* ws_header;  // status, item count, counter
   uint32_t* items;      // work list
   long long item_capacity;
+  // hstu_paged only (null / 0 otherwise): the page table the keys / values were gathered from, for the pre-pass's
+  // consistency check
+  const void* page_offsets;   // [batch + 1]
+  const void* page_ids;       // [num_page_ids]
+  const void* last_page_len;  // [batch]
+  long long num_pages, num_page_ids;
+  int page_size;
 };
 
 // Backward call: the forward's parameters plus the gradient tensors.
@@ -126,6 +133,27 @@ HSTU_HD unsigned check_seq(const KParams& p, int b) {
   long long t = p.tgt ? load_index(p.tgt, p.index_bytes, b) : 0;
   if (c < 0 || t < 0 || c + t > q1 - q0 || t > k1 - k0) st |= HSTU_ST_BAD_CTX_TARGET;
   return st;
+}
+
+// hstu_paged: the page table of sequence b must describe exactly the cached part of its keys,
+// (pages - 1) * page_size + last_page_len == len_k - num_target, with page ids inside the cache
+// (the reference golden asserts the former, hstu_forward_v1/test/pytest/common.py:286).
+HSTU_HD unsigned check_pages(const KParams& p, int b) {
+  if (!p.page_offsets) return 0;
+  const long long pg0 = load_index(p.page_offsets, p.index_bytes, b), pg1 = load_index(p.page_offsets, p.index_bytes, b + 1);
+  if (pg0 < 0 || pg1 < pg0 || pg1 > p.num_page_ids) return HSTU_ST_BAD_PAGES;
+  const long long last = p.last_page_len ? load_index(p.last_page_len, p.index_bytes, b) : p.page_size;
+  const long long k0 = load_index(p.offk, p.index_bytes, b), k1 = load_index(p.offk, p.index_bytes, b + 1);
+  long long t = p.tgt ? load_index(p.tgt, p.index_bytes, b) : 0;
+  if (t < 0) t = 0;
+  const long long pages = pg1 - pg0;
+  const long long cached = pages > 0 ? (pages - 1) * p.page_size + last : 0;
+  if (last < 0 || last > p.page_size || (pages > 0 && last == 0) || cached != (k1 - k0) - t) return HSTU_ST_BAD_PAGES;
+  for (long long s = pg0; s < pg1; ++s) {
+    const long long pid = load_index(p.page_ids, p.index_bytes, s);
+    if (pid < 0 || pid >= p.num_pages) return HSTU_ST_BAD_PAGES;
+  }
+  return 0;
 }
 
 // Visibility of row i as column bounds:  allowed(j)  <=>  j < lim1  ||  (lo2 <= j && j <= hi2).

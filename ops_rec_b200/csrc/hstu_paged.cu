@@ -1,0 +1,149 @@
+// hstu_paged: the key / value gather that turns a paged KV cache plus the new target rows into the packed
+// [tokens, heads, dim] layout the attention kernels read.
+//
+// The reference operator (ascendc/attention/hstu_v1/torch_extension/hstu_paged_plugin.cpp:21-72; kernel
+// .../hstu_forward_v1/op_kernel/atlas950/hstu_paged_forward_kernel.h, FetchKvMayFromCache) attends, per sequence,
+// over   K/V = [ page 0 | page 1 | ... | last page cut to last_page_len ]  ++  [ the target rows of the input k / v ]
+// where the pages are kv_cache[page_ids[page_offsets[b] .. page_offsets[b + 1])] and the target rows are the last
+// num_target[b] rows of the sequence's segment of the input k / v (the history rows of the input are not used).
+// Here one HBM-bound pass writes exactly that into two staging tensors inside the caller's workspace, after which the
+// call is an ordinary jagged forward in its `.delta` form (len_q = new history + targets <= len_k = cache + targets)
+// on the same tcgen05 / generic kernels, scheduler and mask algebra.  A page of the cache is contiguous
+// [page_size, heads, dim], so every page is one straight copy of page_size * heads * dim elements.
+//
+// Inconsistent page tables are flagged by the scheduling pre-pass (HSTU_ST_BAD_PAGES); this pass only makes them
+// harmless: a row whose source does not exist (a page slot outside the sequence's range, a page id outside the cache)
+// becomes zeros, and nothing outside the tensors is ever addressed.
+#include "hstu_common.cuh"
+
+namespace hstu {
+
+namespace {
+
+constexpr int kGatherThreads = 256;
+constexpr int kGatherRowsPerWarp = 4;   // consecutive staging rows per warp (mostly of one sequence: one look-up)
+
+struct GatherParams {
+  const unsigned char* cache;   // [pages, 2, page_size, heads_k, dim]
+  const unsigned char* k_in;    // [total_q, heads_k, dim]
+  const unsigned char* v_in;
+  unsigned char* k_out;         // [capacity, heads_k, dim]
+  unsigned char* v_out;
+  const void* offq;
+  const void* offk;
+  const void* tgt;
+  const void* page_offsets;
+  const void* page_ids;
+  long long total_q, capacity, num_pages, num_page_ids;
+  int index_bytes, batch, page_size;
+  int row_bytes;                // heads_k * dim * element size
+};
+
+template <typename V>
+__device__ __forceinline__ void copy_row(unsigned char* dst, const unsigned char* src, int row_bytes, int lane) {
+  for (int i = lane * static_cast<int>(sizeof(V)); i < row_bytes; i += 32 * static_cast<int>(sizeof(V)))
+    *reinterpret_cast<V*>(dst + i) = src ? *reinterpret_cast<const V*>(src + i) : V{};
+}
+
+// One warp per kGatherRowsPerWarp consecutive rows of the staging tensors (grid.y = 0: keys, 1: values).  The warp
+// finds the sequence of a row by bisection over seq_offset_k; rows behind the last sequence are zeros for one K/V
+// tile's worth (a tile that runs past the end of the data multiplies those rows by P = 0, which must not meet the
+// NaN bit patterns uninitialised memory may hold), the rest of the capacity is never read.
+template <typename V>
+__global__ void __launch_bounds__(kGatherThreads) hstu_paged_gather_kernel(const GatherParams p) {
+  const bool is_v = blockIdx.y != 0;
+  unsigned char* out = is_v ? p.v_out : p.k_out;
+  const unsigned char* in = is_v ? p.v_in : p.k_in;
+  const int lane = threadIdx.x & 31;
+  const long long first = (static_cast<long long>(blockIdx.x) * (kGatherThreads / 32) + (threadIdx.x >> 5)) *
+                          kGatherRowsPerWarp;
+  long long k_end = load_index(p.offk, p.index_bytes, p.batch);
+  if (k_end < 0) k_end = 0;
+  if (k_end > p.capacity) k_end = p.capacity;
+  const long long page_bytes = static_cast<long long>(p.page_size) * p.row_bytes;
+  int b = -1;
+  long long k0 = 0, k1 = -1, q1 = 0, t = 0, pg0 = 0, pg1 = 0;
+  for (long long row = first; row < first + kGatherRowsPerWarp && row < p.capacity; ++row) {
+    if (row >= k_end) {
+      if (row < k_end + kTileN) copy_row<V>(out + row * p.row_bytes, nullptr, p.row_bytes, lane);
+      continue;
+    }
+    if (row >= k1) {
+      // the last sequence whose first row is <= row (sequences of length 0 share their offset with the next one)
+      int lo = b < 0 ? 0 : b, hi = p.batch - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (load_index(p.offk, p.index_bytes, mid) <= row) lo = mid; else hi = mid - 1;
+      }
+      b = lo;
+      k0 = load_index(p.offk, p.index_bytes, b);
+      k1 = load_index(p.offk, p.index_bytes, b + 1);
+      const long long q0 = load_index(p.offq, p.index_bytes, b);
+      q1 = load_index(p.offq, p.index_bytes, b + 1);
+      if (q1 > p.total_q) q1 = p.total_q;
+      t = p.tgt ? load_index(p.tgt, p.index_bytes, b) : 0;
+      if (t < 0) t = 0;
+      if (t > q1 - q0) t = q1 - q0 > 0 ? q1 - q0 : 0;
+      pg0 = load_index(p.page_offsets, p.index_bytes, b);
+      pg1 = load_index(p.page_offsets, p.index_bytes, b + 1);
+      if (pg0 < 0) pg0 = 0;
+      if (pg1 > p.num_page_ids) pg1 = p.num_page_ids;
+    }
+    if (row < k0 || row >= k1) continue;   // offsets that are not monotone (flagged by the pre-pass): nothing to copy
+    const long long r = row - k0, cache_len = (k1 - k0) - t;
+    const unsigned char* src = nullptr;    // null: zeros (an inconsistent table has no source for this row)
+    if (r < cache_len) {
+      const long long slot = pg0 + r / p.page_size;
+      if (slot < pg1) {
+        const long long pid = load_index(p.page_ids, p.index_bytes, slot);
+        if (pid >= 0 && pid < p.num_pages)
+          src = p.cache + (pid * 2 + (is_v ? 1 : 0)) * page_bytes + (r % p.page_size) * p.row_bytes;
+      }
+    } else {
+      const long long at = q1 - t + (r - cache_len);
+      if (at >= 0 && at < p.total_q) src = in + at * p.row_bytes;
+    }
+    copy_row<V>(out + row * p.row_bytes, src, p.row_bytes, lane);
+  }
+}
+
+}  // namespace
+
+// Enqueues the gather.  All pointers are device pointers; capacity = rows of each staging tensor.
+cudaError_t launch_paged_gather(const KParams& p, const void* kv_cache, const void* k_in, const void* v_in,
+                                void* k_out, void* v_out, long long capacity, long long num_pages,
+                                long long num_page_ids, int esize, cudaStream_t stream) {
+  GatherParams g;
+  g.cache = static_cast<const unsigned char*>(kv_cache);
+  g.k_in = static_cast<const unsigned char*>(k_in);
+  g.v_in = static_cast<const unsigned char*>(v_in);
+  g.k_out = static_cast<unsigned char*>(k_out);
+  g.v_out = static_cast<unsigned char*>(v_out);
+  g.offq = p.offq;
+  g.offk = p.offk;
+  g.tgt = p.tgt;
+  g.page_offsets = p.page_offsets;
+  g.page_ids = p.page_ids;
+  g.total_q = p.total_q;
+  g.capacity = capacity;
+  g.num_pages = num_pages;
+  g.num_page_ids = num_page_ids;
+  g.index_bytes = p.index_bytes;
+  g.batch = p.batch;
+  g.page_size = p.page_size;
+  g.row_bytes = p.hk * p.dqk * esize;
+  const long long rows_per_cta = static_cast<long long>(kGatherThreads / 32) * kGatherRowsPerWarp;
+  const dim3 grid(static_cast<unsigned>((capacity + rows_per_cta - 1) / rows_per_cta), 2, 1);
+  const uintptr_t align = reinterpret_cast<uintptr_t>(kv_cache) | reinterpret_cast<uintptr_t>(k_in) |
+                          reinterpret_cast<uintptr_t>(v_in) | reinterpret_cast<uintptr_t>(k_out) |
+                          reinterpret_cast<uintptr_t>(v_out) | static_cast<uintptr_t>(g.row_bytes);
+  if ((align & 15u) == 0)
+    hstu_paged_gather_kernel<uint4><<<grid, kGatherThreads, 0, stream>>>(g);
+  else if ((align & 3u) == 0)
+    hstu_paged_gather_kernel<uint32_t><<<grid, kGatherThreads, 0, stream>>>(g);
+  else
+    hstu_paged_gather_kernel<uint16_t><<<grid, kGatherThreads, 0, stream>>>(g);
+  return cudaGetLastError();
+}
+
+}  // namespace hstu

@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
 
   unsigned st = 0;
   for (int b = tid; b < p.batch; b += kPreThreads) {
-    st |= check_seq(p, b);
+    st |= check_seq(p, b) | check_pages(p, b);
     if (build_items) {
       const SeqInfo s = load_seq(p, b);
       atomicAdd(&s_count[pairs_of(s.lq)], 1u);
@@ -120,7 +120,7 @@ cudaError_t launch_prepass(const KParams& p, bool build_items, cudaStream_t stre
 long long plan_host(const KParams& p, uint32_t* items, long long capacity, uint32_t* status) {
   unsigned st = 0;
   long long n = 0;
-  for (int b = 0; b < p.batch; ++b) st |= check_seq(p, b);
+  for (int b = 0; b < p.batch; ++b) st |= check_seq(p, b) | check_pages(p, b);
   for (int key = kMaxPairs; key >= 1; --key) {
     for (int b = 0; b < p.batch; ++b) {
       const SeqInfo s = load_seq(p, b);

@@ -407,6 +407,73 @@ at::Tensor hstu_dense_meta(const at::Tensor& q, const at::Tensor&, const at::Ten
   return at::empty_like(q, q.options().device(c10::kMeta));
 }
 
+// hstu_paged (ascendc/attention/hstu_v1/torch_extension/hstu_paged_plugin.cpp:21-72): the same checks and
+// conversions - kv_cache / page_ids / last_page_len not empty, the page table and seq_offset_k / seq_offset_t
+// converted to seq_offset's integer type, q 3-D, offsets of at least two entries, targetGroupSize > 0 with numTarget,
+// silu_scale 0 -> 1 / max_seq_len, alpha None -> 1, no num_context (the reference passes zeros).
+at::Tensor hstu_paged(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& kv_cache,
+                      const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& attn_bias,
+                      int64_t mask_type, int64_t max_seq_len, int64_t max_seq_len_k, double silu_scale,
+                      const at::Tensor& seq_offset, const at::Tensor& seq_offset_k, const at::Tensor& seq_offset_t,
+                      const at::Tensor& page_offsets, const at::Tensor& page_ids, const at::Tensor& last_page_len,
+                      const at::Tensor& num_target, int64_t target_group_size, c10::optional<double> alpha,
+                      bool deterministic) {
+  TORCH_CHECK(kv_cache.defined() && kv_cache.numel() > 0, "kv_cache is empty");
+  TORCH_CHECK(page_ids.defined() && page_ids.numel() > 0, "page_ids is empty");
+  TORCH_CHECK(last_page_len.defined() && last_page_len.numel() > 0, "last_page_len is empty");
+  TORCH_CHECK(q.dim() == 3, "The q should be 3D in jagged layout");
+  TORCH_CHECK(seq_offset.defined() && seq_offset_k.defined() && page_offsets.defined(),
+              "seq_offset, seq_offset_k and page_offsets are required");
+  TORCH_CHECK(seq_offset_t.defined() ? seq_offset_t.size(0) >= 2 : true,
+              "acSeqOffsetT params error should have at least two element.");
+  TORCH_CHECK(!num_target.defined() || target_group_size > 0,
+              "targetGroupSize must be greater than 0 when numTarget is defined");
+  TORCH_CHECK(kv_cache.dim() == 5 && kv_cache.size(1) == 2 && kv_cache.size(3) == k.size(1) &&
+                  kv_cache.size(4) == k.size(2) && kv_cache.scalar_type() == q.scalar_type(),
+              "kv_cache must be [pages, 2, page_size, heads_k, dim] in q's dtype");
+  TORCH_CHECK(k.size(0) == q.size(0), "k and v hold the same tokens as q (only their target rows are read)");
+  c10::cuda::CUDAGuard guard(q.device());
+  c10::optional<at::Tensor> tgt = num_target.defined() ? c10::optional<at::Tensor>(num_target) : c10::nullopt;
+  Prepared pr = prepare(q, k, v, mask, attn_bias, mask_type, max_seq_len, max_seq_len_k, silu_scale, seq_offset,
+                        seq_offset_k, c10::nullopt, tgt, target_group_size, alpha, deterministic);
+  for (const auto* t : {&kv_cache, &page_offsets, &page_ids, &last_page_len}) check_same_device(*t, q, "a page-table tensor");
+  const auto it = pr.off_q.scalar_type();
+  auto cache = kv_cache.contiguous();
+  auto po = page_offsets.to(it).contiguous(), pi = page_ids.to(it).contiguous(), ll = last_page_len.to(it).contiguous();
+  TORCH_CHECK(po.numel() == pr.off_q.numel(), "page_offsets must have batch + 1 entries");
+  TORCH_CHECK(ll.numel() >= pr.off_q.numel() - 1, "last_page_len is shorter than the batch");
+  HstuPagedArgs a;
+  memset(&a, 0, sizeof(a));
+  a.struct_bytes = sizeof(a);
+  a.page_size = static_cast<int32_t>(cache.size(2));
+  a.base = pr.a;
+  auto out = at::empty({pr.q.size(0), pr.q.size(1), pr.v.size(2)}, pr.q.options());
+  a.base.out = out.data_ptr();
+  a.kv_cache = cache.data_ptr();
+  a.page_offsets = po.data_ptr();
+  a.page_ids = pi.data_ptr();
+  a.last_page_len = ll.data_ptr();
+  a.num_pages = cache.size(0);
+  a.num_page_ids = pi.numel();
+  uint64_t ws_bytes = 0;
+  int rc = hstu_paged_fwd_get_workspace_size(&a, &ws_bytes);
+  TORCH_CHECK(rc == 0, "hstu_paged: ", hstu_last_error());
+  auto ws = at::empty({static_cast<int64_t>(ws_bytes)}, pr.q.options().dtype(at::kByte));
+  rc = hstu_paged_fwd(&a, ws.data_ptr(), ws_bytes, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "hstu_paged: ", hstu_last_error());
+  return out;
+}
+
+// (hstu_paged_plugin.cpp:107-118)
+at::Tensor hstu_paged_meta(const at::Tensor& q, const at::Tensor&, const at::Tensor&, const at::Tensor&,
+                           const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&, int64_t, int64_t,
+                           int64_t, double, const at::Tensor&, const at::Tensor&, const at::Tensor&,
+                           const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&, int64_t,
+                           c10::optional<double>, bool) {
+  TORCH_CHECK(q.dim() == 3, "The q should be 3D in jagged layout");
+  return at::empty_like(q, q.options().device(c10::kMeta));
+}
+
 at::Tensor meta_out(const at::Tensor& q, const at::Tensor& v) {
   TORCH_CHECK(q.dim() == 3, "The q should be 3D in jagged layout");
   std::vector<c10::SymInt> shape = {q.sym_size(0), q.sym_size(1), v.sym_size(2)};
@@ -452,6 +519,12 @@ TORCH_LIBRARY_FRAGMENT(ops_rec, m) {
         "(Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("hstu_dense(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
         "int max_seq_len=0, float silu_scale=0.0) -> Tensor");
+  // hstu_paged_plugin.cpp:75-98
+  m.def("hstu_paged(Tensor q, Tensor k, Tensor v, Tensor kv_cache=None, Tensor? mask=None, Tensor? attn_bias=None,"
+        " int mask_type=0, int max_seq_len=0, int max_seq_len_k=0, float silu_scale=0.0, Tensor seq_offset=None,"
+        " Tensor seq_offset_k=None, Tensor seq_offset_t=None, Tensor page_offsets=None, Tensor page_ids=None,"
+        " Tensor last_page_len=None, Tensor num_target=None, int target_group_size=0, float? alpha=1.0,"
+        " bool deterministic=False) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(ops_rec, CUDA, m) {
@@ -462,6 +535,7 @@ TORCH_LIBRARY_IMPL(ops_rec, CUDA, m) {
   m.impl("ln_mul", TORCH_FN(ln_mul));
   m.impl("distance_in_linear_silu", TORCH_FN(in_linear_silu_fwd));
   m.impl("hstu_dense", TORCH_FN(hstu_dense));
+  m.impl("hstu_paged", TORCH_FN(hstu_paged));
 }
 
 TORCH_LIBRARY_IMPL(ops_rec, Meta, m) {
@@ -472,4 +546,5 @@ TORCH_LIBRARY_IMPL(ops_rec, Meta, m) {
   m.impl("ln_mul", TORCH_FN(ln_mul_meta));
   m.impl("distance_in_linear_silu", TORCH_FN(in_linear_silu_fwd_meta));
   m.impl("hstu_dense", TORCH_FN(hstu_dense_meta));
+  m.impl("hstu_paged", TORCH_FN(hstu_paged_meta));
 }

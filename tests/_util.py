@@ -27,7 +27,7 @@ def load_fixture(name):
 
 def fixture_names():
     names = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
-    return [n for n in names if n != "mask_grid" and not n.startswith(("dense_", "bwd_", "lnmul_", "linsilu_"))]
+    return [n for n in names if n != "mask_grid" and not n.startswith(("dense_", "bwd_", "lnmul_", "linsilu_", "paged_"))]
 
 
 def bwd_fixture_names():

@@ -321,10 +321,94 @@ def main_in_linear_silu(ref_root):
         print(f"{os.path.basename(path):32s} {os.path.getsize(path) / 1024:8.1f} KiB")
 
 
+# name, B, heads (q, k), dim, max new history, max targets, page size, previous history in the cache, dtype, mask
+PAGED_CASES = [
+    dict(name="paged_fp32_p32", B=3, Hq=2, Hk=2, D=32, hist=100, cand=25, page=32, prev=False, dtype="fp32", mask_type=0),
+    dict(name="paged_fp32_p128_prev", B=4, Hq=4, Hk=2, D=32, hist=200, cand=25, page=128, prev=True, dtype="fp32",
+         mask_type=0),
+    dict(name="paged_fp32_nocand", B=2, Hq=2, Hk=2, D=16, hist=100, cand=0, page=32, prev=True, dtype="fp32", mask_type=0),
+    dict(name="paged_fp32_custom", B=2, Hq=2, Hk=1, D=16, hist=70, cand=9, page=32, prev=False, dtype="fp32", mask_type=3),
+    dict(name="paged_bf16_p256", B=2, Hq=2, Hk=2, D=128, hist=200, cand=40, page=256, prev=True, dtype="bf16",
+         mask_type=0),
+    dict(name="paged_bf16_d64_p32", B=5, Hq=4, Hk=2, D=64, hist=200, cand=30, page=32, prev=False, dtype="bf16",
+         mask_type=0),
+]
+
+
+def main_paged(ref_root, v1c):
+    """hstu_paged fixtures.  Inputs come from the reference test's own generators and the expected outputs from its two
+    goldens: the torch golden `_hstu_paged_kv_attention` (hstu_forward_v1/test/pytest/test_hstu_paged.py:203-277; has
+    alpha, a cache longer than the new history, custom masks) for every case, and the numpy golden `get_golden_paged`
+    (test/pytest/common.py:255-300; no alpha, cache length == history) where it applies.  test_hstu_paged.py imports
+    `ops_rec` and asks `torch.npu` for a device at module / call level; both get stand-ins that run on the CPU."""
+    d = os.path.join(ref_root, "ascendc/attention/hstu_v1/hstu_forward_v1/test/pytest")
+    torch.npu = types.SimpleNamespace(config=types.SimpleNamespace(), current_device=lambda: "cpu",
+                                      synchronize=lambda: None)
+    sys.modules["common"] = v1c
+    sys.modules.setdefault("ops_rec", types.ModuleType("ops_rec"))
+    spec = importlib.util.spec_from_file_location("ref_paged_test", os.path.join(d, "test_hstu_paged.py"))
+    rp = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rp)
+    for case in PAGED_CASES:
+        torch.manual_seed(77 + len(case["name"]))
+        dtype = torch.float32 if case["dtype"] == "fp32" else torch.bfloat16
+        B, Hq, Hk, D, page = case["B"], case["Hq"], case["Hk"], case["D"], case["page"]
+        # the input recipe of paged_hstu_attn_kernel (test_hstu_paged.py:373-412), with its own helper functions
+        kv_data, new_hist, kv_len = rp.generate_kvdata_testcase(case["hist"], B, Hq, Hk, D, is_prev_hist=case["prev"])
+        kv_data = kv_data.to(dtype)
+        table, meta = rp.setup_kvcache_testcase(page, Hk, D, dtype, kv_data, kv_len, None)
+        if case["cand"] > 0:
+            cand = torch.randint(1, case["cand"] + 1, (B,), dtype=torch.int32)
+        else:
+            cand = torch.zeros((B,), dtype=torch.int32)
+        seqlen = new_hist + cand
+        off_q = rp.get_offsets_from_lengths(seqlen)
+        off_k = rp.get_offsets_from_lengths(cand + kv_len)
+        off_t = rp.get_offsets_from_lengths(cand)
+        T = int(off_q[-1])
+        q = torch.empty(T, Hq, D).uniform_(-1, 1).to(dtype)
+        k = torch.empty(T, Hk, D).uniform_(-1, 1).to(dtype)
+        v = torch.empty(T, Hk, D).uniform_(-1, 1).to(dtype)
+        max_q, max_k = int(seqlen.max()), int((cand + kv_len).max())
+        mask = rp.generate_attn_mask(B, Hq, max_q, max_k, dtype, seqlen, meta, page, cand, case["mask_type"])
+        alpha = 1.0 / (D ** 0.5)
+        page_ids = torch.tensor(meta[0], dtype=torch.int32)
+        page_off = torch.tensor(meta[1], dtype=torch.int32)
+        last_len = torch.tensor(meta[2], dtype=torch.int32)
+
+        def golden(up):
+            out = rp._hstu_paged_kv_attention(
+                num_heads_q=Hq, num_heads_k=Hk, attention_dim=D, linear_dim=D, seqlen_q=max_q, seqlen_k=max_k,
+                q=q, k=k, v=v, q_offsets=off_q, k_offsets=off_k, num_targets=cand, invalid_attn_mask=mask, upcast=up,
+                kv_cache=table, page_offsets=page_off, page_ids=page_ids, last_page_lens=last_len, alpha=alpha)
+            return out.view(-1, Hq, D)
+
+        arrays = dict(q=q, k=k, v=v, kv_cache=table, mask=mask if case["mask_type"] == 3 else None,
+                      seq_offset=off_q.to(torch.int64), seq_offset_k=off_k.to(torch.int64),
+                      seq_offset_t=off_t.to(torch.int64), page_offsets=page_off, page_ids=page_ids,
+                      last_page_len=last_len, num_target=cand.to(torch.int64), alpha=np.float64(alpha),
+                      meta=np.array([B, Hq, Hk, D, page, max_q, max_k, case["mask_type"]], dtype=np.int64),
+                      out_torch_fp32=golden(True).float())
+        if dtype != torch.float32:
+            arrays["out_torch_lowp"] = golden(False)
+        if not case["prev"] and case["mask_type"] == 0 and Hq == Hk:
+            # the numpy golden (equal head counts only): no alpha (scores enter SiLU as they are), explicit scale
+            arrays["out_numpy_noalpha"] = v1c.get_golden_paged(
+                q.float().numpy(), k.float().numpy(), v.float().numpy(), table.float().numpy(), off_q.numpy(),
+                page_off.numpy(), page_ids.numpy(), last_len.numpy(), cand.numpy(), 1.0 / max_q)
+        path = os.path.join(HERE, case["name"] + ".npz")
+        _store(path, arrays)
+        print(f"{case['name']:28s} {os.path.getsize(path) / 1024:8.1f} KiB")
+
+
 def main():
     if len(sys.argv) < 2:
-        sys.exit("usage: python tests/golden/make_golden.py <path to the ops-rec tree> [backward | ln_mul | in_linear_silu]")
+        sys.exit("usage: python tests/golden/make_golden.py <path to the ops-rec tree> [backward | ln_mul | in_linear_silu | paged]")
     ref_root = sys.argv[1]
+    if len(sys.argv) > 2 and sys.argv[2] == "paged":            # only the hstu_paged fixtures
+        v1c, _ = _load_reference(ref_root)
+        main_paged(ref_root, v1c)
+        return
     if len(sys.argv) > 2 and sys.argv[2] == "in_linear_silu":   # only the in_linear_silu fixtures
         main_in_linear_silu(ref_root)
         return
@@ -338,6 +422,7 @@ def main():
     main_backward(ref_root, v1c)
     main_ln_mul(ref_root)
     main_in_linear_silu(ref_root)
+    main_paged(ref_root, v1c)
     for case in CASES:
         arrays = build_case(case, v1c, v2b)
         path = os.path.join(HERE, case["name"] + ".npz")

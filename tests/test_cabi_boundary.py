@@ -133,7 +133,7 @@ def test_meta_dispatch_and_overload_resolution():
     out = hj(q, k, v, None, None, 0, 16, 16, 0.0, off, off)                       # .delta
     assert out.shape == (10, 4, 32)
     with pytest.raises(AttributeError, match="Available ops"):
-        ops_rec.ascendc.attention.hstu_paged
+        ops_rec.ascendc.attention.fa_infer_with_arbitrary_func
     with pytest.raises(RuntimeError, match="3D"):
         hj(q[0], k, v, None, None, 0, 16, 0.0, off)
 
