@@ -34,9 +34,9 @@ if ROOT not in sys.path:
 METRIC = "hstu_jagged_fwd_causal_tflops"
 UNIT = "TFLOP/s"
 
-# DRAM bytes (read + write) per token of one attention-kernel launch, from the ncu capture summarised in
-# profiles/hstu_tc_kernel_cfg4.md (first 24 sequences of cfg4: 613 MB for 51 883 tokens; the traffic is q/k/v/out
-# movement plus K/V re-reads and scales with the tokens a launch processes).
+# DRAM bytes (read + write) per token of one attention-kernel launch, from one ncu capture of the first 24 sequences
+# of cfg4 (613 MB for 51 883 tokens).  An estimate for the full launch, not a measurement of it: the compulsory part
+# (q / k / v / out) scales with the tokens, the K/V re-reads after L2 eviction grow faster with the sequence length.
 TRAFFIC_BYTES_PER_TOKEN = {"cfg4": 612.8e6 / 51883}
 
 WORKLOAD_DESC = {
@@ -116,69 +116,119 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
-def cpu_oracle_sample(w, seconds_target=15.0):
-    """Time the CPU oracle (torch, all host threads) on a length-stratified sample of the workload's sequences.
-    Returns (tflops, tokens_per_s, description, cores, seconds)."""
+def load_workloads():
+    """ops_rec_b200/workloads.py loaded by path: importing the package would load the native libraries, and the
+    reference arm must run without any of the product's code in its process."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_hstu_workloads", os.path.join(ROOT, "ops_rec_b200", "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod   # (dataclasses look their module up by name)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def cpu_forward_sample(w, W, seconds_target=15.0):
+    """Time the reference's CPU implementation of the forward (torch, all host threads) on a length-stratified sample
+    of the workload's sequences.  With the reference's own files present (baseline/_ref, see oracle/fetch_reference.py)
+    this is `Kernel._forward_impl` of its PyTorch golden, one B = 1 call per sampled sequence with explicit
+    scale = 1 / max_seq_len (its batched form pads to [B, H, maxL, maxL]: 550 GB for cfg4) and the mask built by its
+    create_causal_mask - kind "reference"; otherwise the restatement in oracle/hstu_oracle.py - kind "port".
+    Returns a dict(tflops, tokens_per_s, desc, cores, seconds, kind)."""
     import numpy as np
     import torch
 
-    from oracle import hstu_oracle as O
-    from ops_rec_b200 import workloads as W
+    from oracle import fetch_reference
 
     torch.set_num_threads(os.cpu_count() or 1)
     order = np.argsort(w.lengths, kind="stable")
-    # start with ~8 sequences spread over the length distribution; grow while the sample stays cheap
     n = min(8, len(order))
     picks = order[np.linspace(0, len(order) - 1, n).round().astype(int)]
     sub = w.subset(np.unique(picks), name=w.name + "-sample")
     kw = W.materialize(sub, "cpu")
+    ref = fetch_reference.load()
+    if ref is not None:
+        Kernel, causal_mask = ref
+        off = kw["seq_offset"].tolist()
+        scale = 1.0 / kw["max_seq_len"]
+        tgt = kw["num_target"].tolist() if kw["num_target"] is not None else None
+        bias = kw["attn_bias"]
+
+        def run():
+            outs = []
+            for b in range(len(off) - 1):
+                L = off[b + 1] - off[b]
+                o = torch.tensor([0, L])
+                sl = slice(off[b], off[b + 1])
+                rab = None
+                if bias is not None:
+                    blk = bias if bias.dim() == 3 else bias[b]
+                    rab = blk[None, :, :L, :L].float().clone()
+                t = tgt[b] if tgt else None
+                mask = causal_mask(L, L, None, t if t else None, kw["target_group_size"] if t else None)[None, None]
+                ker = Kernel(kw["alpha"], scale, rab is not None, L, L, o, o)
+                outs.append(ker._forward_impl(kw["q"][sl].float(), kw["k"][sl].float(), kw["v"][sl].float(), rab, mask))
+            return outs
+        kind, what = "reference", "the reference's PyTorch golden Kernel._forward_impl (fp32, one B=1 call per sequence)"
+    else:
+        from oracle import hstu_oracle as O
+
+        def run():
+            return O.hstu_jagged_forward(**kw)
+        kind, what = "port", "CPU restatement of the reference golden (fp32; the reference's own files are not present)"
     t0 = time.perf_counter()
-    O.hstu_jagged_forward(**kw)
+    run()
     dt = time.perf_counter() - t0
     reps = 1
     # repeat the same sample to fill the time budget (bounded), keep the best rate
     while dt * (reps + 1) < seconds_target and reps < 5:
         t1 = time.perf_counter()
-        O.hstu_jagged_forward(**kw)
+        run()
         dt = min(dt, time.perf_counter() - t1)
         reps += 1
     desc = (f"{sub.batch} of {w.batch} sequences of {w.name} (length-stratified, {sub.tokens} tokens, "
-            f"{sub.flops() / 1e9:.1f} GFLOP), torch fp32 CPU oracle, best of {reps}")
-    return sub.flops() / dt / 1e12, sub.tokens / dt, desc, torch.get_num_threads(), dt
+            f"{sub.flops() / 1e9:.1f} GFLOP), {what}, best of {reps}")
+    return dict(tflops=sub.flops() / dt / 1e12, tokens_per_s=sub.tokens / dt, desc=desc,
+                cores=torch.get_num_threads(), seconds=dt, kind=kind)
 
 
 def run_reference(args, rank):
+    """--impl reference: the reference's CPU implementation alone, on this box's host cores.  Nothing of the product
+    is imported (no native library is loaded into this process)."""
     if rank != 0:
         return
-    from ops_rec_b200 import workloads as W
-
+    W = load_workloads()
     w = W.make_workload(args.workload)
     if args.max_batch:
         import numpy as np
         w = w.subset(np.arange(min(args.max_batch, w.batch)))
-    vals, toks = [], []
-    desc, cores = "", 0
+    vals = []
+    r = None
     t_all = time.perf_counter()
     for i in range(args.warmup + args.steps):
-        tf, tk, desc, cores, dt = cpu_oracle_sample(w, seconds_target=0.0)
+        r = cpu_forward_sample(w, W, seconds_target=0.0)
         if i >= args.warmup:
-            vals.append((tf, tk, dt))
-        if time.perf_counter() - t_all > 240:  # keep the whole run within minutes
+            vals.append(r)
+        if time.perf_counter() - t_all > 150:  # keep the whole run within minutes
             break
     if not vals:
-        vals = [(tf, tk, dt)]
-    tf = statistics.median(v[0] for v in vals)
-    tk = statistics.median(v[1] for v in vals)
-    ms = statistics.median(v[2] for v in vals) * 1e3
+        vals = [r]
+    tf = statistics.median(v["tflops"] for v in vals)
+    tk = statistics.median(v["tokens_per_s"] for v in vals)
+    ms = statistics.median(v["seconds"] for v in vals) * 1e3
+    desc, cores, kind = r["desc"], r["cores"], r["kind"]
     line = {
         "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus, "steps": len(vals),
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "tokens_per_s": tk,
         "config": {"workload": WORKLOAD_DESC[args.workload], "step": "bounded sample: " + desc},
-        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc},
         "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    # this arm is the reference alone: none of the product's native code may be in the process
+    with open("/proc/self/maps") as f:
+        maps = f.read()
+    assert "ops_rec_b200" not in sys.modules and "libhstu_b200" not in maps and "_torch_shim" not in maps
     print(json.dumps(line), flush=True)
 
 
@@ -229,7 +279,7 @@ def run_in_linear_silu(args, local_rank):
     import ops_rec_b200 as ops_rec
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    m, k, n = 65536, 1024, 4096
+    m, k, n = args.m, 1024, 4096
     gen = torch.Generator(device=dev).manual_seed(1)
     x = (torch.randn(m, k, device=dev, generator=gen)).to(torch.bfloat16)
     w = (torch.randn(n, k, device=dev, generator=gen) * (6.0 / (n + k)) ** 0.5).to(torch.bfloat16)
@@ -261,6 +311,151 @@ def run_in_linear_silu(args, local_rank):
                      "frac": tf / peaks["tflops_burst"], "traffic": None, "kernel": "in_linear_silu_kernel",
                      "algorithmic_flops_per_launch": flops},
         "gpu_launches": args.steps, "clocks": clocks.summary()}), flush=True)
+
+
+def time_cold(step, flush, reps):
+    """Per-launch device time of `step` with a cold L2: a buffer larger than the L2 is rewritten before every launch,
+    one CUDA-event pair per launch on the launching stream (the host runs ahead while the flush executes, so the
+    interval holds device work only).  Returns the median in ms."""
+    import torch
+    ts = []
+    for _ in range(reps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return statistics.median(ts)
+
+
+def run_also(ops_rec, W, dev, peaks, names=("cfg2", "cfg3", "cfg5"), reps=12):
+    """The other named bf16 shapes, one GPU, cold L2 (their working sets - 87 MB, 149 MB - fit the 126 MB L2, so
+    back-to-back launches would flatter them).  All three are HBM-bound on compulsory traffic: hbm_frac is the
+    fraction that matters, tensor_frac is given beside it."""
+    import torch
+    hj = ops_rec.ascendc.attention.hstu_jagged
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    out = {}
+    for name in names:
+        w = W.make_workload(name)
+        kw = W.materialize(w, dev)
+
+        def step():
+            return hj(kw["q"], kw["k"], kw["v"], None, kw["attn_bias"], 0, kw["max_seq_len"], 0.0, kw["seq_offset"],
+                      None, kw["num_target"], kw["target_group_size"], kw["alpha"])
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        ms = time_cold(step, flush, reps)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        warm_ms = e0.elapsed_time(e1) / 20
+        tf = w.flops() / (ms * 1e-3) / 1e12
+        gbs = w.bytes() / (ms * 1e-3) / 1e9
+        out[name] = {"value": tf, "unit": UNIT, "ms_per_step": ms, "tokens_per_s": w.tokens / (ms * 1e-3),
+                     "hbm_gbs_algorithmic": gbs, "hbm_frac": gbs / peaks["hbm"], "tensor_frac": tf / peaks["tflops_burst"],
+                     "l2": "cold", "steps": reps, "warm_ms_per_step": warm_ms, "workload": WORKLOAD_DESC[name]}
+        del kw
+        torch.cuda.empty_cache()
+    # what a call costs before it computes anything: one sequence of one token (pre-pass + launch + set-up + drain)
+    w1 = W.Workload("one", 1, 4, 128, 128, __import__("numpy").array([1]))
+    kw = W.materialize(w1, dev)
+    f = lambda: hj(kw["q"], kw["k"], kw["v"], None, None, 0, 128, 0.0, kw["seq_offset"], None, None, 0, kw["alpha"])
+    for _ in range(3):
+        f()
+    out["fixed_cost_us"] = time_cold(f, flush, reps) * 1e3
+    return out
+
+
+def paged_workload(W):
+    """A cfg5-shaped serving batch for hstu_paged: every user's history (cfg5's L - T rows) sits in a paged KV cache
+    (pages of 128 rows handed out in shuffled order), the call brings the last 16 history rows (or fewer) plus the
+    T targets as queries."""
+    import numpy as np
+    w = W.make_workload("cfg5")
+    T = w.targets.astype(np.int64)
+    cache_len = np.maximum(w.lengths - T, 1)
+    new_hist = np.minimum(16, cache_len)
+    lq = new_hist + T
+    prev = cache_len - new_hist
+    i = np.arange(16)[None, :]
+    hist_pairs = ((i < new_hist[:, None]) * (i + prev[:, None] + 1)).sum(1)
+    pairs = hist_pairs + T * (cache_len + 1)
+    return dict(w=w, T=T, cache_len=cache_len, new_hist=new_hist, lq=lq, pairs=pairs, page=128)
+
+
+def run_paged(args, local_rank):
+    """--op paged: ops_rec::hstu_paged on the serving batch above (B=4096, H=4, d=64, bf16), inputs resident in HBM.
+    HBM-bound: algorithmic bytes = q + out + the cached K/V rows + the target K/V rows, each once."""
+    import numpy as np
+    import torch
+    import ops_rec_b200 as ops_rec
+    from ops_rec_b200 import workloads as W
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    pw = paged_workload(W)
+    w, page = pw["w"], pw["page"]
+    B, H, D = w.batch, w.heads, w.dim
+    if args.max_batch:
+        B = min(B, args.max_batch)
+    rng = np.random.default_rng(0)
+    cache_len, lq, T = pw["cache_len"][:B], pw["lq"][:B], pw["T"][:B]
+    pages_per = (cache_len + page - 1) // page
+    total_pages = int(pages_per.sum())
+    order = rng.permutation(total_pages)
+    page_off = np.concatenate([[0], np.cumsum(pages_per)])
+    last_len = np.where(cache_len % page == 0, page, cache_len % page)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    rnd = lambda *s: (torch.randn(*s, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+    tq = int(lq.sum())
+    q, k, v = rnd(tq, H, D), rnd(tq, H, D), rnd(tq, H, D)
+    cache = rnd(total_pages, 2, page, H, D)
+    i64 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int64, device=dev)
+    off_q, off_k = i64(np.concatenate([[0], np.cumsum(lq)])), i64(np.concatenate([[0], np.cumsum(cache_len + T)]))
+    off_t = i64(np.concatenate([[0], np.cumsum(T)]))
+    meta = (i64(page_off), i64(order), i64(last_len), i64(T))
+    max_q, max_k = int(lq.max()), int((cache_len + T).max())
+    op = ops_rec.ascendc.attention.hstu_paged
+
+    def step():
+        return op(q, k, v, cache, None, None, 0, max_q, max_k, 0.0, off_q, off_k, off_t, meta[0], meta[1], meta[2],
+                  meta[3], 1, 1.0 / D)
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    with ClockSampler(local_rank) as clocks:
+        for i in range(args.steps):
+            starts[i].record()
+            step()
+            ends[i].record()
+        torch.cuda.synchronize()
+    ms = statistics.mean(s.elapsed_time(e) for s, e in zip(starts, ends))
+    flops = float(H * 4 * D * pw["pairs"][:B].sum())
+    nbytes = float((2 * tq + 2 * int((cache_len + T).sum())) * H * D * 2)
+    peaks = load_peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "hstu_paged_fwd_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "tokens_per_s": tq / (ms * 1e-3),
+        "config": {"workload": f"hstu_paged: B={B} H={H} d={D} bf16, cache rows per user = cfg5's history "
+                               f"(mean {cache_len.mean():.0f}), page size {page}, {int(T.sum())} targets + up to 16 new "
+                               f"history rows per user as queries", "query_tokens": tq,
+                   "kv_rows": int((cache_len + T).sum()), "l2": f"{nbytes / 1e6:.0f} MB per step: no flush"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
+                     "traffic": None, "kernel": "hstu_paged_gather_kernel + hstu_tc_kernel",
+                     "algorithmic_bytes_per_launch": nbytes, "note": "the gather pass moves the K/V rows a second time "
+                     "(staging write + read), which the algorithmic bytes do not count"},
+        "gpu_launches": 4 * args.steps, "clocks": clocks.summary()}), flush=True)
 
 
 def run_backward(args, ops_rec, W, full, mine, kw, dev, rank, world, local_rank, warmup, barrier):
@@ -320,10 +515,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="cfg4", choices=sorted(WORKLOAD_DESC))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--op", default="forward", choices=["forward", "backward", "ln_mul", "in_linear_silu"],
+    ap.add_argument("--op", default="forward", choices=["forward", "backward", "ln_mul", "in_linear_silu", "paged"],
                     help="backward: time hstu_jagged_backward (device-resident only) instead of the forward; "
                          "ln_mul: time ops_rec::ln_mul on [262144, 1024] fp32 (HBM roofline); "
-                         "in_linear_silu: time ops_rec::distance_in_linear_silu, m=65536 k=1024 n=4096 bf16")
+                         "in_linear_silu: time ops_rec::distance_in_linear_silu, m=65536 k=1024 n=4096 bf16; "
+                         "paged: time ops_rec::hstu_paged on a cfg5-shaped serving batch")
+    ap.add_argument("--m", type=int, default=65536, help="--op in_linear_silu: rows of x (small cases for captures)")
+    ap.add_argument("--no-also", action="store_true",
+                    help="skip the cold-L2 timings of cfg2 / cfg3 / cfg5 that the default run adds to its line")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="length of the back-to-back loop behind the line's \"sustained\" figure (0 = skip)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunks", type=int, default=8,
                     help="the end-to-end run sends the batch through in this many chunks of whole sequences")
@@ -346,6 +547,10 @@ def main():
     if args.op == "in_linear_silu":
         if rank == 0:
             run_in_linear_silu(args, local_rank)
+        return
+    if args.op == "paged":
+        if rank == 0:
+            run_paged(args, local_rank)
         return
 
     import numpy as np
@@ -486,6 +691,23 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item()) / args.e2e_steps
 
+    # ---- sustained: the same step back to back for a couple of seconds (all ranks), clocks sampled
+    sus = None
+    if args.sustained_seconds > 0:
+        n_sus = max(args.steps, int(args.sustained_seconds * 1e3 / max(total_ms_max / args.steps, 1e-3)) + 1)
+        with ClockSampler(local_rank) as sus_clocks:
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n_sus):
+                step()
+            e1.record()
+            barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sus = (n_sus, float(t.item()), sus_clocks.summary())
+
     if rank == 0:
         peaks = load_peaks()
         ms_per_step = total_ms_max / args.steps
@@ -524,10 +746,24 @@ def main():
             "gpu_launches": 2 * args.steps,
             "clocks": clocks.summary(),
         }
+        if sus is not None:
+            n_sus, sus_ms, sc = sus
+            sv = full.flops() * n_sus / (sus_ms * 1e-3) / 1e12
+            line["sustained"] = {
+                "value": sv, "unit": UNIT, "steps": n_sus, "seconds": sus_ms * 1e-3,
+                "frac": sv / (world * peaks["tflops_sustained"]), "peak": peaks["tflops_sustained"],
+                "peak_kind": "sustained of " + peaks["source"], "clocks": sc,
+                # what the same run would give at the maximum SM clock (the kernel is clock-bound, not memory-bound)
+                "value_at_max_clock": (sv * sc["sm_max_mhz"] / sc["sm_mhz"]) if sc.get("sm_mhz") else None,
+            }
+        if world == 1 and not args.no_also and not args.max_batch and args.workload == "cfg4":
+            del kw, out, host_in, host_out, chunks
+            torch.cuda.empty_cache()
+            line["also"] = run_also(ops_rec, W, dev, peaks)
         if world == 1 and not args.no_cpu_baseline:
-            tf, tk, desc, cores, _ = cpu_oracle_sample(full)
-            line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc,
-                                    "tokens_per_s": tk}
+            r = cpu_forward_sample(full, W)
+            line["cpu_baseline"] = {"value": r["tflops"], "unit": UNIT, "cores": r["cores"], "kind": r["kind"],
+                                    "sample": r["desc"], "tokens_per_s": r["tokens_per_s"]}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
