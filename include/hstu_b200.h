@@ -247,6 +247,39 @@ typedef struct OpsRecInLinearSiluArgs {
 } OpsRecInLinearSiluArgs;
 HSTU_API int ops_rec_in_linear_silu_fwd(const OpsRecInLinearSiluArgs* args, void* stream);
 
+/* Its backward: replaces the aclnnInLinearSiluBackward call of
+ * ascendc/activation/in_linear_silu/torch_extension/in_linear_silu_backward_plugin.cpp:147-149.  With
+ * g = cat(user_grad, value_grad, query_grad, key_grad) and lo = linear_output (saved by the forward):
+ *   dL = g * sigmoid(lo) * (1 + lo * (1 - sigmoid(lo)));  bias_grad = column sums of dL (fp32);
+ *   x_grad = round(dL) . weight;  weight_grad = round(dL)^T . x        (fp32 accumulation, results in the input type)
+ * Same shape rules as the forward; the gradients and linear_output are [m, split[i]] / [m, n] in the input type,
+ * contiguous, 16-byte aligned; bias_grad is fp32 [n] or NULL.  Two-phase like the attention calls: phase 1 sizes the
+ * workspace (device memory, 256-byte aligned: dL, its transpose, weight^T, x^T and the partial column sums), phase 2
+ * enqueues on `stream`.  m <= 4 194 240. */
+typedef struct OpsRecInLinearSiluBwdArgs {
+  uint32_t struct_bytes;  /* sizeof(OpsRecInLinearSiluBwdArgs) */
+  int32_t dtype;          /* HSTU_DTYPE_BF16 or HSTU_DTYPE_FP16 */
+  const void* x;          /* [m, k] */
+  const void* weight;     /* [n, k] */
+  const void* user_grad;
+  const void* value_grad;
+  const void* query_grad;
+  const void* key_grad;
+  const void* linear_output; /* [m, n] */
+  void* x_grad;           /* [m, k] */
+  void* weight_grad;      /* [n, k] */
+  void* bias_grad;        /* [n] fp32, or NULL */
+  int64_t m;
+  int32_t n;
+  int32_t k;
+  int32_t split[4];
+  void* status;           /* optional device uint32, as in the forward */
+} OpsRecInLinearSiluBwdArgs;
+HSTU_API int ops_rec_in_linear_silu_bwd_get_workspace_size(const OpsRecInLinearSiluBwdArgs* args,
+                                                           uint64_t* workspace_bytes);
+HSTU_API int ops_rec_in_linear_silu_bwd(const OpsRecInLinearSiluBwdArgs* args, void* workspace,
+                                        uint64_t workspace_bytes, void* stream);
+
 /* Optional: wait for `stream` and fetch the device status word of the last launch that used `workspace`
  * (0 = inputs were consistent).  The reference reads out of bounds on such inputs without noticing. */
 HSTU_API int hstu_jagged_fwd_status(const void* workspace, void* stream, uint32_t* status);
@@ -261,17 +294,6 @@ HSTU_API int hstu_jagged_fwd_kernel_kind(const HstuJaggedArgs* args);
 HSTU_API int64_t hstu_plan_host(const HstuJaggedArgs* args, const void* host_offset_q, const void* host_offset_k,
                        const void* host_num_context, const void* host_num_target, uint32_t* items,
                        int64_t capacity, uint32_t* status);
-
-/* Testing hooks: the device mask predicate and K-tile classifier evaluated on the host (same source, compiled
- * for the host).  hstu_debug_mask_host fills out[len_q * len_k] with 0/1 visibility; hstu_debug_tiles_host returns
- * how many K tiles of width bn the q-tile rows [r0, r0+rows) visits and which of them need no per-element
- * predicate.  No counterpart in the reference API; its kernel-side equivalent is
- * ascendc/attention/hstu_v1/hstu_forward_v1/op_kernel/atlas950/hstu_dense_causal_mask.h:63-260. */
-HSTU_API int hstu_debug_mask_host(int32_t len_q, int32_t len_k, int32_t num_context, int32_t num_target,
-                         int32_t target_group_size, int32_t mask_type, uint8_t* out);
-HSTU_API int hstu_debug_tiles_host(int32_t len_q, int32_t len_k, int32_t num_context, int32_t num_target,
-                          int32_t target_group_size, int32_t mask_type, int32_t r0, int32_t rows, int32_t bn,
-                          uint64_t* full_bits);
 
 /* Text of the last error raised on the calling thread ("" if none). */
 HSTU_API const char* hstu_last_error(void);

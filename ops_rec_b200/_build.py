@@ -1,7 +1,9 @@
 """In-tree build of the native libraries (no JIT cache: the .so files sit next to this file).
 
   libhstu_b200.so   the C-ABI library: CUDA kernels for sm_100a + entry points (include/hstu_b200.h); nvcc only
-  _torch_shim.so    registers ops_rec::hstu_jagged.{equal,delta} with torch and forwards to the C ABI
+  _torch_shim.so    registers the operators with torch under the reference's schema strings - ops_rec::hstu_jagged
+                    (.equal / .delta), hstu_jagged_backward (.equal / .delta), hstu_dense, hstu_paged, ln_mul,
+                    distance_in_linear_silu - with their Meta implementations, and forwards to the C ABI
 
 Run `python ops_rec_b200/_build.py` (or call build_all()) after changing anything under csrc/.
 """
@@ -18,7 +20,7 @@ ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libhstu_b200.so")
 SHIM = os.path.join(PKG, "_torch_shim.so")
 
-CUDA_SOURCES = ["hstu_api.cu", "hstu_sched.cu", "hstu_generic.cu", "hstu_tc.cu", "hstu_static.cu", "hstu_paged.cu", "hstu_bwd_generic.cu", "hstu_bwd_tc.cu", "ln_mul.cu", "in_linear_silu.cu"]
+CUDA_SOURCES = ["hstu_api.cu", "hstu_sched.cu", "hstu_generic.cu", "hstu_tc.cu", "hstu_static.cu", "hstu_paged.cu", "hstu_bwd_generic.cu", "hstu_bwd_tc.cu", "ln_mul.cu", "in_linear_silu.cu", "in_linear_silu_bwd.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -38,6 +40,7 @@ def _stale(target, sources):
 def _deps():
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
     deps.append(os.path.join(ROOT, "include", "hstu_b200.h"))
+    deps.append(os.path.join(ROOT, "include", "hstu_b200_testing.h"))
     return deps
 
 

@@ -66,6 +66,32 @@ def _delta_backward(ctx, grad):
     return tuple(grads[:ctx.nargs])
 
 
+# ----------------------------------------------------------------------------------------- in_linear_silu
+# distance_in_linear_silu(x, weight, bias, attr_dict) -> (user, value, query, key, linear_output), bound to
+# in_linear_silu_backward exactly as ascendc/activation/in_linear_silu/torch_extension/_autograd.py:37-85 does: the
+# forward's linear_output is saved, its own incoming gradient is ignored (the backward operator applies the SiLU
+# derivative itself).
+def _linsilu_setup(ctx, inputs, output):
+    x, weight, bias, attr_dict = inputs
+    ctx.has_bias = bias is not None
+    if ctx.has_bias:
+        ctx.save_for_backward(x, weight, bias, output[-1])
+    else:
+        ctx.save_for_backward(x, weight, output[-1])
+    ctx.attr_dict = list(attr_dict)
+
+
+def _linsilu_backward(ctx, user_grad, value_grad, query_grad, key_grad, linear_output_grad):
+    if ctx.has_bias:
+        x, weight, bias, linear_output = ctx.saved_tensors
+    else:
+        x, weight, linear_output = ctx.saved_tensors
+        bias = None
+    x_grad, weight_grad, bias_grad, _ = torch.ops.ops_rec.in_linear_silu_backward(
+        x, weight, bias, user_grad, value_grad, query_grad, key_grad, linear_output, ctx.attr_dict)
+    return x_grad, weight_grad, bias_grad, None
+
+
 def register_autograd():
     """Attach the formulas (idempotent).  A failure for one overload is recorded in `registration_errors` and does
     not stop the other, as in the reference's registration (hstu_v1_autograd.py:301-312)."""
@@ -75,7 +101,9 @@ def register_autograd():
     _registered = True
     for name, op, bwd, setup in (
             ("hstu_jagged.equal", torch.ops.ops_rec.hstu_jagged.equal, _equal_backward, _equal_setup),
-            ("hstu_jagged.delta", torch.ops.ops_rec.hstu_jagged.delta, _delta_backward, _delta_setup)):
+            ("hstu_jagged.delta", torch.ops.ops_rec.hstu_jagged.delta, _delta_backward, _delta_setup),
+            ("distance_in_linear_silu", torch.ops.ops_rec.distance_in_linear_silu.default, _linsilu_backward,
+             _linsilu_setup)):
         try:
             torch.library.register_autograd(op, bwd, setup_context=setup)
         except Exception as e:  # noqa: BLE001 - differences between torch versions are recorded, not fatal

@@ -26,6 +26,7 @@ EXPORTS = (
     "hstu_last_error", "hstu_b200_version", "hstu_jagged_fwd_static", "hstu_jagged_fwd_static_status",
     "hstu_jagged_bwd_get_workspace_size", "hstu_jagged_bwd", "ops_rec_ln_mul_f32", "ops_rec_in_linear_silu_fwd",
     "hstu_paged_fwd_get_workspace_size", "hstu_paged_fwd",
+    "ops_rec_in_linear_silu_bwd_get_workspace_size", "ops_rec_in_linear_silu_bwd",
 )
 STATIC_SCRATCH_BYTES = 1 << 20
 E_SCRATCH_LIMIT = -6
@@ -69,6 +70,15 @@ class OpsRecInLinearSiluArgs(C.Structure):
         ("bias", C.c_void_p), ("user", C.c_void_p), ("value", C.c_void_p), ("query", C.c_void_p), ("key", C.c_void_p),
         ("linear_output", C.c_void_p), ("m", C.c_int64), ("n", C.c_int32), ("k", C.c_int32), ("split", C.c_int32 * 4),
         ("status", C.c_void_p),
+    ]
+
+
+class OpsRecInLinearSiluBwdArgs(C.Structure):
+    _fields_ = [
+        ("struct_bytes", C.c_uint32), ("dtype", C.c_int32), ("x", C.c_void_p), ("weight", C.c_void_p),
+        ("user_grad", C.c_void_p), ("value_grad", C.c_void_p), ("query_grad", C.c_void_p), ("key_grad", C.c_void_p),
+        ("linear_output", C.c_void_p), ("x_grad", C.c_void_p), ("weight_grad", C.c_void_p), ("bias_grad", C.c_void_p),
+        ("m", C.c_int64), ("n", C.c_int32), ("k", C.c_int32), ("split", C.c_int32 * 4), ("status", C.c_void_p),
     ]
 
 
@@ -123,6 +133,11 @@ def load():
     lib.hstu_paged_fwd_get_workspace_size.restype = C.c_int
     lib.hstu_paged_fwd.argtypes = [P, C.c_void_p, C.c_uint64, C.c_void_p]
     lib.hstu_paged_fwd.restype = C.c_int
+    LB = C.POINTER(OpsRecInLinearSiluBwdArgs)
+    lib.ops_rec_in_linear_silu_bwd_get_workspace_size.argtypes = [LB, C.POINTER(C.c_uint64)]
+    lib.ops_rec_in_linear_silu_bwd_get_workspace_size.restype = C.c_int
+    lib.ops_rec_in_linear_silu_bwd.argtypes = [LB, C.c_void_p, C.c_uint64, C.c_void_p]
+    lib.ops_rec_in_linear_silu_bwd.restype = C.c_int
     lib.ops_rec_ln_mul_f32.argtypes = [C.c_void_p] * 5 + [C.c_int64, C.c_int64, C.c_void_p]
     lib.ops_rec_ln_mul_f32.restype = C.c_int
     lib.ops_rec_in_linear_silu_fwd.argtypes = [C.POINTER(OpsRecInLinearSiluArgs), C.c_void_p]
@@ -357,6 +372,34 @@ def in_linear_silu(x, weight, bias, split):
     with torch.cuda.device(x.device):
         check(load().ops_rec_in_linear_silu_fwd(C.byref(a), stream))
     return (*outs, lin)
+
+
+def in_linear_silu_backward(x, weight, bias, user_grad, value_grad, query_grad, key_grad, linear_output, split):
+    """(x_grad, weight_grad, bias_grad or None) through ops_rec_in_linear_silu_bwd on CUDA tensors (argument order of
+    ops_rec::in_linear_silu_backward).  bias only says whether bias_grad is wanted."""
+    import torch
+    ts = [t.contiguous() for t in (x, weight, user_grad, value_grad, query_grad, key_grad, linear_output)]
+    x, weight = ts[0], ts[1]
+    x_grad, w_grad = torch.empty_like(x), torch.empty_like(weight)
+    b_grad = torch.empty(weight.shape[0], dtype=torch.float32, device=x.device) if bias is not None else None
+    a = OpsRecInLinearSiluBwdArgs()
+    a.struct_bytes = C.sizeof(OpsRecInLinearSiluBwdArgs)
+    a.dtype = _dtype_code(x.dtype)
+    a.x, a.weight = x.data_ptr(), weight.data_ptr()
+    a.user_grad, a.value_grad, a.query_grad, a.key_grad = (t.data_ptr() for t in ts[2:6])
+    a.linear_output = ts[6].data_ptr()
+    a.x_grad, a.weight_grad = x_grad.data_ptr(), w_grad.data_ptr()
+    a.bias_grad = b_grad.data_ptr() if b_grad is not None else None
+    a.m, a.n, a.k = x.shape[0], weight.shape[0], x.shape[1]
+    a.split = (C.c_int32 * 4)(*[int(s) for s in split])
+    n = C.c_uint64(0)
+    check(load().ops_rec_in_linear_silu_bwd_get_workspace_size(C.byref(a), C.byref(n)))
+    ws = torch.empty(n.value, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(load().ops_rec_in_linear_silu_bwd(C.byref(a), ws.data_ptr(), n.value,
+                                                torch.cuda.current_stream(x.device).cuda_stream))
+    del ts
+    return x_grad, w_grad, b_grad
 
 
 def ln_mul(x, u, gamma, beta):

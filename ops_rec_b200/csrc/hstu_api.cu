@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <cstring>
 
+#include "../../include/hstu_b200_testing.h"
 #include "hstu_common.cuh"
 
 namespace hstu {
@@ -24,6 +25,11 @@ cudaError_t launch_ln_mul(const float* x, const float* u, const float* gamma, co
                           long long rows, int cols, float eps, int num_sms, cudaStream_t stream);
 cudaError_t launch_in_linear_silu(const LinSiluParams& p, const void* x, const void* weight, int dtype,
                                   cudaStream_t stream);
+uint64_t in_linear_silu_bwd_workspace(long long m, int n, int k);
+cudaError_t launch_in_linear_silu_bwd(const LinSiluParams& shape, const void* x, const void* weight,
+                                      const void* const grads[4], const void* lo, void* x_grad, void* weight_grad,
+                                      float* bias_grad, void* workspace, int dtype, uint32_t* status,
+                                      cudaStream_t stream);
 cudaError_t launch_paged_gather(const KParams& p, const void* kv_cache, const void* k_in, const void* v_in,
                                 void* k_out, void* v_out, long long capacity, long long num_pages,
                                 long long num_page_ids, int esize, cudaStream_t stream);
@@ -462,6 +468,86 @@ int ops_rec_in_linear_silu_fwd(const OpsRecInLinearSiluArgs* a, void* stream_v) 
   const cudaError_t e = hstu::launch_in_linear_silu(p, a->x, a->weight, a->dtype, static_cast<cudaStream_t>(stream_v));
   if (e == cudaErrorNotSupported) return fail(HSTU_E_CUDA, "cuTensorMapEncodeTiled failed or is unavailable");
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "in_linear_silu launch: %s", cudaGetErrorString(e));
+  return HSTU_OK;
+}
+
+static int validate_linsilu_bwd(const OpsRecInLinearSiluBwdArgs* a) {
+  if (!a) return fail(HSTU_E_NULL, "args is null");
+  if (a->struct_bytes != sizeof(OpsRecInLinearSiluBwdArgs))
+    return fail(HSTU_E_PARAM, "struct_bytes is %u, this library expects %zu", a->struct_bytes,
+                sizeof(OpsRecInLinearSiluBwdArgs));
+  if (a->dtype != HSTU_DTYPE_BF16 && a->dtype != HSTU_DTYPE_FP16)
+    return fail(HSTU_E_PARAM, "in_linear_silu_backward: tensors must be bf16 or fp16");
+  long long total = 0;
+  for (int i = 0; i < 4; ++i) {
+    if (a->split[i] < 16 || a->split[i] > 8192 || a->split[i] % 16 != 0)
+      return fail(HSTU_E_PARAM, "uvqk dim must in range[16, 8192] and multiples of 16.");
+    total += a->split[i];
+  }
+  if (a->k < 16 || a->k > 8192 || a->k % 16 != 0)
+    return fail(HSTU_E_PARAM, "x dim[1] must in range[16, 8192] and multiples of 16.");
+  if (a->n < 64 || a->n > 32768 || a->n % 16 != 0)
+    return fail(HSTU_E_PARAM, "weight dim[0] must in range[64, 32768] and multiples of 16.");
+  if (total != a->n) return fail(HSTU_E_PARAM, "weight_dim[0] must equal to sum(split_list).");
+  if (a->n % (4 * a->k) != 0) return fail(HSTU_E_PARAM, "weight dim[0] must be a multiple of 4 x dim[1]");
+  if (a->m < 0 || a->m > 4194240ll) return fail(HSTU_E_PARAM, "in_linear_silu_backward: row count expect in [0, 4194240]");
+  return HSTU_OK;
+}
+
+int ops_rec_in_linear_silu_bwd_get_workspace_size(const OpsRecInLinearSiluBwdArgs* a, uint64_t* workspace_bytes) {
+  g_err[0] = 0;
+  if (!workspace_bytes) return fail(HSTU_E_NULL, "workspace_bytes is null");
+  int rc = validate_linsilu_bwd(a);
+  if (rc) return rc;
+  *workspace_bytes = hstu::in_linear_silu_bwd_workspace(a->m, a->n, a->k) + 256;
+  return HSTU_OK;
+}
+
+int ops_rec_in_linear_silu_bwd(const OpsRecInLinearSiluBwdArgs* a, void* workspace, uint64_t workspace_bytes,
+                               void* stream_v) {
+  g_err[0] = 0;
+  int rc = validate_linsilu_bwd(a);
+  if (rc) return rc;
+  if (a->m == 0) return HSTU_OK;
+  if (!a->x || !a->weight || !a->user_grad || !a->value_grad || !a->query_grad || !a->key_grad || !a->linear_output ||
+      !a->x_grad || !a->weight_grad)
+    return fail(HSTU_E_NULL, "in_linear_silu_backward: null pointer");
+  const uintptr_t align = reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->weight) |
+                          reinterpret_cast<uintptr_t>(a->user_grad) | reinterpret_cast<uintptr_t>(a->value_grad) |
+                          reinterpret_cast<uintptr_t>(a->query_grad) | reinterpret_cast<uintptr_t>(a->key_grad) |
+                          reinterpret_cast<uintptr_t>(a->linear_output) | reinterpret_cast<uintptr_t>(a->x_grad) |
+                          reinterpret_cast<uintptr_t>(a->weight_grad);
+  if (align & 15u) return fail(HSTU_E_PARAM, "in_linear_silu_backward: every tensor must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(a->bias_grad) | reinterpret_cast<uintptr_t>(a->status)) & 3u)
+    return fail(HSTU_E_PARAM, "in_linear_silu_backward: bias_grad / status must be 4-byte aligned");
+  const uint64_t need = hstu::in_linear_silu_bwd_workspace(a->m, a->n, a->k) + 256;
+  if (!workspace) return fail(HSTU_E_WORKSPACE, "workspace is null (%llu bytes needed)", (unsigned long long)need);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(HSTU_E_WORKSPACE, "workspace must be 256-byte aligned");
+  if (workspace_bytes < need)
+    return fail(HSTU_E_WORKSPACE, "workspace has %llu bytes, %llu needed", (unsigned long long)workspace_bytes,
+                (unsigned long long)need);
+  DeviceInfo dev;
+  rc = device_info(&dev);
+  if (rc) return rc;
+  if (dev.major != 10) return fail(HSTU_E_ARCH, "this library is built for sm_100a only; device has compute capability %d.x", dev.major);
+  hstu::LinSiluParams p;
+  memset(&p, 0, sizeof(p));
+  int at = 0;
+  for (int i = 0; i < 4; ++i) {
+    p.width[i] = a->split[i];
+    p.start[i] = at;
+    at += a->split[i];
+  }
+  p.start[4] = at;
+  p.m = a->m;
+  p.n = a->n;
+  p.k = a->k;
+  const void* grads[4] = {a->user_grad, a->value_grad, a->query_grad, a->key_grad};
+  const cudaError_t e = hstu::launch_in_linear_silu_bwd(
+      p, a->x, a->weight, grads, a->linear_output, a->x_grad, a->weight_grad, static_cast<float*>(a->bias_grad),
+      workspace, a->dtype, static_cast<uint32_t*>(a->status), static_cast<cudaStream_t>(stream_v));
+  if (e == cudaErrorNotSupported) return fail(HSTU_E_CUDA, "cuTensorMapEncodeTiled failed or is unavailable");
+  if (e != cudaSuccess) return fail(HSTU_E_CUDA, "in_linear_silu_backward launch: %s", cudaGetErrorString(e));
   return HSTU_OK;
 }
 

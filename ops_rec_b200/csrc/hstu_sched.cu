@@ -9,9 +9,9 @@
 //
 // Order of the list: sequences by number of q-pairs, longest first (a counting sort, stable in the sequence
 // index); inside a sequence head-major, and inside a head the q-pairs from the last (most K tiles) to the
-// first.  Persistent CTAs take items round-robin in a boustrophedon order, so each CTA gets a near-equal share
-// of the heavy head of the list, and the CTAs that run at the same time work on neighbouring q-pairs of the
-// same few (sequence, head) - their K/V stays in L2.
+// first.  Persistent CTAs draw items from a global atomic counter, so the order of the list is greedy
+// longest-first scheduling, and the CTAs that run at the same time work on neighbouring q-pairs of the same few
+// (sequence, head) - their K/V stays in L2.
 #include "hstu_common.cuh"
 
 namespace hstu {

@@ -9,19 +9,21 @@
 //     O += P.V             tcgen05.mma with P as the TMEM operand, V N-major from shared memory
 //
 // S and P never leave the SM; O stays in TMEM for the whole row of K tiles (there is no softmax, so no
-// rescaling), then goes TMEM -> registers -> 16-byte stores into the jagged [tokens, heads, dim] output.
+// rescaling), then goes TMEM -> registers -> shared memory -> TMA stores (a tile cut by the sequence end: 16-byte
+// row stores that stop at the end) into the jagged [tokens, heads, dim] output.
 // Compare the reference kernel, which moves every S tile and every P tile through a global-memory ring
 // between its matrix and vector cores and accumulates partial O rows with atomics
 // (…/op_kernel/atlas950/hstu_dense_forward_kernel_patten_bsnd.h:156-176, 590-689,
 //  hstu_dense_forward_jagged_kernel.h:257-398).
 //
 // Warp roles (384 threads): warp 0 = TMA producer, warps 1 and 3 = MMA issuers (one per Q tile), warp 2 = TMEM
-// allocator and work-item scheduler,
-// warps 4-7 = P/O group of Q tile 0, warps 8-11 = P/O group of Q tile 1.
+// allocator, work-item scheduler and TMA producer of the staged bias tiles, warps 4-7 and 8-11 = the two P/O groups:
+// both work on both Q tiles, group g owning 64 of the 128 score columns and half of the output columns of each.
 //
 // Every wait on an mbarrier is bounded: after ~1 s without progress the waiter raises HSTU_ST_PIPE_TIMEOUT in
 // the workspace status word and a CTA-wide abort flag that turns all later waits into no-ops, so the kernel
-// always runs to its end, frees its tensor memory and returns (with garbage in `out` and the flag set).
+// always runs to its end, frees its tensor memory and returns (with garbage in `out` and the flag set).  Once the flag
+// is up no role touches a barrier any more: a role that passed a wait only because of the flag leaves its loop.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <cuda_bf16.h>
@@ -150,19 +152,6 @@ struct ItemFeed {
   }
 };
 
-// Investigation build (-DHSTU_PROF): per-role cycle counters and an event trace of CTA 0, read back through
-// hstu_debug_read_prof / hstu_debug_read_trace.  The production library is built without it.
-#ifdef HSTU_PROF
-__device__ unsigned long long g_prof[160][24];
-__device__ unsigned long long g_trace[4][512];   // CTA 0: roles 0,1 = P/O groups, 2,3 = MMA issuers
-#define TRACE(role, code) do { if (blockIdx.x == 0 && trace_n < 512) g_trace[role][trace_n++] = (static_cast<unsigned long long>(clock64()) << 8) | (code); } while (0)
-#define PROF_T0(var) const long long var = clock64()
-#define PROF_ADD(slot, var) prof_acc[slot] += clock64() - (var)
-#else
-#define PROF_T0(var)
-#define PROF_ADD(slot, var)
-#define TRACE(role, code)
-#endif
 
 __device__ __forceinline__ Item load_item(const KParams& p, long long idx) {
   Item it;
@@ -517,11 +506,6 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       const uint32_t bar_bias_free = ptx::smem_u32(&bars->bias_free[t]);
       uint32_t q_uses = 0, p_uses = 0, o_uses = 0, b_uses = 0;
       uint32_t ring_base = 0;
-#ifdef HSTU_PROF
-      unsigned long long prof_acc[6] = {0, 0, 0, 0, 0, 0};
-      const long long t_all = clock64();
-      int trace_n = 0;
-#endif
       for (Item it; feed.next(it);) {
         const int n = it.n(t);
         for (int step = 0; step <= it.nmax; ++step) {
@@ -535,7 +519,6 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           // The two issuers run free of each other: the P/O groups serve the tiles in a fixed order (tile 0,
           // tile 1, tile 0 ...), so the P tiles - and with them the MMA bursts - alternate by themselves.
           // poll everything this step needs at once
-          PROF_T0(t_kv);
           const bool ok_v = has_v ? ptx::mbar_try_wait(bar_vf, par_vf) : true;
           const bool ok_k = has_k ? ptx::mbar_try_wait(bar_kf, par_kf) : true;
           const bool ok_p = do_pv ? ptx::mbar_try_wait(bar_p_full, p_uses & 1u) : true;
@@ -543,20 +526,13 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           w.wait_polled(ok_v, bar_vf, par_vf);
           w.wait_polled(ok_k, bar_kf, par_kf);
           if (kBias == 2 && do_qk) w.wait_polled(ok_b, bar_bias_full, b_uses & 1u);
-          PROF_ADD(0, t_kv);
-          PROF_T0(t_p);
           w.wait_polled(ok_p, bar_p_full, p_uses & 1u);
-          PROF_ADD(1, t_p);
-          PROF_T0(t_of);
           if (do_pv && step == 1) w.wait(bar_o_free, (o_uses & 1u) ^ 1u);
           if (do_qk && step == 0) w.wait(bar_q_full, q_uses & 1u);
-          PROF_ADD(2, t_of);
           if (w.aborted()) break;  // a wait gave up somewhere: issue nothing more, touch no barrier
           ptx::tc_fence_after();
-          TRACE(2 + t, 1);
           if (do_pv) {
             // O_t (+)= P_t(step-1) . V(step-1)
-            PROF_T0(t_ipv);
             const uint64_t vbase = kDescV | static_cast<uint64_t>((sm_ring + st_v * C::kTileBytes) >> 4);
             // P arrives in two steps: first the leading 32 keys of both 64-key halves (k-steps 0, 1, 4, 5), then,
             // while these MMAs run, the rest.  Keys 0..63 sit at columns 0..31 of the S tile, keys 64..127 at
@@ -576,7 +552,6 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
             pv(6, 1u);
             pv(7, 1u);
             ++p_uses;
-            PROF_ADD(4, t_ipv);
             if (step == n) {
               ptx::mma_commit(bar_o_full);
               ++o_uses;
@@ -584,7 +559,6 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           }
           if (do_qk) {
             // S_t = Q_t . K(step)^T
-            PROF_T0(t_iqk);
             const uint64_t kbase = kDescK | static_cast<uint64_t>((sm_ring + st_k * C::kTileBytes) >> 4);
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
@@ -608,14 +582,12 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
               ptx::mma_commit(bar_bias_free);
               ++b_uses;
             }
-            PROF_ADD(5, t_iqk);
             ptx::mma_commit(bar_s_full);
             if (step == n - 1) {
               ptx::mma_commit(bar_q_free);
               ++q_uses;
             }
           }
-          TRACE(2 + t, 2);
           // release the K/V tiles of this step: after this tile's MMAs that read them, or at once when this
           // tile does not visit them (the tile is loaded - waited above - so the arrival counts for its
           // current use)
@@ -634,14 +606,6 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       // all MMAs (and the mbarrier arrivals of their commits) complete before the CTA tears down
       ptx::mma_commit(ptx::smem_u32(&bars->done[t]));
       w.wait(ptx::smem_u32(&bars->done[t]), 0);
-#ifdef HSTU_PROF
-      prof_acc[3] = clock64() - t_all;
-      if (t == 0) {
-        for (int i = 0; i < 4; ++i) g_prof[blockIdx.x][12 + i] = prof_acc[i];
-        g_prof[blockIdx.x][20] = prof_acc[4];
-        g_prof[blockIdx.x][21] = prof_acc[5];
-      }
-#endif
     }
   } else if (warp == 2) {
     // ------------------------------------------------------------------ scheduler: draws items from the global
@@ -755,10 +719,6 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     const float c_bias = alpha_first ? (kExact ? 1.f : 0.5f) : c_in;
     uint32_t s_uses[2] = {0, 0}, o_uses[2] = {0, 0};
     uint32_t out_chunks = 0;              // TMA-store chunks issued so far by this warp (selects the staging buffer)
-#ifdef HSTU_PROF
-    unsigned long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-    int trace_n = 0;
-#endif
     // O tiles: this group's half of the columns.  A Q tile that lies wholly inside its sequence leaves through
     // shared memory and TMA stores (32 rows x 32 columns per warp and store, double buffered); a tile cut by the
     // sequence end must not touch the rows after it and is written row by row.
@@ -770,12 +730,8 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       T* orow = static_cast<T*>(p.out) + ((ot.q0 + tile_r0 + row) * p.hq + ot.h) * D + col0;
       if (ot.n > 0) {
         const uint32_t t_o = tmem + lane_base + (t == 0 ? kColO0 : C::kColO1) + col0;
-        PROF_T0(t_wo);
         w.wait(ptx::smem_u32(&bars->o_full[t]), o_uses[t] & 1u);
         if (w.aborted()) return;  // nothing valid to store; the barriers are left alone
-        PROF_ADD(2, t_wo);
-        PROF_T0(t_epi);
-        if (grp == 0 && row == 0) TRACE(t, 5);
         ++o_uses[t];
         ptx::tc_fence_after();
         const bool by_tma = C::kOutBytes > 0 && tile_r0 + kTileM <= ot.lq;
@@ -826,8 +782,6 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         }
         ptx::tc_fence_before();
         ptx::mbar_arrive(ptx::smem_u32(&bars->o_free[t]));
-        if (grp == 0 && row == 0) TRACE(t, 6);
-        PROF_ADD(3, t_epi);
       } else if (row_ok_t) {
         uint4* dst = reinterpret_cast<uint4*>(orow);
 #pragma unroll
@@ -835,13 +789,8 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       }
     };
     // the S tiles arrive in the order the MMA issuers alternate: tile 0 step j, tile 1 step j, tile 0 step j+1 ..
-#ifdef HSTU_PROF
-    const long long t_role = clock64();
-#endif
     for (Item it;;) {
-      PROF_T0(t_item);
       if (!feed.next(it)) break;
-      PROF_ADD(4, t_item);
       int i_row[2];
       bool row_ok[2];
       RowBounds rb[2];
@@ -898,12 +847,8 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
             }
           }
           const int fix_ch = (kBias == 2 && fix_mine) ? ((fix_col >> 5) & 1) : -1;
-          PROF_T0(t_ws);
           w.wait(ptx::smem_u32(&bars->s_full[t]), s_uses[t] & 1u);
           if (w.aborted()) break;  // (the item feed then ends the outer loops)
-          PROF_ADD(0, t_ws);
-          PROF_T0(t_silu);
-          if (grp == 0 && row == 0) TRACE(t, 3);
           ++s_uses[t];
           ptx::tc_fence_after();
           const BiasRow br{p.bias, bias_row[t], row_ok[t], bias_vec_ok != 0, p.maxk, it.s.lk};
@@ -911,23 +856,12 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
             p_half<T, kBias, false>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p, fix_ch, fix_col & 16, fix_n, fixv);
           else
             p_half<T, kBias, true>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p, fix_ch, fix_col & 16, fix_n, fixv);
-          if (grp == 0 && row == 0) TRACE(t, 4);
-          PROF_ADD(1, t_silu);
-#ifdef HSTU_PROF
-          prof_acc[5] += 1;
-#endif
         }
       }
       if (!o0_stored) store_o(0, out0);
       store_o(1, OutTile{it.s.q0, it.s.lq, it.r0 + kTileM, it.h, it.n1});
     }
     if (C::kOutBytes > 0 && lane == 0) ptx::bulk_wait<0>();  // this thread's TMA stores have completed
-#ifdef HSTU_PROF
-    if (row == 0) {
-      for (int i = 0; i < 6; ++i) g_prof[blockIdx.x][grp * 6 + i] = prof_acc[i];
-      g_prof[blockIdx.x][16 + grp] = clock64() - t_role;
-    }
-#endif
   }
 
   ptx::tc_fence_before();
@@ -1024,24 +958,22 @@ cudaError_t launch_inst(const KParams& p, const CUtensorMap& mq, const CUtensorM
 
 }  // namespace
 
-#ifdef HSTU_PROF
-}  // namespace hstu
-extern "C" __attribute__((visibility("default"))) int hstu_debug_read_trace(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, hstu::g_trace, sizeof(unsigned long long) * 4 * 512) == cudaSuccess ? 0 : -4;
-}
-extern "C" __attribute__((visibility("default"))) int hstu_debug_read_prof(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, hstu::g_prof, sizeof(unsigned long long) * 160 * 24) == cudaSuccess ? 0 : -4;
-}
-namespace hstu {
-#endif
 
 // 2-D view (cols, rows) of a contiguous 16-bit [rows, cols] matrix; box = 64 x box_rows (<= 256), 128-byte swizzle
 // (a K-major operand tile of 64 K values).  Reads past either edge give zeros.
+bool make_matrix_map_ld(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld, int dtype,
+                        int box_rows);
 bool make_matrix_map(CUtensorMap* m, const void* base, long long rows, long long cols, int dtype, int box_rows) {
+  return make_matrix_map_ld(m, base, rows, cols, cols, dtype, box_rows);
+}
+// The same with a row pitch of `ld` elements (a multiple of 8: TMA wants 16-byte strides); columns at or past `cols`
+// read as zeros whatever the padding holds.
+bool make_matrix_map_ld(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld, int dtype,
+                        int box_rows) {
   auto fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows > 0 ? rows : 1)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
   cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   const CUtensorMapDataType dt = dtype == HSTU_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16

@@ -80,7 +80,9 @@ __device__ __forceinline__ void ls_wait(LsBars* bars, uint32_t* status, uint32_t
   }
 }
 
-template <typename T>
+// kPlain: the bare product  out = x . weight^T  rounded to the element type, written to p.linear ([m, n]) - the two
+// matrix products of the backward (in_linear_silu_bwd.cu) run on this same pipeline.
+template <typename T, bool kPlain>
 __global__ void __launch_bounds__(kLsThreads, 1)
 in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap tm_x,
                       const __grid_constant__ CUtensorMap tm_w) {
@@ -110,7 +112,7 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
   }
   // the bias values of this tile's columns (zeros without a bias / past the last column), read by every epilogue thread
   float* s_bias = reinterpret_cast<float*>(base_ptr + kLsStages * 2 * kLsChunkBytes + 256);
-  if (tid < kLsTile) s_bias[tid] = (p.bias && n0 + tid < p.n) ? p.bias[n0 + tid] : 0.f;
+  if (tid < kLsTile) s_bias[tid] = (!kPlain && p.bias && n0 + tid < p.n) ? p.bias[n0 + tid] : 0.f;
   if (warp == 2) {
     ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), 512);
     ptx::tmem_relinquish();
@@ -188,21 +190,22 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
         const float v1 = LsPack<T>::round(__uint_as_float(acc[2 * e + 1]) + b1);
         lin[e] = LsPack<T>::pack(v0, v1);
         // SiLU of the rounded value
-        act[e] = LsPack<T>::pack(__fdividef(v0, 1.f + __expf(-v0)), __fdividef(v1, 1.f + __expf(-v1)));
+        if (!kPlain) act[e] = LsPack<T>::pack(__fdividef(v0, 1.f + __expf(-v0)), __fdividef(v1, 1.f + __expf(-v1)));
       }
       __syncwarp();   // the previous chunk's staged rows have been read
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
         *reinterpret_cast<uint4*>(stage + lane * kPitch + q4 * 16) =
             make_uint4(lin[4 * q4], lin[4 * q4 + 1], lin[4 * q4 + 2], lin[4 * q4 + 3]);
-        *reinterpret_cast<uint4*>(stage + 32 * kPitch + lane * kPitch + q4 * 16) =
-            make_uint4(act[4 * q4], act[4 * q4 + 1], act[4 * q4 + 2], act[4 * q4 + 3]);
+        if (!kPlain)
+          *reinterpret_cast<uint4*>(stage + 32 * kPitch + lane * kPitch + q4 * 16) =
+              make_uint4(act[4 * q4], act[4 * q4 + 1], act[4 * q4 + 2], act[4 * q4 + 3]);
       }
       __syncwarp();
       // this lane's 8 columns: c0 + 8 part .. ; their 16-column group decides the SiLU output tensor
       const int cg = c0 + 16 * (part >> 1);
       const bool col_ok = cg < p.n;   // n is a multiple of 16
-      const int which = (cg >= p.start[1]) + (cg >= p.start[2]) + (cg >= p.start[3]);
+      const int which = kPlain ? 0 : (cg >= p.start[1]) + (cg >= p.start[2]) + (cg >= p.start[3]);
       T* obase = static_cast<T*>(which == 0 ? p.out[0] : which == 1 ? p.out[1] : which == 2 ? p.out[2] : p.out[3]);
       const int owidth = which == 0 ? p.width[0] : which == 1 ? p.width[1] : which == 2 ? p.width[2] : p.width[3];
       const int ostart = which == 0 ? p.start[0] : which == 1 ? p.start[1] : which == 2 ? p.start[2] : p.start[3];
@@ -214,7 +217,7 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
           const uint4 l = *reinterpret_cast<const uint4*>(stage + r * kPitch + part * 16);
           const uint4 a = *reinterpret_cast<const uint4*>(stage + 32 * kPitch + r * kPitch + part * 16);
           *reinterpret_cast<uint4*>(static_cast<T*>(p.linear) + gr * p.n + c0 + part * 8) = l;
-          *reinterpret_cast<uint4*>(obase + gr * owidth + (cg - ostart) + (part & 1) * 8) = a;
+          if (!kPlain) *reinterpret_cast<uint4*>(obase + gr * owidth + (cg - ostart) + (part & 1) * 8) = a;
         }
       }
     }
@@ -228,11 +231,11 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
   }
 }
 
-template <typename T>
+template <typename T, bool kPlain>
 cudaError_t launch_t(const LinSiluParams& p, const CUtensorMap& mx, const CUtensorMap& mw, cudaStream_t stream) {
   constexpr int smem = 1024 + kLsStages * 2 * kLsChunkBytes + 256 + kLsTile * 4;
   static_assert(sizeof(LsBars) <= 256, "barrier block too large");
-  auto kern = in_linear_silu_kernel<T>;
+  auto kern = in_linear_silu_kernel<T, kPlain>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   const long long tiles = static_cast<long long>((p.n + kLsTile - 1) / kLsTile) * ((p.m + kLsTile - 1) / kLsTile);
@@ -250,7 +253,32 @@ cudaError_t launch_in_linear_silu(const LinSiluParams& p, const void* x, const v
   CUtensorMap mx, mw;
   if (!make_matrix_map(&mx, x, p.m, p.k, dtype, kLsTile) || !make_matrix_map(&mw, weight, p.n, p.k, dtype, kLsTile))
     return cudaErrorNotSupported;
-  return dtype == HSTU_DTYPE_BF16 ? launch_t<__nv_bfloat16>(p, mx, mw, stream) : launch_t<__half>(p, mx, mw, stream);
+  return dtype == HSTU_DTYPE_BF16 ? launch_t<__nv_bfloat16, false>(p, mx, mw, stream)
+                                  : launch_t<__half, false>(p, mx, mw, stream);
+}
+
+bool make_matrix_map_ld(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld, int dtype,
+                        int box_rows);
+
+// out [rows_a, rows_b] = a . b^T in the element type (fp32 accumulation, one rounding); a [rows_a, kdim] with row pitch
+// lda, b [rows_b, kdim] with row pitch ldb (pitches multiples of 8 elements, bases 16-byte aligned, rows_b a multiple of
+// 16, out contiguous).  kdim need not be a multiple of anything: what lies past it reads as zeros.
+cudaError_t launch_gemm_abt(const void* a, long long rows_a, long long lda, const void* b, int rows_b, long long ldb,
+                            long long kdim, void* out, int dtype, uint32_t* status, cudaStream_t stream) {
+  if (rows_a == 0 || rows_b == 0) return cudaSuccess;
+  CUtensorMap ma, mb;
+  if (!make_matrix_map_ld(&ma, a, rows_a, kdim, lda, dtype, kLsTile) ||
+      !make_matrix_map_ld(&mb, b, rows_b, kdim, ldb, dtype, kLsTile))
+    return cudaErrorNotSupported;
+  LinSiluParams p = {};
+  p.linear = out;
+  p.m = rows_a;
+  p.n = rows_b;
+  p.k = static_cast<int>(kdim);
+  p.start[4] = rows_b;
+  p.status = status;
+  return dtype == HSTU_DTYPE_BF16 ? launch_t<__nv_bfloat16, true>(p, ma, mb, stream)
+                                  : launch_t<__half, true>(p, ma, mb, stream);
 }
 
 }  // namespace hstu

@@ -376,6 +376,84 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> in_linear
                          at::empty({m, split[3]}, o), at::empty({m, weight.size(0)}, o));
 }
 
+// in_linear_silu_backward (ascendc/activation/in_linear_silu/torch_extension/in_linear_silu_backward_plugin.cpp:
+// checks :41-103, implementation :118-152): (x_grad, weight_grad, bias_grad, undefined).  bias_grad is fp32 like the
+// bias; x_grad / weight_grad come back in the input type.
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> in_linear_silu_bwd(
+    const at::Tensor& x, const at::Tensor& weight, const c10::optional<at::Tensor>& bias, const at::Tensor& user_grad,
+    const at::Tensor& value_grad, const at::Tensor& query_grad, const at::Tensor& key_grad,
+    const at::Tensor& linear_output, at::IntArrayRef split) {
+  TORCH_CHECK(x.defined() && x.numel() > 0, "x is empty");
+  TORCH_CHECK(weight.defined() && weight.numel() > 0, "weight is empty");
+  TORCH_CHECK(x.dim() == 2, "x must be 2D");
+  TORCH_CHECK(weight.dim() == 2, "weight must be 2D");
+  TORCH_CHECK(split.size() == 4, "split_list must have 4 elements.");
+  TORCH_CHECK(x.is_cuda() && weight.is_cuda(), "in_linear_silu_backward: tensors must be CUDA tensors");
+  TORCH_CHECK(weight.scalar_type() == x.scalar_type(), "weight must have the dtype of x");
+  TORCH_CHECK(weight.size(1) == x.size(1), "weight dim[1] must equal to x dim[1].");
+  const at::Tensor* gs[5] = {&user_grad, &value_grad, &query_grad, &key_grad, &linear_output};
+  const char* names[5] = {"user_grad", "value_grad", "query_grad", "key_grad", "linear_output"};
+  for (int i = 0; i < 5; ++i) {
+    TORCH_CHECK(gs[i]->defined() && gs[i]->numel() > 0, names[i], " is empty");
+    TORCH_CHECK(gs[i]->dim() == 2, names[i], " must be 2D");
+    TORCH_CHECK(gs[i]->device() == x.device() && gs[i]->scalar_type() == x.scalar_type(), names[i],
+                " must be on x's device and of x's dtype");
+    TORCH_CHECK(gs[i]->size(0) == x.size(0),
+                "user_grad, value_grad, query_grad, key_grad linear_output dim[0] must equal to x dim[0].");
+    if (i < 4) TORCH_CHECK(gs[i]->size(1) == split[i], "user_grad, value_grad, query_grad, key_grad dim[1] must be equal to split_list.");
+  }
+  TORCH_CHECK(linear_output.size(1) == weight.size(0), "linear_output dim[1] must equal to weight dim[0].");
+  const bool has_bias = bias.has_value() && bias->defined();
+  if (has_bias) {
+    TORCH_CHECK(bias->dim() == 1 && bias->numel() > 0, "bias must be 1D and not empty");
+    TORCH_CHECK(bias->size(0) == weight.size(0), "bias dim[0] must equal to weight dim[0].");
+    TORCH_CHECK(bias->device() == x.device(), "bias must be on x's device");
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  auto xc = x.contiguous(), wc = weight.contiguous();
+  at::Tensor gc[5];
+  for (int i = 0; i < 5; ++i) gc[i] = gs[i]->contiguous();
+  auto x_grad = at::empty_like(xc), w_grad = at::empty_like(wc);
+  at::Tensor b_grad;
+  if (has_bias) b_grad = at::empty({wc.size(0)}, xc.options().dtype(at::kFloat));
+  OpsRecInLinearSiluBwdArgs a;
+  memset(&a, 0, sizeof(a));
+  a.struct_bytes = sizeof(a);
+  a.dtype = dtype_code(x.scalar_type());
+  TORCH_CHECK(a.dtype != HSTU_DTYPE_FP32, "in_linear_silu_backward: tensors must be bf16 or fp16");
+  a.x = xc.data_ptr();
+  a.weight = wc.data_ptr();
+  a.user_grad = gc[0].data_ptr();
+  a.value_grad = gc[1].data_ptr();
+  a.query_grad = gc[2].data_ptr();
+  a.key_grad = gc[3].data_ptr();
+  a.linear_output = gc[4].data_ptr();
+  a.x_grad = x_grad.data_ptr();
+  a.weight_grad = w_grad.data_ptr();
+  a.bias_grad = has_bias ? b_grad.data_ptr() : nullptr;
+  a.m = xc.size(0);
+  a.n = static_cast<int32_t>(wc.size(0));
+  a.k = static_cast<int32_t>(xc.size(1));
+  for (int i = 0; i < 4; ++i) a.split[i] = static_cast<int32_t>(split[i]);
+  uint64_t ws_bytes = 0;
+  int rc = ops_rec_in_linear_silu_bwd_get_workspace_size(&a, &ws_bytes);
+  TORCH_CHECK(rc == 0, hstu_last_error());
+  auto ws = at::empty({static_cast<int64_t>(ws_bytes)}, xc.options().dtype(at::kByte));
+  rc = ops_rec_in_linear_silu_bwd(&a, ws.data_ptr(), ws_bytes, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, hstu_last_error());
+  if (has_bias && bias->scalar_type() != at::kFloat) b_grad = b_grad.to(bias->scalar_type());
+  return std::make_tuple(x_grad, w_grad, b_grad, at::Tensor());
+}
+
+// (in_linear_silu_backward_plugin.cpp:105-116)
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> in_linear_silu_bwd_meta(
+    const at::Tensor& x, const at::Tensor& weight, const c10::optional<at::Tensor>& bias, const at::Tensor&,
+    const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&, at::IntArrayRef) {
+  at::Tensor b_grad;
+  if (bias.has_value() && bias->defined()) b_grad = at::empty_like(*bias);
+  return std::make_tuple(at::empty_like(x), at::empty_like(weight), b_grad, at::Tensor());
+}
+
 // hstu_dense: [B, S, N, D] layout, every batch row one sequence of S tokens
 // (ascendc/attention/hstu_v1/torch_extension/hstu_dense_plugin.cpp:19-40).  It is the jagged forward over equal
 // lengths: the tensors are viewed as [B*S, N, D] and the offsets 0, S, 2S, ... are generated on the device.
@@ -519,6 +597,9 @@ TORCH_LIBRARY_FRAGMENT(ops_rec, m) {
         "(Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("hstu_dense(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
         "int max_seq_len=0, float silu_scale=0.0) -> Tensor");
+  // in_linear_silu_backward_plugin.cpp:154-161
+  m.def("in_linear_silu_backward(Tensor x, Tensor weight, Tensor ? bias,Tensor user_grad, Tensor value_grad, "
+        "Tensor query_grad, Tensor key_grad,Tensor linear_output,int[] attr_dict) -> (Tensor, Tensor, Tensor, Tensor)");
   // hstu_paged_plugin.cpp:75-98
   m.def("hstu_paged(Tensor q, Tensor k, Tensor v, Tensor kv_cache=None, Tensor? mask=None, Tensor? attn_bias=None,"
         " int mask_type=0, int max_seq_len=0, int max_seq_len_k=0, float silu_scale=0.0, Tensor seq_offset=None,"
@@ -536,6 +617,7 @@ TORCH_LIBRARY_IMPL(ops_rec, CUDA, m) {
   m.impl("distance_in_linear_silu", TORCH_FN(in_linear_silu_fwd));
   m.impl("hstu_dense", TORCH_FN(hstu_dense));
   m.impl("hstu_paged", TORCH_FN(hstu_paged));
+  m.impl("in_linear_silu_backward", TORCH_FN(in_linear_silu_bwd));
 }
 
 TORCH_LIBRARY_IMPL(ops_rec, Meta, m) {
@@ -547,4 +629,5 @@ TORCH_LIBRARY_IMPL(ops_rec, Meta, m) {
   m.impl("distance_in_linear_silu", TORCH_FN(in_linear_silu_fwd_meta));
   m.impl("hstu_dense", TORCH_FN(hstu_dense_meta));
   m.impl("hstu_paged", TORCH_FN(hstu_paged_meta));
+  m.impl("in_linear_silu_backward", TORCH_FN(in_linear_silu_bwd_meta));
 }

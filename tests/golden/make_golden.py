@@ -321,6 +321,35 @@ def main_in_linear_silu(ref_root):
         print(f"{os.path.basename(path):32s} {os.path.getsize(path) / 1024:8.1f} KiB")
 
 
+def main_in_linear_silu_backward(ref_root):
+    """in_linear_silu_backward fixtures: inputs from the reference test's `get_data` and the outputs of its two goldens,
+    `ln_linear_silu_backward_golden_cpu` (fp32) and `ln_linear_silu_backward_npu` (16-bit intermediate), in
+    in_linear_silu_backward/test/pytest/test_in_linear_silu_backward.py:125-195.  The module imports `ops_rec` and
+    touches `torch.npu` at import time; both get empty stand-ins."""
+    d = os.path.join(ref_root, "ascendc/activation/in_linear_silu/in_linear_silu_backward/test/pytest")
+    torch.npu = types.SimpleNamespace(config=types.SimpleNamespace())
+    sys.modules.setdefault("ops_rec", types.ModuleType("ops_rec"))
+    spec = importlib.util.spec_from_file_location("ref_linsilu_bwd_test", os.path.join(d, "test_in_linear_silu_backward.py"))
+    rb = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rb)
+    for name, m, dim, has_bias, dt, diff in (("linsilu_bwd_37x64x256_bf16", 37, (64, 256), True, torch.bfloat16, False),
+                                             ("linsilu_bwd_130x128x512_fp16_diff", 130, (128, 512), True, torch.float16, True),
+                                             ("linsilu_bwd_64x16x128_bf16_nobias", 64, (16, 128), False, torch.bfloat16, False)):
+        torch.manual_seed(0)
+        u, v, q, k, x, w, bias, lo, split = rb.get_data(m, dim[0], dim[1], has_bias, dt, diff)
+        mixed = torch.cat((u, v, q, k), dim=-1)
+        xg32, wg32, bg32 = rb.ln_linear_silu_backward_golden_cpu(mixed, x, w, bias, lo)
+        xg16, wg16, bg16 = rb.ln_linear_silu_backward_npu(mixed, x, w, bias, lo, dt)
+        as16 = (lambda t: t) if dt == torch.bfloat16 else (lambda t: t.float())   # fp16 is stored as fp32 (exact)
+        arrays = dict(user_grad=as16(u), value_grad=as16(v), query_grad=as16(q), key_grad=as16(k), x=as16(x),
+                      weight=as16(w), bias=bias, linear_output=as16(lo), split=np.array(split, dtype=np.int64),
+                      is_fp16=np.int64(dt == torch.float16), x_grad_fp32=xg32, weight_grad_fp32=wg32, bias_grad_fp32=bg32,
+                      x_grad_lowp=xg16.float(), weight_grad_lowp=wg16.float(), bias_grad_lowp=bg16)
+        path = os.path.join(HERE, name + ".npz")
+        _store(path, arrays)
+        print(f"{name:36s} {os.path.getsize(path) / 1024:8.1f} KiB")
+
+
 # name, B, heads (q, k), dim, max new history, max targets, page size, previous history in the cache, dtype, mask
 PAGED_CASES = [
     dict(name="paged_fp32_p32", B=3, Hq=2, Hk=2, D=32, hist=100, cand=25, page=32, prev=False, dtype="fp32", mask_type=0),
@@ -403,8 +432,11 @@ def main_paged(ref_root, v1c):
 
 def main():
     if len(sys.argv) < 2:
-        sys.exit("usage: python tests/golden/make_golden.py <path to the ops-rec tree> [backward | ln_mul | in_linear_silu | paged]")
+        sys.exit("usage: python tests/golden/make_golden.py <path to the ops-rec tree> [backward | ln_mul | in_linear_silu | in_linear_silu_backward | paged]")
     ref_root = sys.argv[1]
+    if len(sys.argv) > 2 and sys.argv[2] == "in_linear_silu_backward":
+        main_in_linear_silu_backward(ref_root)
+        return
     if len(sys.argv) > 2 and sys.argv[2] == "paged":            # only the hstu_paged fixtures
         v1c, _ = _load_reference(ref_root)
         main_paged(ref_root, v1c)
@@ -422,6 +454,7 @@ def main():
     main_backward(ref_root, v1c)
     main_ln_mul(ref_root)
     main_in_linear_silu(ref_root)
+    main_in_linear_silu_backward(ref_root)
     main_paged(ref_root, v1c)
     for case in CASES:
         arrays = build_case(case, v1c, v2b)
