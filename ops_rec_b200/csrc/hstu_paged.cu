@@ -21,7 +21,7 @@ namespace hstu {
 namespace {
 
 constexpr int kGatherThreads = 256;
-constexpr int kGatherRowsPerWarp = 4;   // consecutive staging rows per warp (mostly of one sequence: one look-up)
+constexpr int kGatherRows = 64;   // consecutive staging rows per CTA
 
 struct GatherParams {
   const unsigned char* cache;   // [pages, 2, page_size, heads_k, dim]
@@ -39,71 +39,83 @@ struct GatherParams {
   int row_bytes;                // heads_k * dim * element size
 };
 
-template <typename V>
-__device__ __forceinline__ void copy_row(unsigned char* dst, const unsigned char* src, int row_bytes, int lane) {
-  for (int i = lane * static_cast<int>(sizeof(V)); i < row_bytes; i += 32 * static_cast<int>(sizeof(V)))
-    *reinterpret_cast<V*>(dst + i) = src ? *reinterpret_cast<const V*>(src + i) : V{};
-}
-
-// One warp per kGatherRowsPerWarp consecutive rows of the staging tensors (grid.y = 0: keys, 1: values).  The warp
-// finds the sequence of a row by bisection over seq_offset_k; rows behind the last sequence are zeros for one K/V
-// tile's worth (a tile that runs past the end of the data multiplies those rows by P = 0, which must not meet the
-// NaN bit patterns uninitialised memory may hold), the rest of the capacity is never read.
+// One CTA per kGatherRows consecutive rows of a staging tensor (grid.y = 0: keys, 1: values).
+//   phase 1  one thread per row finds the row's source: its sequence by bisection over seq_offset_k, then either a row
+//            of a cache page or a target row of the input; rows behind the last sequence become zeros for one K/V
+//            tile's worth (a tile that runs past the end of the data multiplies those rows by P = 0, which must not
+//            meet the NaN bit patterns uninitialised memory may hold), the rest of the capacity is never read
+//   phase 2  all threads copy: a warp takes four rows at a time and issues their loads before the first store
 template <typename V>
 __global__ void __launch_bounds__(kGatherThreads) hstu_paged_gather_kernel(const GatherParams p) {
+  __shared__ const unsigned char* s_src[kGatherRows];
+  __shared__ unsigned char s_mode[kGatherRows];   // 0: skip the row, 1: copy from s_src, 2: zeros
   const bool is_v = blockIdx.y != 0;
   unsigned char* out = is_v ? p.v_out : p.k_out;
-  const unsigned char* in = is_v ? p.v_in : p.k_in;
-  const int lane = threadIdx.x & 31;
-  const long long first = (static_cast<long long>(blockIdx.x) * (kGatherThreads / 32) + (threadIdx.x >> 5)) *
-                          kGatherRowsPerWarp;
-  long long k_end = load_index(p.offk, p.index_bytes, p.batch);
-  if (k_end < 0) k_end = 0;
-  if (k_end > p.capacity) k_end = p.capacity;
-  const long long page_bytes = static_cast<long long>(p.page_size) * p.row_bytes;
-  int b = -1;
-  long long k0 = 0, k1 = -1, q1 = 0, t = 0, pg0 = 0, pg1 = 0;
-  for (long long row = first; row < first + kGatherRowsPerWarp && row < p.capacity; ++row) {
-    if (row >= k_end) {
-      if (row < k_end + kTileN) copy_row<V>(out + row * p.row_bytes, nullptr, p.row_bytes, lane);
-      continue;
-    }
-    if (row >= k1) {
+  const long long first = static_cast<long long>(blockIdx.x) * kGatherRows;
+  if (threadIdx.x < kGatherRows) {
+    const long long row = first + threadIdx.x;
+    const unsigned char* src = nullptr;
+    unsigned char mode = 0;
+    long long k_end = load_index(p.offk, p.index_bytes, p.batch);
+    if (k_end < 0) k_end = 0;
+    if (k_end > p.capacity) k_end = p.capacity;
+    if (row < p.capacity && row >= k_end) {
+      mode = row < k_end + kTileN ? 2 : 0;
+    } else if (row < p.capacity) {
       // the last sequence whose first row is <= row (sequences of length 0 share their offset with the next one)
-      int lo = b < 0 ? 0 : b, hi = p.batch - 1;
+      int lo = 0, hi = p.batch - 1;
       while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
         if (load_index(p.offk, p.index_bytes, mid) <= row) lo = mid; else hi = mid - 1;
       }
-      b = lo;
-      k0 = load_index(p.offk, p.index_bytes, b);
-      k1 = load_index(p.offk, p.index_bytes, b + 1);
-      const long long q0 = load_index(p.offq, p.index_bytes, b);
-      q1 = load_index(p.offq, p.index_bytes, b + 1);
-      if (q1 > p.total_q) q1 = p.total_q;
-      t = p.tgt ? load_index(p.tgt, p.index_bytes, b) : 0;
-      if (t < 0) t = 0;
-      if (t > q1 - q0) t = q1 - q0 > 0 ? q1 - q0 : 0;
-      pg0 = load_index(p.page_offsets, p.index_bytes, b);
-      pg1 = load_index(p.page_offsets, p.index_bytes, b + 1);
-      if (pg0 < 0) pg0 = 0;
-      if (pg1 > p.num_page_ids) pg1 = p.num_page_ids;
-    }
-    if (row < k0 || row >= k1) continue;   // offsets that are not monotone (flagged by the pre-pass): nothing to copy
-    const long long r = row - k0, cache_len = (k1 - k0) - t;
-    const unsigned char* src = nullptr;    // null: zeros (an inconsistent table has no source for this row)
-    if (r < cache_len) {
-      const long long slot = pg0 + r / p.page_size;
-      if (slot < pg1) {
-        const long long pid = load_index(p.page_ids, p.index_bytes, slot);
-        if (pid >= 0 && pid < p.num_pages)
-          src = p.cache + (pid * 2 + (is_v ? 1 : 0)) * page_bytes + (r % p.page_size) * p.row_bytes;
+      const int b = lo;
+      const long long k0 = load_index(p.offk, p.index_bytes, b), k1 = load_index(p.offk, p.index_bytes, b + 1);
+      if (row >= k0 && row < k1) {   // (offsets that are not monotone, flagged by the pre-pass, leave rows uncovered)
+        mode = 2;                    // zeros unless a source exists (an inconsistent table has none for this row)
+        const long long q0 = load_index(p.offq, p.index_bytes, b);
+        long long q1 = load_index(p.offq, p.index_bytes, b + 1);
+        if (q1 > p.total_q) q1 = p.total_q;
+        long long t = p.tgt ? load_index(p.tgt, p.index_bytes, b) : 0;
+        if (t < 0) t = 0;
+        if (t > q1 - q0) t = q1 - q0 > 0 ? q1 - q0 : 0;
+        const long long r = row - k0, cache_len = (k1 - k0) - t;
+        if (r < cache_len) {
+          long long pg0 = load_index(p.page_offsets, p.index_bytes, b), pg1 = load_index(p.page_offsets, p.index_bytes, b + 1);
+          if (pg0 < 0) pg0 = 0;
+          if (pg1 > p.num_page_ids) pg1 = p.num_page_ids;
+          const long long slot = pg0 + r / p.page_size;
+          if (slot < pg1) {
+            const long long pid = load_index(p.page_ids, p.index_bytes, slot);
+            if (pid >= 0 && pid < p.num_pages) {
+              src = p.cache + ((pid * 2 + (is_v ? 1 : 0)) * p.page_size + r % p.page_size) * p.row_bytes;
+              mode = 1;
+            }
+          }
+        } else {
+          const long long at = q1 - t + (r - cache_len);
+          if (at >= 0 && at < p.total_q) {
+            src = (is_v ? p.v_in : p.k_in) + at * p.row_bytes;
+            mode = 1;
+          }
+        }
       }
-    } else {
-      const long long at = q1 - t + (r - cache_len);
-      if (at >= 0 && at < p.total_q) src = in + at * p.row_bytes;
     }
-    copy_row<V>(out + row * p.row_bytes, src, p.row_bytes, lane);
+    s_src[threadIdx.x] = src;
+    s_mode[threadIdx.x] = mode;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kWarps = kGatherThreads / 32;
+  constexpr int kBatch = 4;   // rows in flight per warp
+  for (int r0 = warp * kBatch; r0 < kGatherRows; r0 += kWarps * kBatch) {
+    for (int i = lane * static_cast<int>(sizeof(V)); i < p.row_bytes; i += 32 * static_cast<int>(sizeof(V))) {
+      V v[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) v[j] = s_mode[r0 + j] == 1 ? *reinterpret_cast<const V*>(s_src[r0 + j] + i) : V{};
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j)
+        if (s_mode[r0 + j]) *reinterpret_cast<V*>(out + (first + r0 + j) * p.row_bytes + i) = v[j];
+    }
   }
 }
 
@@ -132,8 +144,7 @@ cudaError_t launch_paged_gather(const KParams& p, const void* kv_cache, const vo
   g.batch = p.batch;
   g.page_size = p.page_size;
   g.row_bytes = p.hk * p.dqk * esize;
-  const long long rows_per_cta = static_cast<long long>(kGatherThreads / 32) * kGatherRowsPerWarp;
-  const dim3 grid(static_cast<unsigned>((capacity + rows_per_cta - 1) / rows_per_cta), 2, 1);
+  const dim3 grid(static_cast<unsigned>((capacity + kGatherRows - 1) / kGatherRows), 2, 1);
   const uintptr_t align = reinterpret_cast<uintptr_t>(kv_cache) | reinterpret_cast<uintptr_t>(k_in) |
                           reinterpret_cast<uintptr_t>(v_in) | reinterpret_cast<uintptr_t>(k_out) |
                           reinterpret_cast<uintptr_t>(v_out) | static_cast<uintptr_t>(g.row_bytes);
