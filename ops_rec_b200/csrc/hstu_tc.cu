@@ -283,6 +283,27 @@ __device__ __forceinline__ uint32_t visible_bits(const RowBounds& rb, int j0) {
   return low_bits(rb.lim1 - j0) | (low_bits(rb.hi2 + 1 - j0) & ~low_bits(rb.lo2 - j0));
 }
 
+// kBias == 2, a sequence's last K tile: the 16-column slice that contains the sequence end is not added by the tensor
+// cores - whatever lies in the bias buffer beyond column lk would reach the slice's visible columns through the
+// identity product (0 x NaN).  The warps that own the slice add its n (< 16) in-sequence bias values of their rows to
+// S in tensor memory before they compute P: load 16 columns, add, store back.  `bv` holds the slice as packed
+// pairs, fetched from global memory before the wait for the scores (zeros for rows outside the sequence).  Called by
+// whole warps (the tensor-memory accesses are warp-wide); kept out of p_half so that tiles without such a slice
+// execute none of it.
+template <typename T>
+__device__ __forceinline__ void add_end_slice(uint32_t t_slice, const uint32_t (&bv)[8], int n) {
+  uint32_t v[16];
+  ptx::tmem_ld16(t_slice, v);
+  ptx::tmem_wait_ld();
+#pragma unroll
+  for (int e = 0; e < 15; ++e) {
+    const float2 b2 = Pack<T>::unpack(bv[e >> 1]);
+    if (e < n) v[e] = __float_as_uint(__uint_as_float(v[e]) + ((e & 1) ? b2.y : b2.x));
+  }
+  ptx::tmem_st16(t_slice, v);
+  ptx::tmem_wait_st();
+}
+
 // This thread's 64 columns of one 128 x 128 score tile, its row: S (TMEM, fp32) -> P (TMEM, packed 16-bit).
 // Group g reads the S columns [64g, 64g+64) and writes its half of P inside its own column range (keys 0..63 at
 // columns 0..31, keys 64..127 at columns 64..95), so neither group ever overwrites scores the other still has to
@@ -290,16 +311,11 @@ __device__ __forceinline__ uint32_t visible_bits(const RowBounds& rb, int j0) {
 // cuts through (kMasked) every warp classifies each 32 x 32 chunk of its rows: all visible -> plain path, nothing
 // visible -> zeros without any arithmetic, mixed -> per-element select.
 //
-// kBias == 2: the bias is already inside S (added by the tensor cores) except for the one 16-column slice of a
-// sequence's last K tile that contains the sequence end - the issuer leaves that slice out, because whatever lies
-// in the bias buffer beyond column lk would reach the visible columns of the slice through the identity product
-// (0 x NaN).  The thread that owns that slice of its row (fix_ch = the 32-column chunk of this thread that holds
-// it, -1 = none; fix_lo = 0 or 16, its position inside the chunk) adds the fix_n bias values that lie inside the
-// sequence; the caller has fetched the slice into fixv (two values per word) before it waited for the scores.
+// kBias == 2: the bias is already inside S when this runs (added by the tensor cores, and for the one slice that
+// holds a sequence's end by add_end_slice below).
 template <typename T, int kBias, bool kMasked>
 __device__ __forceinline__ void p_half(uint32_t t_s, int grp, int c0, const BiasRow& br, const RowBounds& rb,
-                                       float c_in, float c_bias, float scale, uint32_t bar_p0, int fix_ch,
-                                       int fix_lo, int fix_n, const uint32_t (&fixv)[8]) {
+                                       float c_in, float c_bias, float scale, uint32_t bar_p0) {
   uint32_t sbuf[2][32];
   uint32_t bv[16];
   uint32_t pr[16];
@@ -319,22 +335,6 @@ __device__ __forceinline__ void p_half(uint32_t t_s, int grp, int c0, const Bias
     if ((kBias == 1 || kBias == 3) && !all_off) load_bias32<T>(br, j0 + ch * 32, bv);
     ptx::tmem_wait_ld_dep(sbuf[ch]);
     if (ch == 0) ptx::tmem_ld32(s_col + 32, sbuf[1]);
-    if (kBias == 2 && fix_ch == ch) {
-      if (fix_lo == 0) {
-#pragma unroll
-        for (int e = 0; e < 15; ++e) {
-          const float2 b2 = Pack<T>::unpack(fixv[e >> 1]);
-          if (e < fix_n) sbuf[ch][e] = __float_as_uint(__uint_as_float(sbuf[ch][e]) + ((e & 1) ? b2.y : b2.x));
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 15; ++e) {
-          const float2 b2 = Pack<T>::unpack(fixv[e >> 1]);
-          if (e < fix_n)
-            sbuf[ch][16 + e] = __float_as_uint(__uint_as_float(sbuf[ch][16 + e]) + ((e & 1) ? b2.y : b2.x));
-        }
-      }
-    }
     if (all_on) {
       silu_chunk<T, kBias, false>(sbuf[ch], bv, pr, c_in, c_bias, scale, 0u);
     } else if (all_off) {
@@ -823,13 +823,13 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           const uint32_t t_s = tmem + lane_base + (t == 0 ? kColS0 : kColS1);
           const uint32_t bar_p = ptx::smem_u32(&bars->p_full[t][0]);
           // kBias == 2: the 16-column slice of the sequence's last K tile that holds the sequence end (if any) is
-          // added here, not by the tensor cores; its owner fetches it now, before it waits for the scores
+          // added here, not by the tensor cores; the group that owns it fetches it now, before it waits for the scores
           const int rem = it.s.lk - c0;
           const int fix_n = (kBias == 2 && rem < kTileN) ? (rem & 15) : 0;
           const int fix_col = rem & ~15;
-          const bool fix_mine = fix_n > 0 && (fix_col >> 6) == grp && row_ok[t];
-          uint32_t fixv[8];
-          if (kBias == 2 && fix_mine) {
+          const bool fix_here = fix_n > 0 && (fix_col >> 6) == grp;   // the same for every thread of the group
+          uint32_t fixv[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+          if (kBias == 2 && fix_here && row_ok[t]) {
             const T* src = static_cast<const T*>(p.bias) + bias_row[t] + c0 + fix_col;
             if (c0 + fix_col + 16 <= p.maxk) {  // 32-byte aligned: the rows are 16-byte aligned and c0 + fix_col is a multiple of 16
               const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(src));
@@ -846,16 +846,16 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
               }
             }
           }
-          const int fix_ch = (kBias == 2 && fix_mine) ? ((fix_col >> 5) & 1) : -1;
           w.wait(ptx::smem_u32(&bars->s_full[t]), s_uses[t] & 1u);
           if (w.aborted()) break;  // (the item feed then ends the outer loops)
           ++s_uses[t];
           ptx::tc_fence_after();
           const BiasRow br{p.bias, bias_row[t], row_ok[t], bias_vec_ok != 0, p.maxk, it.s.lk};
+          if (kBias == 2 && fix_here) add_end_slice<T>(t_s + fix_col, fixv, fix_n);
           if (full)
-            p_half<T, kBias, false>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p, fix_ch, fix_col & 16, fix_n, fixv);
+            p_half<T, kBias, false>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p);
           else
-            p_half<T, kBias, true>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p, fix_ch, fix_col & 16, fix_n, fixv);
+            p_half<T, kBias, true>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p);
         }
       }
       if (!o0_stored) store_o(0, out0);

@@ -55,8 +55,8 @@ def test_cfg4_sampled_sequences_and_properties():
     out, status = _run(kw)
     assert status == 0 and torch.isfinite(out.float()).all()
     order = np.argsort(w.lengths)
-    picks = [int(order[0]), int(order[len(order) // 2]), int(order[-8]), int(order[-1])]
-    _check_sample(w, kw, out, picks, heads=[0, 7])
+    picks = [int(order[0]), int(order[len(order) // 4]), int(order[len(order) // 2]), int(order[-8]), int(order[-1])]
+    _check_sample(w, kw, out, picks, heads=[0, 3, 7])
     # bitwise reproducible
     out2, _ = _run(kw)
     assert torch.equal(out, out2)
@@ -87,8 +87,11 @@ def test_cfg5_sampled_sequences_shared_bias_and_targets():
     out, status = _run(kw)
     assert status == 0 and torch.isfinite(out.float()).all()
     order = np.argsort(w.lengths)
-    picks = [int(order[0]), int(order[1000]), int(order[2048]), int(order[3500]), int(order[-1])]
-    _check_sample(w, kw, out, picks, heads=[0, 3])
+    # 40 sequences spread over the sorted lengths (shortest, longest and the quantiles between), every head
+    ranks = sorted(set(np.linspace(0, len(order) - 1, 38).astype(int).tolist() + [1, len(order) - 2]))
+    picks = [int(order[r]) for r in ranks]
+    assert len(picks) >= 32
+    _check_sample(w, kw, out, picks, heads=range(kw["q"].shape[1]))
     out2, _ = _run(kw)
     assert torch.equal(out, out2)
 
