@@ -541,16 +541,37 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
               ptx::mma_ts(col_o, col_s + (ks >> 2) * 64 + (ks & 3) * 8, vbase + static_cast<uint64_t>((ks * 2048) >> 4),
                           idesc_pv, acc);
             };
-            pv(0, step > 1 ? 1u : 0u);
-            pv(1, 1u);
-            pv(4, 1u);
-            pv(5, 1u);
-            w.wait(bar_p_half1, p_uses & 1u);
-            ptx::tc_fence_after();
-            pv(2, 1u);
-            pv(3, 1u);
-            pv(6, 1u);
-            pv(7, 1u);
+            // A sequence's last K/V tile: only the 16-key steps that hold keys of the sequence.  The rows behind them
+            // belong to the next sequence (P is 0 there, but 0 x NaN is not); the few rows between the sequence end
+            // and the end of its last 16-key step have been zeroed in shared memory by the P/O groups.
+            const int ksteps = (it.s.lk - (step - 1) * kTileN + 15) >> 4;
+            if (ksteps >= 8) {
+              pv(0, step > 1 ? 1u : 0u);
+              pv(1, 1u);
+              pv(4, 1u);
+              pv(5, 1u);
+              w.wait(bar_p_half1, p_uses & 1u);
+              ptx::tc_fence_after();
+              pv(2, 1u);
+              pv(3, 1u);
+              pv(6, 1u);
+              pv(7, 1u);
+            } else {
+              // (predicated instructions, not branches: a branch between two MMAs costs the issuing thread ~40 cycles)
+              auto pv_if = [&](int ks) {
+                ptx::mma_ts_if(ks < ksteps ? 1u : 0u, col_o, col_s + (ks >> 2) * 64 + (ks & 3) * 8,
+                               vbase + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv, 1u);
+              };
+              pv(0, step > 1 ? 1u : 0u);
+              pv_if(1);
+              pv_if(4);
+              pv_if(5);
+              w.wait(bar_p_half1, p_uses & 1u);
+              ptx::tc_fence_after();
+              pv_if(2);
+              pv_if(3);
+              pv_if(6);
+            }
             ++p_uses;
             if (step == n) {
               ptx::mma_commit(bar_o_full);
@@ -789,6 +810,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       }
     };
     // the S tiles arrive in the order the MMA issuers alternate: tile 0 step j, tile 1 step j, tile 0 step j+1 ..
+    uint32_t ring_base = 0;   // position of the current item's first K tile in the K/V ring (as the issuers count it)
     for (Item it;;) {
       if (!feed.next(it)) break;
       int i_row[2];
@@ -822,6 +844,24 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           const bool full = tile_is_full(it.s, tile_r0, kTileM, c0, kTileN, p.mask_type, p.group);
           const uint32_t t_s = tmem + lane_base + (t == 0 ? kColS0 : kColS1);
           const uint32_t bar_p = ptx::smem_u32(&bars->p_full[t][0]);
+          // A sequence's last K/V tile holds rows of the NEXT sequence behind the sequence end.  P is 0 there, but
+          // 0 x NaN is not: the issuer leaves out the 16-key steps that lie wholly behind the end, and group 1 zeroes
+          // the V rows between the end and the end of its 16-key step here, in shared memory, once the tile has
+          // landed - ordered before this tile's P.V by the hand-over of P (generic-proxy stores, proxy fence, arrive).
+          // (Measured alternatives, all slower: one warp instead of the group, the zeroing right before the first
+          // hand-over, one polling lane per warp.)
+          if (grp == 1 && it.s.lk - c0 < kTileN && ((it.s.lk - c0) & 15) != 0) {
+            const int z0 = it.s.lk - c0, z1 = (z0 + 15) & ~15;
+            const uint32_t pos_v = ring_base + 2u * j + 1u, st_v = pos_v % C::kStages;
+            w.wait(ptx::smem_u32(&bars->kv_full[st_v]), (pos_v / C::kStages) & 1u);
+            if (w.aborted()) break;
+            const int per_box = (z1 - z0) * 8;   // 16-byte pieces per 64-column box (a row of a box is 128 bytes)
+            for (int i = row; i < per_box * (D / 64); i += kTileM) {
+              const int box = i / per_box, piece = i - box * per_box;
+              ptx::st_shared_zero16(sm_ring + st_v * C::kTileBytes + box * C::kHalfBytes + z0 * 128 + piece * 16);
+            }
+            ptx::fence_proxy_async();
+          }
           // kBias == 2: the 16-column slice of the sequence's last K tile that holds the sequence end (if any) is
           // added here, not by the tensor cores; the group that owns it fetches it now, before it waits for the scores
           const int rem = it.s.lk - c0;
@@ -860,6 +900,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       }
       if (!o0_stored) store_o(0, out0);
       store_o(1, OutTile{it.s.q0, it.s.lq, it.r0 + kTileM, it.h, it.n1});
+      ring_base += 2u * it.nmax;
     }
     if (C::kOutBytes > 0 && lane == 0) ptx::bulk_wait<0>();  // this thread's TMA stores have completed
   }

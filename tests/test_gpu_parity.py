@@ -207,6 +207,28 @@ def test_results_are_bitwise_reproducible():
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("poison", [float("nan"), float("inf")])
+@pytest.mark.parametrize("D,dtype,rab", [(128, BF16, None), (64, BF16, "batch"), (128, FP16, "shared3"), (32, FP32, None)])
+def test_non_finite_values_of_a_neighbouring_sequence_do_not_leak(D, dtype, rab, poison):
+    """The reference golden slices every sequence out of the packed tensors, so nothing of one sequence can reach
+    another.  Here a K/V tile that runs past a sequence end holds the next sequence's rows: with every second
+    sequence's q, k and v made non-finite, the others must come out finite and bit for bit as without the poison."""
+    args = make_case(9, 2, 2, D, D, 3, 420, dtype, seed=23, rab=rab)
+    clean, status = run_cabi(args)
+    assert status == 0
+    off = args["seq_offset"].tolist()
+    bad = dict(args, q=args["q"].clone(), k=args["k"].clone(), v=args["v"].clone())
+    for b in range(1, 9, 2):
+        for name in ("q", "k", "v"):
+            bad[name][off[b]:off[b + 1]] = poison
+    out, status = run_cabi(bad)
+    assert status == 0
+    for b in range(0, 9, 2):
+        rows = slice(off[b], off[b + 1])
+        assert torch.isfinite(out[rows].float()).all(), f"sequence {b} (L={off[b + 1] - off[b]})"
+        assert torch.equal(out[rows], clean[rows]), f"sequence {b}"
+
+
 def test_output_rows_outside_the_call_are_untouched():
     args = to_cuda(make_case(5, 2, 2, 128, 128, 1, 300, BF16, seed=19))
     T = args["q"].shape[0]
