@@ -289,7 +289,8 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // (an elected thread, not `lane == 0`: the compiler then keeps descriptors and barrier addresses in uniform registers)
+    if (ptx::elect_one()) {
       constexpr uint32_t idesc_t = ptx::umma_idesc_f16(BPack<T>::kFormat, kTileM, kTileN, 0);
       constexpr uint32_t idesc_acc = ptx::umma_idesc_f16(BPack<T>::kFormat, kTileM, D, 1);
       constexpr uint64_t kDescK = ptx::umma_desc_sw128_hi(16, 1024);           // K-major tiles

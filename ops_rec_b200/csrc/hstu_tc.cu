@@ -304,6 +304,14 @@ __device__ __forceinline__ void add_end_slice(uint32_t t_slice, const uint32_t (
   ptx::tmem_wait_st();
 }
 
+// Zeroes `pieces` 16-byte pieces from shared-memory address `first` on, in each of `boxes` regions `box_bytes` apart
+// (the rows of a V tile behind a sequence end); called by the 128 threads of a P/O group, `tid` = 0..127.
+__device__ __noinline__ void zero_v_rows(uint32_t first, int pieces, int tid, int boxes, int box_bytes) {
+  for (int i = tid; i < pieces; i += kTileM)
+    for (int b = 0; b < boxes; ++b) ptx::st_shared_zero16(first + b * box_bytes + i * 16);
+  ptx::fence_proxy_async();
+}
+
 // This thread's 64 columns of one 128 x 128 score tile, its row: S (TMEM, fp32) -> P (TMEM, packed 16-bit).
 // Group g reads the S columns [64g, 64g+64) and writes its half of P inside its own column range (keys 0..63 at
 // columns 0..31, keys 64..127 at columns 64..95), so neither group ever overwrites scores the other still has to
@@ -481,7 +489,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     // Each chain (S_t = Q_t.K^T, then O_t += P_t.V) is issued by its own thread: a barrier poll costs the
     // issuing thread ~130 cycles and the tensor pipe queues only a few instructions, so while one issuer
     // waits for its P tile the other keeps the pipe fed.  The chains share nothing but the read-only K/V tiles.
-    if (lane == 0) {
+    // The thread is an elected one, not `lane == 0`: the compiler then knows that a single thread runs this code
+    // and keeps the descriptors and barrier addresses in uniform registers (cfg5-shaped batches: -18 % time).
+    // (The same for the producer and the scheduler was measured slower.)
+    if (ptx::elect_one()) {
       const int t = warp == 1 ? 0 : 1;
       constexpr uint32_t idesc_qk = ptx::umma_idesc_f16(Pack<T>::kFormat, kTileM, kTileN, 0);
       constexpr uint32_t idesc_pv = ptx::umma_idesc_f16(Pack<T>::kFormat, kTileM, D, 1);
@@ -516,6 +527,13 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           const bool do_pv = has_v && step - 1 < n, do_qk = has_k && step < n;
           const uint32_t bar_vf = ptx::smem_u32(&bars->kv_full[st_v]), par_vf = (pos_v / C::kStages) & 1u;
           const uint32_t bar_kf = ptx::smem_u32(&bars->kv_full[st_k]), par_kf = (pos_k / C::kStages) & 1u;
+          // A V tile that is cut by its sequence's end is waited for a step early, together with its K tile: the
+          // completion of S(step) then tells the P/O groups that V(step) has landed too (they zero the rows behind
+          // the end in it without having to poll its barrier).  (Waiting early for every V tile costs ring depth:
+          // -14 % on long sequences.)
+          const bool cut_v = has_k && it.s.lk - step * kTileN < kTileN;
+          const uint32_t bar_vc = ptx::smem_u32(&bars->kv_full[(pos_k + 1u) % C::kStages]);
+          const uint32_t par_vc = ((pos_k + 1u) / C::kStages) & 1u;
           // The two issuers run free of each other: the P/O groups serve the tiles in a fixed order (tile 0,
           // tile 1, tile 0 ...), so the P tiles - and with them the MMA bursts - alternate by themselves.
           // poll everything this step needs at once
@@ -525,6 +543,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           const bool ok_b = (kBias == 2 && do_qk) ? ptx::mbar_try_wait(bar_bias_full, b_uses & 1u) : true;
           w.wait_polled(ok_v, bar_vf, par_vf);
           w.wait_polled(ok_k, bar_kf, par_kf);
+          if (cut_v) w.wait(bar_vc, par_vc);
           if (kBias == 2 && do_qk) w.wait_polled(ok_b, bar_bias_full, b_uses & 1u);
           w.wait_polled(ok_p, bar_p_full, p_uses & 1u);
           if (do_pv && step == 1) w.wait(bar_o_free, (o_uses & 1u) ^ 1u);
@@ -541,37 +560,16 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
               ptx::mma_ts(col_o, col_s + (ks >> 2) * 64 + (ks & 3) * 8, vbase + static_cast<uint64_t>((ks * 2048) >> 4),
                           idesc_pv, acc);
             };
-            // A sequence's last K/V tile: only the 16-key steps that hold keys of the sequence.  The rows behind them
-            // belong to the next sequence (P is 0 there, but 0 x NaN is not); the few rows between the sequence end
-            // and the end of its last 16-key step have been zeroed in shared memory by the P/O groups.
-            const int ksteps = (it.s.lk - (step - 1) * kTileN + 15) >> 4;
-            if (ksteps >= 8) {
-              pv(0, step > 1 ? 1u : 0u);
-              pv(1, 1u);
-              pv(4, 1u);
-              pv(5, 1u);
-              w.wait(bar_p_half1, p_uses & 1u);
-              ptx::tc_fence_after();
-              pv(2, 1u);
-              pv(3, 1u);
-              pv(6, 1u);
-              pv(7, 1u);
-            } else {
-              // (predicated instructions, not branches: a branch between two MMAs costs the issuing thread ~40 cycles)
-              auto pv_if = [&](int ks) {
-                ptx::mma_ts_if(ks < ksteps ? 1u : 0u, col_o, col_s + (ks >> 2) * 64 + (ks & 3) * 8,
-                               vbase + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv, 1u);
-              };
-              pv(0, step > 1 ? 1u : 0u);
-              pv_if(1);
-              pv_if(4);
-              pv_if(5);
-              w.wait(bar_p_half1, p_uses & 1u);
-              ptx::tc_fence_after();
-              pv_if(2);
-              pv_if(3);
-              pv_if(6);
-            }
+            pv(0, step > 1 ? 1u : 0u);
+            pv(1, 1u);
+            pv(4, 1u);
+            pv(5, 1u);
+            w.wait(bar_p_half1, p_uses & 1u);
+            ptx::tc_fence_after();
+            pv(2, 1u);
+            pv(3, 1u);
+            pv(6, 1u);
+            pv(7, 1u);
             ++p_uses;
             if (step == n) {
               ptx::mma_commit(bar_o_full);
@@ -844,24 +842,6 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           const bool full = tile_is_full(it.s, tile_r0, kTileM, c0, kTileN, p.mask_type, p.group);
           const uint32_t t_s = tmem + lane_base + (t == 0 ? kColS0 : kColS1);
           const uint32_t bar_p = ptx::smem_u32(&bars->p_full[t][0]);
-          // A sequence's last K/V tile holds rows of the NEXT sequence behind the sequence end.  P is 0 there, but
-          // 0 x NaN is not: the issuer leaves out the 16-key steps that lie wholly behind the end, and group 1 zeroes
-          // the V rows between the end and the end of its 16-key step here, in shared memory, once the tile has
-          // landed - ordered before this tile's P.V by the hand-over of P (generic-proxy stores, proxy fence, arrive).
-          // (Measured alternatives, all slower: one warp instead of the group, the zeroing right before the first
-          // hand-over, one polling lane per warp.)
-          if (grp == 1 && it.s.lk - c0 < kTileN && ((it.s.lk - c0) & 15) != 0) {
-            const int z0 = it.s.lk - c0, z1 = (z0 + 15) & ~15;
-            const uint32_t pos_v = ring_base + 2u * j + 1u, st_v = pos_v % C::kStages;
-            w.wait(ptx::smem_u32(&bars->kv_full[st_v]), (pos_v / C::kStages) & 1u);
-            if (w.aborted()) break;
-            const int per_box = (z1 - z0) * 8;   // 16-byte pieces per 64-column box (a row of a box is 128 bytes)
-            for (int i = row; i < per_box * (D / 64); i += kTileM) {
-              const int box = i / per_box, piece = i - box * per_box;
-              ptx::st_shared_zero16(sm_ring + st_v * C::kTileBytes + box * C::kHalfBytes + z0 * 128 + piece * 16);
-            }
-            ptx::fence_proxy_async();
-          }
           // kBias == 2: the 16-column slice of the sequence's last K tile that holds the sequence end (if any) is
           // added here, not by the tensor cores; the group that owns it fetches it now, before it waits for the scores
           const int rem = it.s.lk - c0;
@@ -890,6 +870,15 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           if (w.aborted()) break;  // (the item feed then ends the outer loops)
           ++s_uses[t];
           ptx::tc_fence_after();
+          // A sequence's last K/V tile holds rows of the NEXT sequence behind the sequence end.  P is 0 there, but
+          // 0 x NaN is not, so group 1 zeroes those V rows in shared memory before it hands P over (generic-proxy
+          // stores, proxy fence, arrive: ordered before this tile's P.V).  The tile has landed: the issuer waited for
+          // it before it issued the S tile whose completion this thread has just seen.
+          // (The stores sit in a function of their own, not inlined: inlined, their mere presence cost the P loop 5 %
+          // on batches that hardly ever run them.)
+          if (grp == 1 && rem < kTileN)
+            zero_v_rows(sm_ring + ((ring_base + 2u * j + 1u) % C::kStages) * C::kTileBytes + rem * 128,
+                        (kTileN - rem) * 8, row, C::kHalves, C::kHalfBytes);
           const BiasRow br{p.bias, bias_row[t], row_ok[t], bias_vec_ok != 0, p.maxk, it.s.lk};
           if (kBias == 2 && fix_here) add_end_slice<T>(t_s + fix_col, fixv, fix_n);
           if (full)

@@ -140,7 +140,8 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // (an elected thread, not `lane == 0`: the compiler then keeps descriptors and barrier addresses in uniform registers)
+    if (ptx::elect_one()) {
       constexpr uint32_t idesc = ptx::umma_idesc_f16(LsPack<T>::kFormat, 128, kLsTile, 0);
       constexpr uint64_t kDescK = ptx::umma_desc_sw128_hi(16, 1024);
       for (int c = 0; c < chunks; ++c) {

@@ -73,6 +73,17 @@ template <int N> __device__ __forceinline__ void bulk_wait() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 // make this thread's shared-memory writes visible to the async proxy (TMA) before it is asked to read them
+// True in exactly one lane of a converged warp.  Unlike `lane == 0` the compiler sees that a single thread runs the
+// guarded code and keeps its operands in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 // 16 zero bytes at a 16-byte aligned shared-memory address
 __device__ __forceinline__ void st_shared_zero16(uint32_t addr) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
