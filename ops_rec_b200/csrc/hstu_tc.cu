@@ -647,9 +647,18 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         ptx::mbar_arrive(ptx::smem_u32(&bars->sched_full[n % kSchedStages]));
         return more;
       };
+      // How far this CTA draws ahead of the item its P/O groups have started: an item drawn is an item no other CTA
+      // can take, so with few items per CTA a deep look-ahead hands the whole list to the CTAs that start first
+      // (cfg2: 392 items, 148 CTAs, 8 slots - a third of the CTAs took everything).  One item of look-ahead is
+      // what the loads need; more only pays when items are short and plentiful.
+      const long long per_cta = num_items / (4 * static_cast<long long>(gridDim.x));
+      const uint32_t ahead = static_cast<uint32_t>(per_cta < 1 ? 1 : (per_cta > kSchedStages ? kSchedStages : per_cta));
       if (kBias != 2) {
         for (uint32_t n = 0;; ++n) {
           w.wait(ptx::smem_u32(&bars->sched_free[n % kSchedStages]), ((n / kSchedStages) & 1u) ^ 1u);
+          // (slot n - ahead has been read by every role: its P/O groups have started that item)
+          if (ahead < kSchedStages && n >= ahead)
+            w.wait(ptx::smem_u32(&bars->sched_free[(n - ahead) % kSchedStages]), ((n - ahead) / kSchedStages) & 1u);
           if (!publish(n)) break;
         }
       } else {
@@ -669,7 +678,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           bool progress = false;
           if (!sched_done &&
               ptx::mbar_try_wait(ptx::smem_u32(&bars->sched_free[n_pub % kSchedStages]),
-                                 ((n_pub / kSchedStages) & 1u) ^ 1u)) {
+                                 ((n_pub / kSchedStages) & 1u) ^ 1u) &&
+              (ahead >= kSchedStages || n_pub < ahead ||
+               ptx::mbar_try_wait(ptx::smem_u32(&bars->sched_free[(n_pub - ahead) % kSchedStages]),
+                                                   ((n_pub - ahead) / kSchedStages) & 1u))) {
             if (!publish(n_pub)) sched_done = true;
             ++n_pub;
             progress = true;
