@@ -31,6 +31,8 @@
 
 #include <mutex>
 
+#include <type_traits>
+
 #include "hstu_common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -637,12 +639,16 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       long long num_items = p.ws_header[1];
       if (num_items > p.item_capacity) num_items = p.item_capacity;  // never read past the list (inconsistent offsets)
       // Draw the next item from the global counter and publish it in ring slot n % kSchedStages.
+      uint32_t q0_uses = 0;      // items published so far whose Q tile 0 visits at least one K tile
+      bool last_has_q0 = false;  // ... the last one published among them
       auto publish = [&](uint32_t n) -> bool {
         const long long idx = static_cast<long long>(atomicAdd(&p.ws_header[2], 1u));
         const bool more = idx < num_items && !*reinterpret_cast<volatile int*>(&bars->abort_flag);
         Item it;
         if (more) it = load_item(p, idx);
         else it.valid = 0;
+        last_has_q0 = more && it.n0 > 0;
+        q0_uses += last_has_q0 ? 1u : 0u;
         bars->sched_item[n % kSchedStages] = it;
         ptx::mbar_arrive(ptx::smem_u32(&bars->sched_full[n % kSchedStages]));
         return more;
@@ -659,6 +665,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
           // (slot n - ahead has been read by every role: its P/O groups have started that item)
           if (ahead < kSchedStages && n >= ahead)
             w.wait(ptx::smem_u32(&bars->sched_free[(n - ahead) % kSchedStages]), ((n - ahead) / kSchedStages) & 1u);
+          // With one item of look-ahead, draw the next item only when the last one is about to end (the Q tile 0
+          // buffer is released with its last Q.K^T): the loads of the next item cannot start before that anyway,
+          // and an item still in the list can go to a CTA that has run dry.
+          if (ahead == 1 && n >= 1 && last_has_q0) w.wait(ptx::smem_u32(&bars->q_free[0]), (q0_uses - 1u) & 1u);
           if (!publish(n)) break;
         }
       } else {
@@ -667,21 +677,30 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         // products have completed, early in the step) it requests that tile's next bias tile - so a bias tile has
         // a whole step to arrive, whatever the other loads are waiting for.  A cursor holds its item's ring slot
         // (it counts as one reader) until the item's last bias tile is requested.
+        // (The loop exists twice, with and without the look-ahead limits: this thread's reaction time is the
+        // latency of every bias tile, and the extra polls cost 5 % on batches of many short items.)
+        uint32_t loads[2] = {0, 0};
+        auto run = [&](auto limited) {
+        constexpr bool kLimited = decltype(limited)::value;
         uint32_t n_pub = 0;
         bool sched_done = false;
-        uint32_t cur_item[2] = {0, 0}, loads[2] = {0, 0};
+        uint32_t cur_item[2] = {0, 0};
         int cur_j[2] = {0, 0};
         bool cur_done[2] = {false, false};
         long long t_progress = clock64();
         unsigned spins = 0;
         while (!(sched_done && cur_done[0] && cur_done[1])) {
           bool progress = false;
-          if (!sched_done &&
-              ptx::mbar_try_wait(ptx::smem_u32(&bars->sched_free[n_pub % kSchedStages]),
-                                 ((n_pub / kSchedStages) & 1u) ^ 1u) &&
-              (ahead >= kSchedStages || n_pub < ahead ||
-               ptx::mbar_try_wait(ptx::smem_u32(&bars->sched_free[(n_pub - ahead) % kSchedStages]),
-                                                   ((n_pub - ahead) / kSchedStages) & 1u))) {
+          bool may_draw = !sched_done && ptx::mbar_try_wait(ptx::smem_u32(&bars->sched_free[n_pub % kSchedStages]),
+                                                            ((n_pub / kSchedStages) & 1u) ^ 1u);
+          if (kLimited && may_draw) {
+            if (n_pub >= ahead)
+              may_draw = ptx::mbar_try_wait(ptx::smem_u32(&bars->sched_free[(n_pub - ahead) % kSchedStages]),
+                                            ((n_pub - ahead) / kSchedStages) & 1u);
+            if (may_draw && ahead == 1 && n_pub >= 1 && last_has_q0)
+              may_draw = ptx::mbar_try_wait(ptx::smem_u32(&bars->q_free[0]), (q0_uses - 1u) & 1u);
+          }
+          if (may_draw) {
             if (!publish(n_pub)) sched_done = true;
             ++n_pub;
             progress = true;
@@ -725,6 +744,9 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
             }
           }
         }
+        };
+        if (ahead < kSchedStages) run(std::true_type{});
+        else run(std::false_type{});
         // the bias tiles this thread requested have landed (already true unless a wait gave up)
         for (int t = 0; t < 2; ++t) {
           if (loads[t] == 0) continue;
