@@ -657,8 +657,13 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       // can take, so with few items per CTA a deep look-ahead hands the whole list to the CTAs that start first
       // (cfg2: 392 items, 148 CTAs, 8 slots - a third of the CTAs took everything).  One item of look-ahead is
       // what the loads need; more only pays when items are short and plentiful.
+      // Long items (mean sequence length >= 1024: dozens of steps each) are taken one at a time as well: drawing ahead
+      // buys nothing there (the next item's loads wait for the Q buffer anyway) and costs balance at the end of the
+      // kernel (cfg4: + 5 %).
       const long long per_cta = num_items / (4 * static_cast<long long>(gridDim.x));
-      const uint32_t ahead = static_cast<uint32_t>(per_cta < 1 ? 1 : (per_cta > kSchedStages ? kSchedStages : per_cta));
+      const bool long_items = p.batch > 0 && p.total_q / p.batch >= 1024;
+      const uint32_t ahead = static_cast<uint32_t>(
+          per_cta < 1 || long_items ? 1 : (per_cta > kSchedStages ? kSchedStages : per_cta));
       if (kBias != 2) {
         for (uint32_t n = 0;; ++n) {
           w.wait(ptx::smem_u32(&bars->sched_free[n % kSchedStages]), ((n / kSchedStages) & 1u) ^ 1u);
@@ -691,14 +696,19 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         unsigned spins = 0;
         while (!(sched_done && cur_done[0] && cur_done[1])) {
           bool progress = false;
-          bool may_draw = !sched_done && ptx::mbar_try_wait(ptx::smem_u32(&bars->sched_free[n_pub % kSchedStages]),
-                                                            ((n_pub / kSchedStages) & 1u) ^ 1u);
-          if (kLimited && may_draw) {
-            if (n_pub >= ahead)
+          // one poll per round: with a limit, the limit is the condition that binds (slots are released in item
+          // order, so the ring slot itself - last used by item n - 8 - is free whenever item n - ahead has been read,
+          // and the Q buffer of item n - 1 is released long after every role has read that item)
+          bool may_draw = !sched_done;
+          if (may_draw) {
+            if (kLimited && ahead == 1 && n_pub >= 1 && last_has_q0)
+              may_draw = ptx::mbar_try_wait(ptx::smem_u32(&bars->q_free[0]), (q0_uses - 1u) & 1u);
+            else if (kLimited && n_pub >= ahead)
               may_draw = ptx::mbar_try_wait(ptx::smem_u32(&bars->sched_free[(n_pub - ahead) % kSchedStages]),
                                             ((n_pub - ahead) / kSchedStages) & 1u);
-            if (may_draw && ahead == 1 && n_pub >= 1 && last_has_q0)
-              may_draw = ptx::mbar_try_wait(ptx::smem_u32(&bars->q_free[0]), (q0_uses - 1u) & 1u);
+            else
+              may_draw = ptx::mbar_try_wait(ptx::smem_u32(&bars->sched_free[n_pub % kSchedStages]),
+                                            ((n_pub / kSchedStages) & 1u) ^ 1u);
           }
           if (may_draw) {
             if (!publish(n_pub)) sched_done = true;
