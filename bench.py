@@ -35,9 +35,9 @@ METRIC = "hstu_jagged_fwd_causal_tflops"
 UNIT = "TFLOP/s"
 
 # DRAM bytes (read + write) per token of one attention-kernel launch, from one ncu capture of the first 24 sequences
-# of cfg4 (613 MB for 51 883 tokens).  An estimate for the full launch, not a measurement of it: the compulsory part
-# (q / k / v / out) scales with the tokens, the K/V re-reads after L2 eviction grow faster with the sequence length.
-TRAFFIC_BYTES_PER_TOKEN = {"cfg4": 612.8e6 / 51883}
+# of cfg4 (412.4 MB for 51 883 tokens).  An estimate for the full launch, not a measurement of it: the compulsory part
+# (q / k / v / out) scales with the tokens, K/V re-reads after L2 eviction would grow faster with the sequence length.
+TRAFFIC_BYTES_PER_TOKEN = {"cfg4": 412.4e6 / 51883}
 
 WORKLOAD_DESC = {
     "cfg2": "cfg2: B=32 H=4 d=128 bf16, L~U[256,1024], max_seq_len=1024, causal, no rab",
