@@ -1057,6 +1057,22 @@ bool make_matrix_map_ld(CUtensorMap* m, const void* base, long long rows, long l
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 2-D view (cols, rows) of a 16-bit [rows, cols] matrix with row pitch `ld` for TMA stores of 32-row boxes:
+// box_cols = 32 with the 64-byte swizzle (one 64-byte row piece per row), or 16 without swizzle.
+bool make_store_map(CUtensorMap* m, void* base, long long rows, long long cols, long long ld, int dtype, int box_cols) {
+  auto fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols > 0 ? cols : 1), static_cast<cuuint64_t>(rows > 0 ? rows : 1)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), 32};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = dtype == HSTU_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(m, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // The q / k / v tile map for other translation units (the backward kernels).
 bool make_tile_map(CUtensorMap* m, const void* base, long long tokens, int heads, int dim, int dtype) {
   return make_map(m, base, tokens, heads, dim, dtype);
