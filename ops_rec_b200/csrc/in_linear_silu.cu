@@ -55,11 +55,15 @@ template <> struct LsPack<__nv_bfloat16> {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
   }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+  }
   // SiLU in the tanh form, one SFU operation per element: v sigmoid(v) = h (1 + tanh h), h = v / 2.  The error of
   // tanh.approx (2^-11) stays below half a unit in the last place of the bf16 result wherever the result is not tiny.
-  static __device__ __forceinline__ float silu(float v) {
-    const float h = 0.5f * v;
-    return fmaf(h, ptx::tanh_approx(h), h);
+  static __device__ __forceinline__ uint32_t silu2(float2 v) {
+    const float2 h = __fmul2_rn(v, make_float2(0.5f, 0.5f));
+    const float2 o = __ffma2_rn(h, make_float2(ptx::tanh_approx(h.x), ptx::tanh_approx(h.y)), h);
+    return pack(o.x, o.y);
   }
 };
 template <> struct LsPack<__half> {
@@ -69,7 +73,10 @@ template <> struct LsPack<__half> {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
   }
-  static __device__ __forceinline__ float silu(float v) { return __fdividef(v, 1.f + __expf(-v)); }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) { return __half22float2(*reinterpret_cast<const __half2*>(&u)); }
+  static __device__ __forceinline__ uint32_t silu2(float2 v) {
+    return pack(__fdividef(v.x, 1.f + __expf(-v.x)), __fdividef(v.y, 1.f + __expf(-v.y)));
+  }
 };
 
 __device__ __forceinline__ void ls_wait(LsBars* bars, uint32_t* status, uint32_t bar, uint32_t parity) {
@@ -251,16 +258,16 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
             ptx::mbar_arrive(ptx::smem_u32(&bars->acc_free));
           }
           uint32_t lin[16], act[16];
+          // packed f32x2 arithmetic; the rounded values come back out of the packed pair (one conversion each way)
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
             const float2 bb = *reinterpret_cast<const float2*>(&s_bias[ch * 32 + 2 * e]);
-            const float v0 = LsPack<T>::round(__uint_as_float(acc[u][2 * e]) + bb.x);
-            const float v1 = LsPack<T>::round(__uint_as_float(acc[u][2 * e + 1]) + bb.y);
-            lin[e] = LsPack<T>::pack(v0, v1);
-            if (!kPlain) act[e] = LsPack<T>::pack(LsPack<T>::silu(v0), LsPack<T>::silu(v1));   // SiLU of the rounded value
+            const float2 sum = __fadd2_rn(make_float2(__uint_as_float(acc[u][2 * e]), __uint_as_float(acc[u][2 * e + 1])), bb);
+            lin[e] = LsPack<T>::pack(sum.x, sum.y);
+            if (!kPlain) act[e] = LsPack<T>::silu2(LsPack<T>::unpack(lin[e]));   // SiLU of the rounded value
           }
           // the stores of the previous round have read the staging block
-          if (lane == 0) ptx::bulk_wait_read<0>();
+          if (lane < 3) ptx::bulk_wait_read<0>();   // (lanes 0..2 issue one store each)
           __syncwarp();
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
@@ -274,24 +281,27 @@ in_linear_silu_kernel(const LinSiluParams p, const __grid_constant__ CUtensorMap
           }
           ptx::fence_proxy_async();
           __syncwarp();
-          if (lane == 0 && row0 < p.m) {   // rows and columns past the matrix edge are clipped by the tensor maps
-            ptx::tma_store_2d(&tm_lin, st_lin, c0, row0);
-            if (!kPlain) {
-#pragma unroll
-              for (int hf = 0; hf < 2; ++hf) {
-                const int cg = c0 + 16 * hf;   // the 16-column group decides the SiLU output tensor (n, splits: multiples of 16)
-                if (cg >= p.n) break;
+          // three lanes issue one store each (an issue costs its thread ~100 cycles); rows and columns past the
+          // matrix edge are clipped by the tensor maps
+          if (row0 < p.m) {
+            if (lane == 0) {
+              ptx::tma_store_2d(&tm_lin, st_lin, c0, row0);
+              ptx::bulk_commit();
+            } else if (!kPlain && lane < 3) {
+              const int hf = lane - 1;
+              const int cg = c0 + 16 * hf;   // the 16-column group decides the SiLU output tensor (n, splits: multiples of 16)
+              if (cg < p.n) {
                 const int which = (cg >= p.start[1]) + (cg >= p.start[2]) + (cg >= p.start[3]);
                 const CUtensorMap* tm = which == 0 ? &tm_o0 : which == 1 ? &tm_o1 : which == 2 ? &tm_o2 : &tm_o3;
                 ptx::tma_store_2d(tm, st_act + hf * 1024, cg - p.start[which], row0);
+                ptx::bulk_commit();
               }
             }
-            ptx::bulk_commit();
           }
         }
       }
     }
-    if (lane == 0) ptx::bulk_wait<0>();   // this thread's TMA stores have completed
+    if (lane < 3) ptx::bulk_wait<0>();   // this thread's TMA stores have completed
   }
 
   ptx::tc_fence_before();
