@@ -370,6 +370,53 @@ def run_also(ops_rec, W, dev, peaks, names=("cfg2", "cfg3", "cfg5"), reps=12):
     for _ in range(3):
         f()
     out["fixed_cost_us"] = time_cold(f, flush, reps) * 1e3
+    del kw
+    # the backward of the operator (hstu_jagged_backward: 2.5 x the forward's FLOPs) on cfg4 and cfg3, and the
+    # operator that produces q / k / v (distance_in_linear_silu, m = 65536, k = 1024, n = 4096): device-resident,
+    # a few back-to-back steps each, CUDA events
+    hb = ops_rec.ascendc.attention.hstu_jagged_backward
+    for name, steps in (("cfg4", 5), ("cfg3", 12)):
+        w = W.make_workload(name)
+        kw = W.materialize(w, dev)
+        grad = torch.randn_like(kw["q"]) * 0.1
+        ctx = None if kw["num_target"] is None else torch.zeros_like(kw["num_target"])
+
+        def bstep():
+            return hb(grad, kw["q"], kw["k"], kw["v"], None, kw["attn_bias"], 0, kw["max_seq_len"], 0.0,
+                      kw["seq_offset"], ctx, kw["num_target"], kw["target_group_size"], kw["alpha"])
+        for _ in range(3):
+            bstep()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            bstep()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        tf = 2.5 * w.flops() / (ms * 1e-3) / 1e12
+        out["backward_" + name] = {"value": tf, "unit": UNIT, "ms_per_step": ms, "steps": steps,
+                                   "tensor_frac": tf / peaks["tflops_burst"], "l2": "warm (back to back)",
+                                   "flops": "2.5 x forward (S, dP, dV, dK, dQ; recomputation not counted)"}
+        del kw, grad
+        torch.cuda.empty_cache()
+    m, k, n = 65536, 1024, 4096
+    gen = torch.Generator(device=dev).manual_seed(1)
+    x = torch.randn(m, k, device=dev, generator=gen).to(torch.bfloat16)
+    wt = (torch.randn(n, k, device=dev, generator=gen) * (6.0 / (n + k)) ** 0.5).to(torch.bfloat16)
+    bias = torch.ones(n, device=dev)
+    op = ops_rec.ascendc.activation.distance_in_linear_silu
+    for _ in range(3):
+        op(x, wt, bias, [n // 4] * 4)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        op(x, wt, bias, [n // 4] * 4)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 20
+    tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    out["in_linear_silu"] = {"value": tf, "unit": UNIT, "ms_per_step": ms, "steps": 20,
+                             "tensor_frac": tf / peaks["tflops_burst"], "workload": f"bf16 m={m} k={k} n={n}, even split"}
     return out
 
 
