@@ -164,6 +164,10 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   constexpr int kHalfBytes = kTileM * 128;
   constexpr int kTileBytes = kHalves * kHalfBytes;
   constexpr uint32_t kColT1 = 0, kColT2 = 128, kColAcc1 = 256, kColAcc2 = 256 + D;
+  // dQ pass: Acc1 is not used, so T1 (the scores) has a second buffer in the free columns and alternates by step:
+  // the scores of step c + 1 are computed while the element-wise stage of step c still runs, and only the dP
+  // product (whose buffer the 16-bit dS of step c occupies until its accumulate products are done) stays behind them.
+  constexpr uint32_t kColT1b = kDKV ? kColT1 : (D == 128 ? 256u : 384u);
   const KParams& p = bp.f;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -326,17 +330,21 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
       };
       w.wait(ptx::smem_u32(&bars->a_full), tiles_done & 1u);
       for_each_step<kDKV>(p, s, tile0, head, [&](int, int, int) {
-        if (cnt > first) accumulate(cnt - 1);   // must precede this step's T products: they overwrite U1 / U2
+        // dK/dV pass: the accumulate products of the last step must precede this step's T products (they overwrite
+        // U1 / U2).  dQ pass: only U2 is in use, T1 goes to its other buffer first.
+        if (kDKV && cnt > first) accumulate(cnt - 1);
         const uint32_t stage = cnt & 1u;
         w.wait(ptx::smem_u32(&bars->b_full[stage]), (cnt >> 1) & 1u);
         ptx::tc_fence_after();
         const uint64_t b1 = kDescK | static_cast<uint64_t>((sm_b + stage * 2 * kTileBytes) >> 4);
         const uint64_t b2 = kDescK | static_cast<uint64_t>((sm_b + stage * 2 * kTileBytes + kTileBytes) >> 4);
+        const uint32_t col_t1 = (cnt & 1u) ? kColT1b : kColT1;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
-          ptx::mma_ss(tmem + kColT1, a1 + off, b1 + off, idesc_t, ks > 0 ? 1u : 0u);
+          ptx::mma_ss(tmem + col_t1, a1 + off, b1 + off, idesc_t, ks > 0 ? 1u : 0u);
         }
+        if (!kDKV && cnt > first) accumulate(cnt - 1);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
@@ -379,7 +387,7 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
       for (int ch = 0; ch < 2; ++ch) {
         const int col = 64 * grp + 32 * ch;
         uint32_t t1[32], t2[32];
-        ptx::tmem_ld32(tmem + lane_base + kColT1 + col, t1);
+        ptx::tmem_ld32(tmem + lane_base + ((cnt & 1u) ? kColT1b : kColT1) + col, t1);
         ptx::tmem_ld32(tmem + lane_base + kColT2 + col, t2);
         ptx::tmem_wait_ld();
         // bit e of `bits`: element (this row, column col + e) of the tile is visible
