@@ -304,15 +304,18 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
       // accumulate products of step c (its U1 / U2 are written): Acc1 += U1.B2, Acc2 += U2.B1
       // The element-wise groups hand their results over in two parts (values 0..31 and 64..95 of a tile row, then
       // the rest), so the first half of these MMAs runs while the second part is still being computed.
-      auto accumulate = [&](uint32_t c) {
+      auto accumulate = [&](uint32_t c, auto&& between) {
         const uint32_t stage = c & 1u;
+        // dQ pass: the 16-bit dS of step c sits in the score buffer of step c (dead once the scores are read), so
+        // the dP buffer is free for the next step as soon as the element-wise stage has read it
+        const uint32_t col_u2 = kDKV ? kColT2 : ((c & 1u) ? kColT1b : kColT1);
         const uint64_t b1n = kDescN | static_cast<uint64_t>((sm_b + stage * 2 * kTileBytes) >> 4);
         const uint64_t b2n = kDescN | static_cast<uint64_t>((sm_b + stage * 2 * kTileBytes + kTileBytes) >> 4);
         auto part = [&](int ks, uint32_t acc) {
           const uint32_t ucol = (ks >> 2) * 64 + (ks & 3) * 8;
           const uint64_t off = static_cast<uint64_t>((ks * 2048) >> 4);
           if (kDKV) ptx::mma_ts(tmem + kColAcc1, tmem + kColT1 + ucol, b2n + off, idesc_acc, acc);
-          ptx::mma_ts(tmem + kColAcc2, tmem + kColT2 + ucol, b1n + off, idesc_acc, acc);
+          ptx::mma_ts(tmem + kColAcc2, tmem + col_u2 + ucol, b1n + off, idesc_acc, acc);
         };
         w.wait(ptx::smem_u32(&bars->u_full[0]), c & 1u);
         ptx::tc_fence_after();
@@ -322,6 +325,7 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         part(5, 1u);
         w.wait(ptx::smem_u32(&bars->u_full[1]), c & 1u);
         ptx::tc_fence_after();
+        between();   // (dQ pass: the dP product of the next step - its buffer has been read completely by now)
         part(2, 1u);
         part(3, 1u);
         part(6, 1u);
@@ -332,7 +336,7 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
       for_each_step<kDKV>(p, s, tile0, head, [&](int, int, int) {
         // dK/dV pass: the accumulate products of the last step must precede this step's T products (they overwrite
         // U1 / U2).  dQ pass: only U2 is in use, T1 goes to its other buffer first.
-        if (kDKV && cnt > first) accumulate(cnt - 1);
+        if (kDKV && cnt > first) accumulate(cnt - 1, [] {});
         const uint32_t stage = cnt & 1u;
         w.wait(ptx::smem_u32(&bars->b_full[stage]), (cnt >> 1) & 1u);
         ptx::tc_fence_after();
@@ -344,16 +348,20 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
           const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
           ptx::mma_ss(tmem + col_t1, a1 + off, b1 + off, idesc_t, ks > 0 ? 1u : 0u);
         }
-        if (!kDKV && cnt > first) accumulate(cnt - 1);
+        auto t2_product = [&]() {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
-          ptx::mma_ss(tmem + kColT2, a2 + off, b2 + off, idesc_t, ks > 0 ? 1u : 0u);
-        }
-        ptx::mma_commit(ptx::smem_u32(&bars->t_full));
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
+            ptx::mma_ss(tmem + kColT2, a2 + off, b2 + off, idesc_t, ks > 0 ? 1u : 0u);
+          }
+          ptx::mma_commit(ptx::smem_u32(&bars->t_full));
+        };
+        // dQ pass: first half of the last step's accumulate products, this step's dP product, then the second half
+        if (!kDKV && cnt > first) accumulate(cnt - 1, t2_product);
+        else t2_product();
         ++cnt;
       });
-      if (cnt > first) accumulate(cnt - 1);
+      if (cnt > first) accumulate(cnt - 1, [] {});
       ptx::mma_commit(ptx::smem_u32(&bars->acc_full));
       w.wait(ptx::smem_u32(&bars->acc_full), tiles_done & 1u);   // all MMAs and their barrier arrivals are done before teardown
     }
@@ -465,7 +473,7 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
                                         make_float2(0.f, 0.f), p.alpha, p.scale, (bits >> (2 * e)) & 3u, u1[e], u2[e]);
         }
         if (kDKV) ptx::tmem_st16(tmem + lane_base + kColT1 + 64 * grp + 16 * ch, u1);
-        ptx::tmem_st16(tmem + lane_base + kColT2 + 64 * grp + 16 * ch, u2);
+        ptx::tmem_st16(tmem + lane_base + (kDKV ? kColT2 : ((cnt & 1u) ? kColT1b : kColT1)) + 64 * grp + 16 * ch, u2);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(ptx::smem_u32(&bars->u_full[ch]));
