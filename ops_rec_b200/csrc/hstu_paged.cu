@@ -49,9 +49,40 @@ template <typename V>
 __global__ void __launch_bounds__(kGatherThreads) hstu_paged_gather_kernel(const GatherParams p) {
   __shared__ const unsigned char* s_src[kGatherRows];
   __shared__ unsigned char s_mode[kGatherRows];   // 0: skip the row, 1: copy from s_src, 2: zeros
+  __shared__ long long s_off[kGatherRows + 1];    // seq_offset_k[b0 .. b0 + 64], b0 = the sequence of the CTA's first row
+  __shared__ int s_b0;
   const bool is_v = blockIdx.y != 0;
   unsigned char* out = is_v ? p.v_out : p.k_out;
   const long long first = static_cast<long long>(blockIdx.x) * kGatherRows;
+  // The rows of a CTA are consecutive, so their sequences are b0, b0 + 1, ...: warp 0 finds b0 with a 32-way search
+  // (three rounds of loads for 32 768 sequences instead of fifteen dependent ones per row), the offsets from b0 on go
+  // to shared memory, and every row finds its sequence there.  Offsets that are not monotone (flagged by the
+  // pre-pass) may send a row to the wrong sequence; the range check below then gives it no source.
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int lo = 0, hi = p.batch - 1;   // the last sequence whose first row is <= first lies in [lo, hi]
+    while (hi > lo) {
+      const int stride = (hi - lo + 31) >> 5;
+      auto probe = [&](int l) { const int at = lo + (l + 1) * stride; return at < hi ? at : hi; };
+      const bool le = load_index(p.offk, p.index_bytes, probe(lane)) <= first;
+      const int c = __popc(__ballot_sync(0xffffffffu, le));
+      if (c == 0) {
+        hi = probe(0) - 1;
+      } else {
+        const int nlo = probe(c - 1);
+        if (c < 32) hi = probe(c) - 1 > nlo ? probe(c) - 1 : nlo;
+        lo = nlo;
+      }
+    }
+    if (lane == 0) s_b0 = lo;
+  }
+  __syncthreads();
+  const int b0 = s_b0;
+  if (threadIdx.x <= kGatherRows) {
+    const int at = b0 + static_cast<int>(threadIdx.x) < p.batch ? b0 + static_cast<int>(threadIdx.x) : p.batch;
+    s_off[threadIdx.x] = load_index(p.offk, p.index_bytes, at);
+  }
+  __syncthreads();
   if (threadIdx.x < kGatherRows) {
     const long long row = first + threadIdx.x;
     const unsigned char* src = nullptr;
@@ -63,13 +94,27 @@ __global__ void __launch_bounds__(kGatherThreads) hstu_paged_gather_kernel(const
       mode = row < k_end + kTileN ? 2 : 0;
     } else if (row < p.capacity) {
       // the last sequence whose first row is <= row (sequences of length 0 share their offset with the next one)
-      int lo = 0, hi = p.batch - 1;
-      while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (load_index(p.offk, p.index_bytes, mid) <= row) lo = mid; else hi = mid - 1;
+      int b;
+      long long k0, k1;
+      if (row < s_off[kGatherRows] || b0 + kGatherRows >= p.batch) {
+        int lo = 0, hi = kGatherRows - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (s_off[mid] <= row) lo = mid; else hi = mid - 1;
+        }
+        b = b0 + lo < p.batch - 1 ? b0 + lo : p.batch - 1;
+        k0 = s_off[b - b0];
+        k1 = s_off[b - b0 + 1];
+      } else {   // more than 64 sequences begin inside this CTA's rows (runs of empty ones): the long way
+        int lo = b0, hi = p.batch - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (load_index(p.offk, p.index_bytes, mid) <= row) lo = mid; else hi = mid - 1;
+        }
+        b = lo;
+        k0 = load_index(p.offk, p.index_bytes, b);
+        k1 = load_index(p.offk, p.index_bytes, b + 1);
       }
-      const int b = lo;
-      const long long k0 = load_index(p.offk, p.index_bytes, b), k1 = load_index(p.offk, p.index_bytes, b + 1);
       if (row >= k0 && row < k1) {   // (offsets that are not monotone, flagged by the pre-pass, leave rows uncovered)
         mode = 2;                    // zeros unless a source exists (an inconsistent table has none for this row)
         const long long q0 = load_index(p.offq, p.index_bytes, b);
