@@ -296,7 +296,7 @@ def hstu_jagged_backward(grad, q, k, v, mask=None, attn_bias=None, mask_type=0, 
 def hstu_paged_forward(q, k, v, kv_cache, mask=None, attn_bias=None, mask_type=0, max_seq_len=0, max_seq_len_k=0,
                        silu_scale=0.0, seq_offset=None, seq_offset_k=None, seq_offset_t=None, page_offsets=None,
                        page_ids=None, last_page_len=None, num_target=None, target_group_size=0, alpha=1.0, *,
-                       flags=0, return_status=False):
+                       flags=0, return_status=False, workspace_fill=None):
     """ops_rec::hstu_paged through hstu_paged_fwd on CUDA tensors (argument order of the reference schema,
     hstu_v1/torch_extension/hstu_paged_plugin.cpp:75-98).  The page-table tensors are converted to seq_offset's
     integer type like the reference adapter does (:33-35)."""
@@ -328,7 +328,10 @@ def hstu_paged_forward(q, k, v, kv_cache, mask=None, attn_bias=None, mask_type=0
     a.num_pages, a.num_page_ids = kv_cache.shape[0], page_ids.numel()
     n = C.c_uint64(0)
     check(load().hstu_paged_fwd_get_workspace_size(C.byref(a), C.byref(n)))
+    # (workspace_fill: tests fill the workspace with a byte pattern first - nothing the call reads may be uninitialised)
     ws = torch.empty(n.value, dtype=torch.uint8, device=q.device)
+    if workspace_fill is not None:
+        ws.fill_(workspace_fill)
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
         check(load().hstu_paged_fwd(C.byref(a), ws.data_ptr(), n.value, stream))

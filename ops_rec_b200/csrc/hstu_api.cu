@@ -228,6 +228,8 @@ static int jagged_fwd_impl(const HstuJaggedArgs* args, void* workspace, uint64_t
     p.page_size = paged->page_size;
     p.num_pages = paged->num_pages;
     p.num_page_ids = paged->num_page_ids;
+    p.kv_cache = paged->kv_cache;
+    p.paged_direct = paged->paged_direct;
   }
   const bool tc = wants_tc(args, p);
   cudaError_t e = hstu::launch_prepass(p, tc, stream);
@@ -328,6 +330,9 @@ int hstu_paged_fwd(const HstuPagedArgs* args, void* workspace, uint64_t workspac
   p.page_size = args->page_size;
   p.num_pages = args->num_pages;
   p.num_page_ids = args->num_page_ids;
+  p.kv_cache = args->kv_cache;
+  // whole 128-row pages go from the cache straight into the tensor-core kernel's K / V ring
+  p.paged_direct = (args->page_size == hstu::kTileN && args->num_pages <= 0x7fffffll && wants_tc(&pl.fwd, p)) ? 1 : 0;
   const cudaError_t e = hstu::launch_paged_gather(p, args->kv_cache, b->k, b->v, k_stage, v_stage, pl.capacity,
                                                   args->num_pages, args->num_page_ids, pl.esize, stream);
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "gather launch: %s", cudaGetErrorString(e));

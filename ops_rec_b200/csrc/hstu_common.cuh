@@ -61,6 +61,11 @@ struct KParams {
   const void* last_page_len;  // [batch]
   long long num_pages, num_page_ids;
   int page_size;
+  // hstu_paged on the tensor-core kernel with 128-row pages: the K / V tiles that are whole cache pages are read
+  // from the cache itself (one TMA box per page); only the rest of each sequence - its partial last page and the new
+  // rows - goes through the staging tensors
+  const void* kv_cache;       // [num_pages, 2, page_size, hk, d]
+  int paged_direct;
 };
 
 // Backward call: the forward's parameters plus the gradient tensors.
@@ -133,6 +138,30 @@ HSTU_HD unsigned check_seq(const KParams& p, int b) {
   long long t = p.tgt ? load_index(p.tgt, p.index_bytes, b) : 0;
   if (c < 0 || t < 0 || c + t > q1 - q0 || t > k1 - k0) st |= HSTU_ST_BAD_CTX_TARGET;
   return st;
+}
+
+// hstu_paged, direct page reads: how many leading K / V tiles (128 keys each) of sequence b are whole cache pages the
+// attention kernel reads from the cache itself, and the first slot of the sequence in page_ids.  The gather leaves
+// exactly these rows out of the staging tensors, so both sides use this one rule (every index clamped: the
+// result never names a page slot outside page_ids).
+HSTU_HD int paged_full_tiles(const void* offq, const void* offk, const void* tgt, const void* page_offsets,
+                             int index_bytes, long long total_q, long long num_page_ids, int b, long long* first_slot) {
+  const long long k0 = load_index(offk, index_bytes, b), k1 = load_index(offk, index_bytes, b + 1);
+  const long long q0 = load_index(offq, index_bytes, b);
+  long long q1 = load_index(offq, index_bytes, b + 1);
+  if (q1 > total_q) q1 = total_q;
+  long long t = tgt ? load_index(tgt, index_bytes, b) : 0;
+  if (t < 0) t = 0;
+  if (t > q1 - q0) t = q1 - q0 > 0 ? q1 - q0 : 0;
+  long long pg0 = load_index(page_offsets, index_bytes, b), pg1 = load_index(page_offsets, index_bytes, b + 1);
+  if (pg0 < 0) pg0 = 0;
+  if (pg1 > num_page_ids) pg1 = num_page_ids;
+  long long n = ((k1 - k0) - t) / kTileN;   // whole pages of the cached part
+  if (n > pg1 - pg0) n = pg1 - pg0;
+  if (n < 0) n = 0;
+  if (n > 0x7fff) n = 0x7fff;
+  *first_slot = pg0;
+  return static_cast<int>(n);
 }
 
 // hstu_paged: the page table of sequence b must describe exactly the cached part of its keys,

@@ -37,6 +37,7 @@ struct GatherParams {
   long long total_q, capacity, num_pages, num_page_ids;
   int index_bytes, batch, page_size;
   int row_bytes;                // heads_k * dim * element size
+  int skip_full_pages;          // the attention kernel reads whole pages from the cache: stage only the rest
 };
 
 // One CTA per kGatherRows consecutive rows of a staging tensor (grid.y = 0: keys, 1: values).
@@ -124,7 +125,12 @@ __global__ void __launch_bounds__(kGatherThreads) hstu_paged_gather_kernel(const
         if (t < 0) t = 0;
         if (t > q1 - q0) t = q1 - q0 > 0 ? q1 - q0 : 0;
         const long long r = row - k0, cache_len = (k1 - k0) - t;
-        if (r < cache_len) {
+        long long unused_slot;
+        if (p.skip_full_pages &&
+            r < static_cast<long long>(kTileN) * paged_full_tiles(p.offq, p.offk, p.tgt, p.page_offsets, p.index_bytes,
+                                                                  p.total_q, p.num_page_ids, b, &unused_slot)) {
+          mode = 0;   // a row of a whole page: never read from the staging tensor
+        } else if (r < cache_len) {
           long long pg0 = load_index(p.page_offsets, p.index_bytes, b), pg1 = load_index(p.page_offsets, p.index_bytes, b + 1);
           if (pg0 < 0) pg0 = 0;
           if (pg1 > p.num_page_ids) pg1 = p.num_page_ids;
@@ -189,6 +195,7 @@ cudaError_t launch_paged_gather(const KParams& p, const void* kv_cache, const vo
   g.batch = p.batch;
   g.page_size = p.page_size;
   g.row_bytes = p.hk * p.dqk * esize;
+  g.skip_full_pages = p.paged_direct;
   const dim3 grid(static_cast<unsigned>((capacity + kGatherRows - 1) / kGatherRows), 2, 1);
   const uintptr_t align = reinterpret_cast<uintptr_t>(kv_cache) | reinterpret_cast<uintptr_t>(k_in) |
                           reinterpret_cast<uintptr_t>(v_in) | reinterpret_cast<uintptr_t>(k_out) |

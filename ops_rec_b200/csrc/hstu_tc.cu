@@ -81,6 +81,10 @@ struct Item {
   int n0, n1;
   int nmax;
   int valid;  // 0 = end of work
+  // hstu_paged with direct page reads: the K / V tiles 0 .. full_pages - 1 are the cache pages
+  // page_ids[first_slot + j], the others come from the staging tensors like any jagged K / V
+  int full_pages;
+  long long first_slot;
   __device__ __forceinline__ int n(int t) const { return t == 0 ? n0 : n1; }
 };
 
@@ -173,6 +177,11 @@ __device__ __forceinline__ Item load_item(const KParams& p, long long idx) {
   it.n0 = kv_tiles_for_rows(it.s, it.r0, kTileM, p.mask_type, kTileN);
   it.n1 = kv_tiles_for_rows(it.s, it.r0 + kTileM, kTileM, p.mask_type, kTileN);
   it.nmax = it.n0 > it.n1 ? it.n0 : it.n1;
+  it.full_pages = 0;
+  it.first_slot = 0;
+  if (p.paged_direct)
+    it.full_pages = paged_full_tiles(p.offq, p.offk, p.tgt, p.page_offsets, p.index_bytes, p.total_q, p.num_page_ids,
+                                     it.b, &it.first_slot);
   it.valid = 1;
   return it;
 }
@@ -365,7 +374,8 @@ template <int D, typename T, int kBias>
 __global__ void __launch_bounds__(kThreads, 1)
 hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_bias,
-               const __grid_constant__ CUtensorMap tm_out, const int bias_vec_ok) {
+               const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_cache,
+               const int bias_vec_ok) {
   using C = Cfg<D, kBias>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -384,6 +394,7 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     ptx::prefetch_tensormap(&tm_q);
     ptx::prefetch_tensormap(&tm_k);
     ptx::prefetch_tensormap(&tm_v);
+    if (p.paged_direct) ptx::prefetch_tensormap(&tm_cache);
     if (kBias == 2) ptx::prefetch_tensormap(&tm_bias);
     if (C::kOutBytes > 0) ptx::prefetch_tensormap(&tm_out);
     for (int t = 0; t < 2; ++t) {
@@ -454,6 +465,14 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
         load_q(0);
         for (int j = 0; j < it.nmax; ++j) {
           const int row = static_cast<int>(it.s.k0) + j * kTileN;
+          // a whole cache page (hstu_paged): the cache is [pages, 2 (K, V), 128 rows, heads, dim]; a page id outside
+          // the cache (flagged by the pre-pass) reads as zeros - the coordinate lies past the tensor
+          const bool from_cache = j < it.full_pages;
+          long long pid = 0;
+          if (from_cache) {
+            pid = load_index(p.page_ids, p.index_bytes, it.first_slot + j);
+            if (pid < 0 || pid >= p.num_pages) pid = p.num_pages;
+          }
 #pragma unroll
           for (int kv = 0; kv < 2; ++kv) {
             const uint32_t stage = ring_pos % C::kStages;
@@ -462,10 +481,11 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
             w.wait(ptx::smem_u32(&bars->kv_free[stage]), (use & 1u) ^ 1u);
             if (w.aborted()) break;
             ptx::mbar_expect_tx(full, C::kTileBytes);
+            const CUtensorMap* tm = from_cache ? &tm_cache : (kv == 0 ? &tm_k : &tm_v);
+            const int trow = from_cache ? static_cast<int>((pid * 2 + kv) * kTileN) : row;
 #pragma unroll
             for (int hf = 0; hf < C::kHalves; ++hf)
-              ptx::tma_load_3d(sm_ring + stage * C::kTileBytes + hf * C::kHalfBytes, kv == 0 ? &tm_k : &tm_v, full,
-                               hf * 64, it.hk, row);
+              ptx::tma_load_3d(sm_ring + stage * C::kTileBytes + hf * C::kHalfBytes, tm, full, hf * 64, it.hk, trow);
             ++ring_pos;
             if (j == 0 && kv == 0) load_q(1);
           }
@@ -1010,7 +1030,7 @@ bool make_out_map(CUtensorMap* m, const KParams& p, int dtype) {
 
 template <int D, typename T, int kBias>
 cudaError_t launch_inst(const KParams& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                        const CUtensorMap& mb, const CUtensorMap& mo, int bias_vec_ok, int grid,
+                        const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mc, int bias_vec_ok, int grid,
                         cudaStream_t stream) {
   auto kern = hstu_tc_kernel<D, T, kBias>;
   constexpr int smem = Cfg<D, kBias>::kSmemBytes;
@@ -1027,7 +1047,7 @@ cudaError_t launch_inst(const KParams& p, const CUtensorMap& mq, const CUtensorM
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, p, mq, mk, mv, mb, mo, bias_vec_ok);
+  return cudaLaunchKernelEx(&cfg, kern, p, mq, mk, mv, mb, mo, mc, bias_vec_ok);
 }
 
 }  // namespace
@@ -1117,11 +1137,14 @@ cudaError_t launch_tc(const KParams& p_in, int dtype, int num_sms, cudaStream_t 
     bias_mode = 2;
   CUtensorMap mo;
   if (!make_out_map(&mo, p, dtype)) return cudaErrorNotSupported;
+  // hstu_paged with direct page reads: the cache as one K / V tensor of num_pages * 2 * 128 rows
+  CUtensorMap mc = mk;
+  if (p.paged_direct && !make_map(&mc, p.kv_cache, p.num_pages * 2 * kTileN, p.hk, p.dqk, dtype)) return cudaErrorNotSupported;
 #define HSTU_TC_CASE(DD, TT)                                                                       \
-  return bias_mode == 3   ? launch_inst<DD, TT, 3>(p, mq, mk, mv, mb, mo, vec_ok, g, stream)      \
-         : bias_mode == 2 ? launch_inst<DD, TT, 2>(p, mq, mk, mv, mb, mo, vec_ok, g, stream)      \
-         : bias_mode == 1 ? launch_inst<DD, TT, 1>(p, mq, mk, mv, mb, mo, vec_ok, g, stream)      \
-                          : launch_inst<DD, TT, 0>(p, mq, mk, mv, mb, mo, vec_ok, g, stream)
+  return bias_mode == 3   ? launch_inst<DD, TT, 3>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream)  \
+         : bias_mode == 2 ? launch_inst<DD, TT, 2>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream)  \
+         : bias_mode == 1 ? launch_inst<DD, TT, 1>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream)  \
+                          : launch_inst<DD, TT, 0>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream)
   if (dtype == HSTU_DTYPE_BF16) {
     if (p.dqk == 128) { HSTU_TC_CASE(128, __nv_bfloat16); }
     HSTU_TC_CASE(64, __nv_bfloat16);

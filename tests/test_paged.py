@@ -178,6 +178,20 @@ def test_gpu_long_history_gqa_and_custom_mask():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("D", [64, 128])
+def test_gpu_nothing_uninitialised_is_read_from_the_workspace(D):
+    """With 128-row pages the whole pages of the cache never pass through the staging tensors of the workspace: their
+    rows there stay unwritten.  A workspace full of 0xFF bytes (NaN in every 16-bit float) must change nothing."""
+    args = make_paged_case(6, 4, 2, D, 700, 40, 128, True, BF16, seed=11)
+    clean, status = _run(args)
+    assert status == 0
+    dirty, status = _run(args, workspace_fill=0xFF)
+    assert status == 0
+    assert torch.isfinite(dirty.float()).all()
+    assert torch.equal(clean, dirty)
+    _assert_parity(dirty, args, label="page 128, workspace of NaNs")
+
+
 def test_gpu_int32_metadata_and_torch_operator():
     import ops_rec_b200 as ops_rec
     args = make_paged_case(4, 4, 2, 64, 300, 30, 32, True, BF16, seed=9)
