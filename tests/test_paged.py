@@ -192,6 +192,7 @@ def test_gpu_nothing_uninitialised_is_read_from_the_workspace(D):
     _assert_parity(dirty, args, label="page 128, workspace of NaNs")
 
 
+@pytest.mark.gpu
 def test_gpu_int32_metadata_and_torch_operator():
     import ops_rec_b200 as ops_rec
     args = make_paged_case(4, 4, 2, 64, 300, 30, 32, True, BF16, seed=9)
