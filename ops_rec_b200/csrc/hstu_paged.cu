@@ -52,6 +52,7 @@ __global__ void __launch_bounds__(kGatherThreads) hstu_paged_gather_kernel(const
   __shared__ unsigned char s_mode[kGatherRows];   // 0: skip the row, 1: copy from s_src, 2: zeros
   __shared__ long long s_off[kGatherRows + 1];    // seq_offset_k[b0 .. b0 + 64], b0 = the sequence of the CTA's first row
   __shared__ int s_b0;
+  __shared__ int s_skip_all;
   const bool is_v = blockIdx.y != 0;
   unsigned char* out = is_v ? p.v_out : p.k_out;
   const long long first = static_cast<long long>(blockIdx.x) * kGatherRows;
@@ -84,6 +85,21 @@ __global__ void __launch_bounds__(kGatherThreads) hstu_paged_gather_kernel(const
     s_off[threadIdx.x] = load_index(p.offk, p.index_bytes, at);
   }
   __syncthreads();
+  // Direct page reads: most CTAs lie wholly inside the whole pages of one sequence and have nothing to stage.
+  if (p.skip_full_pages) {
+    if (threadIdx.x == 0) {
+      int all = 0;
+      if (first >= s_off[0] && first + kGatherRows <= s_off[1]) {
+        long long slot;
+        const int n = paged_full_tiles(p.offq, p.offk, p.tgt, p.page_offsets, p.index_bytes, p.total_q, p.num_page_ids,
+                                       b0, &slot);
+        all = first + kGatherRows - s_off[0] <= static_cast<long long>(kTileN) * n ? 1 : 0;
+      }
+      s_skip_all = all;
+    }
+    __syncthreads();
+    if (s_skip_all) return;
+  }
   if (threadIdx.x < kGatherRows) {
     const long long row = first + threadIdx.x;
     const unsigned char* src = nullptr;
