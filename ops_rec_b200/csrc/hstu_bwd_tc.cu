@@ -397,6 +397,21 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         uint32_t t1[32], t2[32];
         ptx::tmem_ld32(tmem + lane_base + ((cnt & 1u) ? kColT1b : kColT1) + col, t1);
         ptx::tmem_ld32(tmem + lane_base + kColT2 + col, t2);
+        // dK/dV pass: this key's bias values for the 32 queries of the chunk lie a row pitch apart - all 32 loads
+        // are issued here, ahead of the wait for the products (addresses clamped into the plane: what lies outside
+        // the sequence is never used)
+        uint32_t bcol[16];
+        if (kDKV && p.bias) {
+          const int kk = mine < p.maxk ? mine : p.maxk - 1;
+          const unsigned short* bsrc = static_cast<const unsigned short*>(p.bias) + bias_bh + kk;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int r0 = srow0 + col + 2 * e, r1 = r0 + 1;
+            const uint32_t lo = __ldg(bsrc + static_cast<long long>(r0 < p.maxq ? r0 : p.maxq - 1) * p.maxk);
+            const uint32_t hi = __ldg(bsrc + static_cast<long long>(r1 < p.maxq ? r1 : p.maxq - 1) * p.maxk);
+            bcol[e] = lo | (hi << 16);
+          }
+        }
         ptx::tmem_wait_ld();
         // bit e of `bits`: element (this row, column col + e) of the tile is visible
         uint32_t bits;
@@ -447,9 +462,9 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
             const int c = col + 2 * e;
             float2 bias;
             if (kDKV) {
-              const long long at = bias_bh + static_cast<long long>(srow0 + c) * p.maxk + mine;
-              bias.x = (v2 & 1u) ? BPack<T>::one(p.bias, at) : 0.f;
-              bias.y = (v2 & 2u) ? BPack<T>::one(p.bias, at + p.maxk) : 0.f;
+              const float2 both = BPack<T>::unpack(bcol[e]);
+              bias.x = (v2 & 1u) ? both.x : 0.f;
+              bias.y = (v2 & 2u) ? both.y : 0.f;
             } else {
               const long long at = bias_bh + static_cast<long long>(mine) * p.maxk + srow0 + c;
               bias.x = (v2 & 1u) ? BPack<T>::one(p.bias, at) : 0.f;
