@@ -251,11 +251,22 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
     const int width = p.maxk - first_col;
     T* dbias = static_cast<T*>(bp.dbias);
     const long long brow0 = (static_cast<long long>(b) * p.hq + head) * p.maxq;
-    if (width > 0)
-      for (int idx = tid; idx < kTileM * width; idx += kBwdThreads) {
-        const int r = idx / width, c = idx - r * width;
-        if (tile0 + r < p.maxq) dbias[(brow0 + tile0 + r) * p.maxk + first_col + c] = T(0.f);
+    if (width > 0) {
+      if (p.maxk % 8 == 0 && (reinterpret_cast<uintptr_t>(bp.dbias) & 15u) == 0) {
+        // 16-byte stores: first_col is a multiple of 128, so every row piece starts on a 16-byte boundary
+        const int pieces = width / 8;
+        for (int idx = tid; idx < kTileM * pieces; idx += kBwdThreads) {
+          const int r = idx / pieces, c = idx - r * pieces;
+          if (tile0 + r < p.maxq)
+            *reinterpret_cast<uint4*>(dbias + (brow0 + tile0 + r) * p.maxk + first_col + 8 * c) = make_uint4(0, 0, 0, 0);
+        }
+      } else {
+        for (int idx = tid; idx < kTileM * width; idx += kBwdThreads) {
+          const int r = idx / width, c = idx - r * width;
+          if (tile0 + r < p.maxq) dbias[(brow0 + tile0 + r) * p.maxk + first_col + c] = T(0.f);
+        }
       }
+    }
   }
   if (tile0 >= len) {   // uniform over the CTA
     __syncthreads();
