@@ -89,6 +89,21 @@ def test_gpu_grid_against_the_oracle(m, n, k, dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k,split", [
+    (300, 256, 16, [16, 48, 80, 112]),        # split boundaries at odd multiples of 16: inside a 32-column store chunk
+    (10300, 1024, 64, None),                  # 41 x 4 = 164 tiles on 148 persistent CTAs: some walk two tiles
+    (40000, 512, 128, [64, 64, 192, 192]),    # 157 x 2 = 314 tiles: every CTA walks two or three
+])
+def test_gpu_persistent_tiles_and_split_boundaries(m, n, k, split):
+    x, w, b, split = _case(m, n, k, torch.bfloat16, split=split, seed=5)
+    got = _gpu(x, w, b, split)
+    want = IO.in_linear_silu(x, w, b, split)
+    for g, t, name in zip(got, want, NAMES):
+        assert g.shape == t.shape
+        _close(g, t, torch.bfloat16, f"{m}x{n}x{k} {name}")
+
+
+@pytest.mark.gpu
 def test_gpu_no_bias_even_split_torch_operator_and_errors():
     import ops_rec_b200 as ops_rec
     from ops_rec_b200 import cabi
