@@ -199,6 +199,18 @@ def test_tensor_core_and_generic_kernels_agree(D, dtype):
     assert (tc.float() - gen.float()).abs().max() <= 2e-2 * scale
 
 
+@pytest.mark.parametrize("rab", [None, "shared3"])
+def test_medium_batches_take_the_limited_look_ahead(rab):
+    """Between 4 and 32 work items per CTA the scheduler draws a few items ahead (not one, not the whole ring):
+    400 sequences x 4 heads x 1-2 q-pairs on 148 CTAs."""
+    args = make_case(400, 4, 4, 64, 64, 200, 400, BF16, seed=29, rab=rab, max_seq_len=400)
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label=f"400 sequences, rab={rab}")
+    again, _ = run_cabi(args)
+    assert torch.equal(out, again)
+
+
 def test_results_are_bitwise_reproducible():
     args = make_case(8, 4, 4, 128, 128, 1, 900, BF16, seed=17, rab="batch")
     a, _ = run_cabi(args)
