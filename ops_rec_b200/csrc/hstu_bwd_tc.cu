@@ -31,6 +31,7 @@
 namespace hstu {
 
 bool make_tile_map(CUtensorMap* m, const void* base, long long tokens, int heads, int dim, int dtype);
+bool make_bias_tile_map(CUtensorMap* m, const KParams& p, int dtype);
 
 namespace {
 
@@ -71,6 +72,7 @@ struct BwdBars {
   uint64_t t_full;             // T1 and T2 of the current step are complete
   uint64_t u_full[2];          // their 16-bit replacements are written: first / second 32 values of each 64 (256 arrivals)
   uint64_t acc_full;           // every accumulate MMA is complete
+  uint64_t bias_full, bias_free;   // dK/dV pass with a staged bias tile: landed / read by all 256 element-wise threads
   uint32_t tmem_base;
   int abort_flag;
   int item;                    // the tile every thread of the CTA works on next (-1: none left)
@@ -155,11 +157,13 @@ __device__ __forceinline__ void score_grad2(float2 s, float2 dp, float2 bias, fl
   ds_out = BPack<T>::pack(ds.x, ds.y);
 }
 
-template <int D, typename T, bool kDKV>
+// kStaged (dK/dV pass with a bias that TMA can tile): a kernel of its own - the same code merely present in the
+// bias-free kernel cost that one 4 %.
+template <int D, typename T, bool kDKV, bool kStaged = false>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1,
                    const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_b1,
-                   const __grid_constant__ CUtensorMap tm_b2) {
+                   const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_bias) {
   constexpr int kHalves = D / 64;
   constexpr int kHalfBytes = kTileM * 128;
   constexpr int kTileBytes = kHalves * kHalfBytes;
@@ -177,7 +181,12 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   uint8_t* base_ptr = smem_raw + (base - raw);
   const uint32_t sm_a = base;                        // A1, A2
   const uint32_t sm_b = base + 2 * kTileBytes;       // ring: stage x {B1, B2}
-  BwdBars* bars = reinterpret_cast<BwdBars*>(base_ptr + 6 * kTileBytes);
+  // dK/dV pass with a bias: the 128 x 128 bias tile of a step (rows = the step's queries, columns = this tile's keys),
+  // staged by TMA - a thread owns a key and reads its column, one value per query, from shared memory instead of
+  // 32 strided 2-byte loads from global memory per chunk
+  const uint32_t sm_bias = base + 6 * kTileBytes;    // 2 boxes of 128 rows x 128 bytes, 128-byte swizzle
+  constexpr bool staged = kDKV && kStaged;
+  BwdBars* bars = reinterpret_cast<BwdBars*>(base_ptr + 6 * kTileBytes + (staged ? 2 * kTileM * 128 : 0));
   const BwdWaiter w{&bars->abort_flag, p.ws_header};
 
   if (tid == 0) {
@@ -194,6 +203,9 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
     ptx::mbar_init(ptx::smem_u32(&bars->u_full[0]), 2 * kTileM);
     ptx::mbar_init(ptx::smem_u32(&bars->u_full[1]), 2 * kTileM);
     ptx::mbar_init(ptx::smem_u32(&bars->acc_full), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->bias_full), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->bias_free), 2 * kTileM);
+    if (staged) ptx::prefetch_tensormap(&tm_bias);
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
   }
@@ -288,9 +300,19 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         ptx::tma_load_3d(sm_a + hf * kHalfBytes, &tm_a1, afull, hf * 64, a_head, static_cast<int>(a_row));
         ptx::tma_load_3d(sm_a + kTileBytes + hf * kHalfBytes, &tm_a2, afull, hf * 64, a_head, static_cast<int>(a_row));
       }
-      for_each_step<kDKV>(p, s, tile0, head, [&](int sh, int srow0, int) {
+      for_each_step<kDKV>(p, s, tile0, head, [&](int sh, int srow0, int qh) {
         const uint32_t stage = cnt & 1u;
         const uint32_t full = ptx::smem_u32(&bars->b_full[stage]);
+        if (staged) {
+          // the bias tile of this step, once every element-wise thread has read the last one
+          w.wait(ptx::smem_u32(&bars->bias_free), (cnt & 1u) ^ 1u);
+          const uint32_t bfull = ptx::smem_u32(&bars->bias_full);
+          ptx::mbar_expect_tx(bfull, 2 * kTileM * 128);
+          const int brow = (b * p.hq + qh) * p.maxq + srow0;
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf)
+            ptx::tma_load_2d(sm_bias + hf * (kTileM * 128), &tm_bias, bfull, tile0 + hf * 64, brow);
+        }
         w.wait(ptx::smem_u32(&bars->b_free[stage]), ((cnt >> 1) & 1u) ^ 1u);
         ptx::mbar_expect_tx(full, 2 * kTileBytes);
         const int row = static_cast<int>(b_row0) + srow0;
@@ -412,7 +434,23 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         // are issued here, ahead of the wait for the products (addresses clamped into the plane: what lies outside
         // the sequence is never used)
         uint32_t bcol[16];
-        if (kDKV && p.bias) {
+        if (staged) {
+          if (ch == 0) {
+            w.wait(ptx::smem_u32(&bars->bias_full), cnt & 1u);
+          }
+          // element (query col + e, key row): box row / 64, row = query, 16-byte chunk (key % 64) / 8 ^ (query & 7)
+          const uint32_t box = sm_bias + (row >> 6) * (kTileM * 128) + (row & 7) * 2;
+          const uint32_t kchunk = (row & 63) >> 3;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int q0l = col + 2 * e, q1l = q0l + 1;
+            uint32_t lo, hi;
+            asm volatile("ld.shared.u16 %0, [%1];" : "=r"(lo) : "r"(box + q0l * 128 + ((kchunk ^ (q0l & 7)) << 4)));
+            asm volatile("ld.shared.u16 %0, [%1];" : "=r"(hi) : "r"(box + q1l * 128 + ((kchunk ^ (q1l & 7)) << 4)));
+            bcol[e] = lo | (hi << 16);
+          }
+          if (ch == 1) ptx::mbar_arrive(ptx::smem_u32(&bars->bias_free));   // this thread has read its column
+        } else if (kDKV && p.bias) {
           const int kk = mine < p.maxk ? mine : p.maxk - 1;
           const unsigned short* bsrc = static_cast<const unsigned short*>(p.bias) + bias_bh + kk;
 #pragma unroll
@@ -576,6 +614,8 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
       const uint32_t bar = ptx::smem_u32(&bars->b_full[c & 1u]);
       for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (c >> 1) & 1u); ++spin) {}
     }
+    if (staged && cnt > 0)
+      for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(ptx::smem_u32(&bars->bias_full), (cnt - 1) & 1u); ++spin) {}
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -594,21 +634,32 @@ cudaError_t launch_bwd_tc_t(const BwdParams& bp, int dtype, int num_sms, cudaStr
       !make_tile_map(&mk, p.k, p.total_k, p.hk, p.dqk, dtype) || !make_tile_map(&mv, p.v, p.total_k, p.hk, p.dv, dtype))
     return cudaErrorNotSupported;
   constexpr int smem = 1024 + 6 * (D / 64) * kTileM * 128 + 256;
+  constexpr int smem_kv = smem + 2 * kTileM * 128;   // + the staged bias tile of the dK/dV pass
+  static_assert(smem_kv <= 232448, "shared memory budget of one CTA exceeded");
   static_assert(sizeof(BwdBars) <= 256, "barrier block too large");
+  // the bias as TMA tiles: rows 16-byte aligned and batch blocks back to back (what the forward's staged mode needs)
+  CUtensorMap mb = mq;
+  const int bias_staged = p.bias && (p.maxk % 8 == 0) && (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0 &&
+                          p.bias_bstride == static_cast<long long>(p.hq) * p.maxq * p.maxk &&
+                          make_bias_tile_map(&mb, p, dtype);
   auto kq = hstu_bwd_tc_kernel<D, T, false>;
   auto kkv = hstu_bwd_tc_kernel<D, T, true>;
+  auto kkv_staged = hstu_bwd_tc_kernel<D, T, true, true>;
   cudaError_t e = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(kkv_staged, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_kv);
   if (e != cudaSuccess) return e;
   if (p.total_q > 0) {
     const long long tiles = static_cast<long long>(p.batch) * p.hq * ((p.maxq + kTileM - 1) / kTileM);
-    kq<<<static_cast<unsigned>(tiles < num_sms ? tiles : num_sms), kBwdThreads, smem, stream>>>(bp, mq, mg, mk, mv);
+    kq<<<static_cast<unsigned>(tiles < num_sms ? tiles : num_sms), kBwdThreads, smem, stream>>>(bp, mq, mg, mk, mv, mb);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
   if (p.total_k > 0) {
     const long long tiles = static_cast<long long>(p.batch) * p.hk * ((p.maxk + kTileN - 1) / kTileN);
-    kkv<<<static_cast<unsigned>(tiles < num_sms ? tiles : num_sms), kBwdThreads, smem, stream>>>(bp, mk, mv, mq, mg);
+    const unsigned grid = static_cast<unsigned>(tiles < num_sms ? tiles : num_sms);
+    if (bias_staged) kkv_staged<<<grid, kBwdThreads, smem_kv, stream>>>(bp, mk, mv, mq, mg, mb);
+    else kkv<<<grid, kBwdThreads, smem, stream>>>(bp, mk, mv, mq, mg, mb);
     e = cudaGetLastError();
   }
   return e;

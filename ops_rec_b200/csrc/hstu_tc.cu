@@ -1093,6 +1093,9 @@ bool make_store_map(CUtensorMap* m, void* base, long long rows, long long cols, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The bias tile map (64 x 128 boxes, 128-byte swizzle) for other translation units (the backward kernels).
+bool make_bias_tile_map(CUtensorMap* m, const KParams& p, int dtype) { return make_bias_map(m, p, dtype); }
+
 // The q / k / v tile map for other translation units (the backward kernels).
 bool make_tile_map(CUtensorMap* m, const void* base, long long tokens, int heads, int dim, int dtype) {
   return make_map(m, base, tokens, heads, dim, dtype);
