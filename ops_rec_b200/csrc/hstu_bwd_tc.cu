@@ -181,11 +181,11 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   uint8_t* base_ptr = smem_raw + (base - raw);
   const uint32_t sm_a = base;                        // A1, A2
   const uint32_t sm_b = base + 2 * kTileBytes;       // ring: stage x {B1, B2}
-  // dK/dV pass with a bias: the 128 x 128 bias tile of a step (rows = the step's queries, columns = this tile's keys),
-  // staged by TMA - a thread owns a key and reads its column, one value per query, from shared memory instead of
-  // 32 strided 2-byte loads from global memory per chunk
+  // With a bias that TMA can tile: the 128 x 128 bias tile of a step (rows = queries, columns = keys), staged by TMA.
+  // dK/dV pass: a thread owns a key and reads its column, one value per query, from shared memory instead of 32
+  // strided 2-byte loads from global memory per chunk; dQ pass: a thread owns a query and reads 64 bytes of its row
   const uint32_t sm_bias = base + 6 * kTileBytes;    // 2 boxes of 128 rows x 128 bytes, 128-byte swizzle
-  constexpr bool staged = kDKV && kStaged;
+  constexpr bool staged = kStaged;
   BwdBars* bars = reinterpret_cast<BwdBars*>(base_ptr + 6 * kTileBytes + (staged ? 2 * kTileM * 128 : 0));
   const BwdWaiter w{&bars->abort_flag, p.ws_header};
 
@@ -308,10 +308,12 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
           w.wait(ptx::smem_u32(&bars->bias_free), (cnt & 1u) ^ 1u);
           const uint32_t bfull = ptx::smem_u32(&bars->bias_full);
           ptx::mbar_expect_tx(bfull, 2 * kTileM * 128);
-          const int brow = (b * p.hq + qh) * p.maxq + srow0;
+          // rows = queries, columns = keys: the streamed rows are queries in the dK/dV pass and keys in the dQ pass
+          const int brow = (b * p.hq + qh) * p.maxq + (kDKV ? srow0 : tile0);
+          const int bcol0 = kDKV ? tile0 : srow0;
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf)
-            ptx::tma_load_2d(sm_bias + hf * (kTileM * 128), &tm_bias, bfull, tile0 + hf * 64, brow);
+            ptx::tma_load_2d(sm_bias + hf * (kTileM * 128), &tm_bias, bfull, bcol0 + hf * 64, brow);
         }
         w.wait(ptx::smem_u32(&bars->b_free[stage]), ((cnt >> 1) & 1u) ^ 1u);
         ptx::mbar_expect_tx(full, 2 * kTileBytes);
@@ -434,7 +436,19 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         // are issued here, ahead of the wait for the products (addresses clamped into the plane: what lies outside
         // the sequence is never used)
         uint32_t bcol[16];
-        if (staged) {
+        if (staged && !kDKV) {
+          if (ch == 0) w.wait(ptx::smem_u32(&bars->bias_full), cnt & 1u);
+          // this query's 32 keys col .. col + 31: box col / 64 (= grp), row = query, four 16-byte chunks from
+          // (col % 64) / 8 on, each ^ (query & 7)
+          const uint32_t rowbase = sm_bias + grp * (kTileM * 128) + row * 128;
+          const uint32_t c16 = static_cast<uint32_t>(col & 63) >> 3;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4)
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(bcol[4 * q4]), "=r"(bcol[4 * q4 + 1]), "=r"(bcol[4 * q4 + 2]), "=r"(bcol[4 * q4 + 3])
+                         : "r"(rowbase + (((c16 + q4) ^ (row & 7)) << 4)));
+          if (ch == 1) ptx::mbar_arrive(ptx::smem_u32(&bars->bias_free));   // this thread has read its row
+        } else if (staged) {
           if (ch == 0) {
             w.wait(ptx::smem_u32(&bars->bias_full), cnt & 1u);
           }
@@ -489,6 +503,13 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         if (all_off) {
 #pragma unroll
           for (int e = 0; e < 16; ++e) u1[e] = u2[e] = 0u;
+        } else if (staged && !kDKV) {
+          // (values of rows / keys outside the sequence are never used: their elements are not visible)
+#pragma unroll
+          for (int e = 0; e < 16; ++e)
+            score_grad2<T, true, true>(make_float2(__uint_as_float(t1[2 * e]), __uint_as_float(t1[2 * e + 1])),
+                                       make_float2(__uint_as_float(t2[2 * e]), __uint_as_float(t2[2 * e + 1])),
+                                       BPack<T>::unpack(bcol[e]), p.alpha, p.scale, (bits >> (2 * e)) & 3u, u1[e], u2[e]);
         } else if (!kDKV && bias_vec && mine_ok && srow0 + col + 32 <= p.maxk) {
           // dQ pass: the 32 bias values of this row and chunk are contiguous - four 16-byte loads
           const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + bias_bh +
@@ -645,13 +666,17 @@ cudaError_t launch_bwd_tc_t(const BwdParams& bp, int dtype, int num_sms, cudaStr
   auto kq = hstu_bwd_tc_kernel<D, T, false>;
   auto kkv = hstu_bwd_tc_kernel<D, T, true>;
   auto kkv_staged = hstu_bwd_tc_kernel<D, T, true, true>;
+  auto kq_staged = hstu_bwd_tc_kernel<D, T, false, true>;
   cudaError_t e = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(kkv_staged, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_kv);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(kq_staged, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_kv);
   if (e != cudaSuccess) return e;
   if (p.total_q > 0) {
     const long long tiles = static_cast<long long>(p.batch) * p.hq * ((p.maxq + kTileM - 1) / kTileM);
-    kq<<<static_cast<unsigned>(tiles < num_sms ? tiles : num_sms), kBwdThreads, smem, stream>>>(bp, mq, mg, mk, mv, mb);
+    const unsigned grid = static_cast<unsigned>(tiles < num_sms ? tiles : num_sms);
+    if (bias_staged) kq_staged<<<grid, kBwdThreads, smem_kv, stream>>>(bp, mq, mg, mk, mv, mb);
+    else kq<<<grid, kBwdThreads, smem, stream>>>(bp, mq, mg, mk, mv, mb);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
