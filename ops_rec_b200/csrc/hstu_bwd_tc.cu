@@ -415,9 +415,29 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
     const bool dbias_vec = dbias && (p.maxk % 8 == 0) && (reinterpret_cast<uintptr_t>(bp.dbias) & 15u) == 0;
     const bool bias_vec = p.bias && (p.maxk % 8 == 0) && (p.bias_bstride % 8 == 0) &&
                           (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;
-    // the dK/dV pass holds the score tile transposed (thread = key): a closed form for the visible queries of a key
-    // exists for the plain causal / no-mask cases; context rows and grouped targets take the per-element rule
-    const bool simple_mask = p.mask_type != HSTU_MASK_TRIL || (s.ctx == 0 && (s.tgt == 0 || p.group == 0));
+    // The dK/dV pass holds the score tile transposed (thread = key), so it needs the queries that see key `mine`:
+    // history queries [c_lo, hq_end) by the causal rule, context rows [0, ctx_hi) for a history key, and the target
+    // queries [t_lo, t_hi) - every target for a history key, else the targets of the key's own group from the key's
+    // own position on (the transpose of row_bounds(); no mask: every query).
+    const bool grouped = p.mask_type == HSTU_MASK_TRIL && s.tgt > 0 && p.group > 0;
+    const int hq_end = grouped ? s.lq - s.tgt : s.lq;
+    int c_lo = 0, ctx_hi = 0, t_lo = 0, t_hi = 0;
+    if (kDKV && p.mask_type == HSTU_MASK_TRIL) {
+      const int hist = s.lk - s.tgt;
+      c_lo = mine - (s.lk - s.lq);
+      if (s.ctx > 0 && mine < hist) ctx_hi = s.ctx < hq_end ? s.ctx : hq_end;
+      if (grouped) {
+        if (mine < hist) {
+          t_lo = hq_end;
+          t_hi = s.lq;
+        } else {
+          const int tj = mine - hist;
+          const int gend = (tj / p.group + 1) * p.group;
+          t_lo = hq_end + tj;
+          t_hi = hq_end + (gend < s.tgt ? gend : s.tgt);
+        }
+      }
+    }
     for_each_step<kDKV>(p, s, tile0, head, [&](int, int srow0, int qh) {
       w.wait(ptx::smem_u32(&bars->t_full), cnt & 1u);
       ptx::tc_fence_after();
@@ -484,17 +504,10 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
           bits = 0xffffffffu;
         } else if (mine >= s.lk) {
           bits = 0u;
-        } else if (simple_mask) {
-          // causal: query i sees key j iff i + (lk - lq) >= j; no mask: every query of the sequence sees it
-          const int i0 = srow0 + col;
-          bits = low_bits(s.lq - i0);
-          if (p.mask_type == HSTU_MASK_TRIL) bits &= ~low_bits(mine - (s.lk - s.lq) - i0);
         } else {
-          bits = 0u;   // context rows / grouped targets: evaluate the reference rule element by element
-          for (int e = 0; e < 32; ++e) {
-            const int i = srow0 + col + e;
-            if (i < s.lq && allowed(row_bounds(s, i, p.mask_type, p.group), mine)) bits |= 1u << e;
-          }
+          const int i0 = srow0 + col;
+          bits = (low_bits(hq_end - i0) & ~low_bits(c_lo - i0)) | low_bits(ctx_hi - i0) |
+                 (low_bits(t_hi - i0) & ~low_bits(t_lo - i0));
         }
         uint32_t u1[16], u2[16];
         // per warp: every element visible -> no selects; nothing visible -> zeros without arithmetic; else selects

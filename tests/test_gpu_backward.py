@@ -267,7 +267,10 @@ def test_inconsistent_inputs_set_the_status_word():
     dict(B=4, Hq=4, Hk=2, maxL=700, bias=True),
     dict(B=3, Hq=4, Hk=1, maxL=400, bias=True, ctx=5, tgt=40, g=3),
     dict(B=3, Hq=2, Hk=2, maxL=300, bias=False, ctx=0, tgt=64, g=1),
+    dict(B=3, Hq=2, Hk=2, maxL=450, bias=True, ctx=130, tgt=150, g=7),
+    dict(B=3, Hq=2, Hk=1, maxL=390, bias=False, ctx=70, tgt=33, g=0),
     dict(B=3, Hq=2, Hk=1, maxL=520, bias=True, delta=True),
+    dict(B=3, Hq=2, Hk=2, maxL=520, bias=True, delta=True, ctx=3, tgt=50, g=2),
     dict(B=2, Hq=2, Hk=2, maxL=260, bias=True, mask_type=2),
 ])
 def test_tensor_core_backward(D, dtype, case):
