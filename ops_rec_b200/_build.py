@@ -48,7 +48,7 @@ def build_lib(force=False, verbose=False):
     srcs = [os.path.join(CSRC, s) for s in CUDA_SOURCES]
     if not force and not _stale(LIB, _deps()):
         return LIB
-    cmd = [_nvcc(), "-O3", "-std=c++17", "-lineinfo", *ARCH, "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared",
+    cmd = [_nvcc(), "-O3", "-std=c++17", "-lineinfo", "--threads", "0", *ARCH, "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared",
            "-cudart", "shared", "-I", os.path.join(ROOT, "include"), "-o", LIB, *srcs]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")

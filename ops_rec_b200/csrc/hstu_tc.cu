@@ -370,7 +370,12 @@ __device__ __forceinline__ void p_half(uint32_t t_s, int grp, int c0, const Bias
   }
 }
 
-template <int D, typename T, int kBias>
+// kRolled: the P/O groups run both Q tiles of an item through one copy of their code.  Their code is most of what the
+// SM's instruction caches have to hold; on batches of many short items - where every item walks through every path:
+// tiles with and without a mask, the end-of-sequence slice, both kinds of output store - instruction-cache misses
+// were the largest stall (batch of 4096 sequences of mean length 270 with a bias: - 21 % time).  Long sequences spend
+// their time in one path and prefer the unrolled form (+ 6 % time rolled), so both exist and the launcher chooses.
+template <int D, typename T, int kBias, bool kRolled>
 __global__ void __launch_bounds__(kThreads, 1)
 hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_bias,
@@ -800,7 +805,9 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     // bf16 works on a = y / 2 (tanh form), fp16 on y itself;  x = c_in * s + c_bias * bias
     const float c_in = kExact ? p.alpha : 0.5f * p.alpha;
     const float c_bias = alpha_first ? (kExact ? 1.f : 0.5f) : c_in;
-    uint32_t s_uses[2] = {0, 0}, o_uses[2] = {0, 0};
+    // (per Q tile, as scalars: the loop over the two tiles is not unrolled - this role's code is what the SM's
+    // instruction caches have to hold, and on batches of short sequences their misses were the largest stall)
+    uint32_t s_uses0 = 0, s_uses1 = 0, o_uses0 = 0, o_uses1 = 0;
     uint32_t out_chunks = 0;              // TMA-store chunks issued so far by this warp (selects the staging buffer)
     // O tiles: this group's half of the columns.  A Q tile that lies wholly inside its sequence leaves through
     // shared memory and TMA stores (32 rows x 32 columns per warp and store, double buffered); a tile cut by the
@@ -813,9 +820,10 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
       T* orow = static_cast<T*>(p.out) + ((ot.q0 + tile_r0 + row) * p.hq + ot.h) * D + col0;
       if (ot.n > 0) {
         const uint32_t t_o = tmem + lane_base + (t == 0 ? kColO0 : C::kColO1) + col0;
-        w.wait(ptx::smem_u32(&bars->o_full[t]), o_uses[t] & 1u);
+        w.wait(ptx::smem_u32(&bars->o_full[t]), (t == 0 ? o_uses0 : o_uses1) & 1u);
         if (w.aborted()) return;  // nothing valid to store; the barriers are left alone
-        ++o_uses[t];
+        if (t == 0) ++o_uses0;
+        else ++o_uses1;
         ptx::tc_fence_after();
         const bool by_tma = C::kOutBytes > 0 && tile_r0 + kTileM <= ot.lq;
 #pragma unroll 1
@@ -875,84 +883,115 @@ hstu_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tm_q, const 
     uint32_t ring_base = 0;   // position of the current item's first K tile in the K/V ring (as the issuers count it)
     for (Item it;;) {
       if (!feed.next(it)) break;
-      int i_row[2];
-      bool row_ok[2];
-      RowBounds rb[2];
-      long long bias_row[2];
+      // Step j of Q tile t: S -> P for this thread's row and its group's 64 columns.  False after an abort.
+      auto tile = [&](const int t, const int j, const bool row_ok, const RowBounds& rb, const long long bias_row) -> bool {
+        const int tile_r0 = it.r0 + t * kTileM;
+        const int c0 = j * kTileN;
+        const bool full = tile_is_full(it.s, tile_r0, kTileM, c0, kTileN, p.mask_type, p.group);
+        const uint32_t t_s = tmem + lane_base + (t == 0 ? kColS0 : kColS1);
+        const uint32_t bar_p = ptx::smem_u32(&bars->p_full[t][0]);
+        // kBias == 2: the 16-column slice of the sequence's last K tile that holds the sequence end (if any) is
+        // added here, not by the tensor cores; the group that owns it fetches it now, before it waits for the scores
+        const int rem = it.s.lk - c0;
+        const int fix_n = (kBias == 2 && rem < kTileN) ? (rem & 15) : 0;
+        const int fix_col = rem & ~15;
+        const bool fix_here = fix_n > 0 && (fix_col >> 6) == grp;   // the same for every thread of the group
+        uint32_t fixv[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+        if (kBias == 2 && fix_here && row_ok) {
+          const T* src = static_cast<const T*>(p.bias) + bias_row + c0 + fix_col;
+          if (c0 + fix_col + 16 <= p.maxk) {  // 32-byte aligned: the rows are 16-byte aligned and c0 + fix_col is a multiple of 16
+            const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(src));
+            const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+            fixv[0] = u0.x, fixv[1] = u0.y, fixv[2] = u0.z, fixv[3] = u0.w;
+            fixv[4] = u1.x, fixv[5] = u1.y, fixv[6] = u1.z, fixv[7] = u1.w;
+          } else {
+            const unsigned short* s16 = reinterpret_cast<const unsigned short*>(src);
 #pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        i_row[t] = it.r0 + t * kTileM + row;
-        row_ok[t] = i_row[t] < it.s.lq;
-        rb[t] = row_bounds(it.s, row_ok[t] ? i_row[t] : it.s.lq - 1, p.mask_type, p.group);
-        bias_row[t] = kBias != 0 ? static_cast<long long>(it.b) * p.bias_bstride +
-                                       (static_cast<long long>(it.h) * p.maxq + i_row[t]) * p.maxk
-                                 : 0;
-      }
-      // Tile 0 usually ends one K tile before tile 1: its output leaves while tile 1's last S tile is computed.
-      // (Keeping tile 1's output back until the next item's first score tile has been served was measured too:
-      // slower on every workload.)
-      const OutTile out0{it.s.q0, it.s.lq, it.r0, it.h, it.n0};
-      bool o0_stored = false;
-      for (int j = 0; j < it.nmax; ++j) {
-        if (!o0_stored && j >= it.n(0)) {
-          store_o(0, out0);
-          o0_stored = true;
-        }
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          if (j >= it.n(t)) continue;
-          const int tile_r0 = it.r0 + t * kTileM;
-          const int c0 = j * kTileN;
-          const bool full = tile_is_full(it.s, tile_r0, kTileM, c0, kTileN, p.mask_type, p.group);
-          const uint32_t t_s = tmem + lane_base + (t == 0 ? kColS0 : kColS1);
-          const uint32_t bar_p = ptx::smem_u32(&bars->p_full[t][0]);
-          // kBias == 2: the 16-column slice of the sequence's last K tile that holds the sequence end (if any) is
-          // added here, not by the tensor cores; the group that owns it fetches it now, before it waits for the scores
-          const int rem = it.s.lk - c0;
-          const int fix_n = (kBias == 2 && rem < kTileN) ? (rem & 15) : 0;
-          const int fix_col = rem & ~15;
-          const bool fix_here = fix_n > 0 && (fix_col >> 6) == grp;   // the same for every thread of the group
-          uint32_t fixv[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-          if (kBias == 2 && fix_here && row_ok[t]) {
-            const T* src = static_cast<const T*>(p.bias) + bias_row[t] + c0 + fix_col;
-            if (c0 + fix_col + 16 <= p.maxk) {  // 32-byte aligned: the rows are 16-byte aligned and c0 + fix_col is a multiple of 16
-              const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(src));
-              const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(src) + 1);
-              fixv[0] = u0.x, fixv[1] = u0.y, fixv[2] = u0.z, fixv[3] = u0.w;
-              fixv[4] = u1.x, fixv[5] = u1.y, fixv[6] = u1.z, fixv[7] = u1.w;
-            } else {
-              const unsigned short* s16 = reinterpret_cast<const unsigned short*>(src);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const uint32_t lo = 2 * e < fix_n ? s16[2 * e] : 0u;
-                const uint32_t hi = 2 * e + 1 < fix_n ? s16[2 * e + 1] : 0u;
-                fixv[e] = lo | (hi << 16);
-              }
+            for (int e = 0; e < 8; ++e) {
+              const uint32_t lo = 2 * e < fix_n ? s16[2 * e] : 0u;
+              const uint32_t hi = 2 * e + 1 < fix_n ? s16[2 * e + 1] : 0u;
+              fixv[e] = lo | (hi << 16);
             }
           }
-          w.wait(ptx::smem_u32(&bars->s_full[t]), s_uses[t] & 1u);
-          if (w.aborted()) break;  // (the item feed then ends the outer loops)
-          ++s_uses[t];
-          ptx::tc_fence_after();
-          // A sequence's last K/V tile holds rows of the NEXT sequence behind the sequence end.  P is 0 there, but
-          // 0 x NaN is not, so group 1 zeroes those V rows in shared memory before it hands P over (generic-proxy
-          // stores, proxy fence, arrive: ordered before this tile's P.V).  The tile has landed: the issuer waited for
-          // it before it issued the S tile whose completion this thread has just seen.
-          // (The stores sit in a function of their own, not inlined: inlined, their mere presence cost the P loop 5 %
-          // on batches that hardly ever run them.)
-          if (grp == 1 && rem < kTileN)
-            zero_v_rows(sm_ring + ((ring_base + 2u * j + 1u) % C::kStages) * C::kTileBytes + rem * 128,
-                        (kTileN - rem) * 8, row, C::kHalves, C::kHalfBytes);
-          const BiasRow br{p.bias, bias_row[t], row_ok[t], bias_vec_ok != 0, p.maxk, it.s.lk};
-          if (kBias == 2 && fix_here) add_end_slice<T>(t_s + fix_col, fixv, fix_n);
-          if (full)
-            p_half<T, kBias, false>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p);
-          else
-            p_half<T, kBias, true>(t_s, grp, c0, br, rb[t], c_in, c_bias, p.scale, bar_p);
         }
+        w.wait(ptx::smem_u32(&bars->s_full[t]), (t == 0 ? s_uses0 : s_uses1) & 1u);
+        if (w.aborted()) return false;  // (the item feed then ends the outer loops)
+        if (t == 0) ++s_uses0;
+        else ++s_uses1;
+        ptx::tc_fence_after();
+        // A sequence's last K/V tile holds rows of the NEXT sequence behind the sequence end.  P is 0 there, but
+        // 0 x NaN is not, so group 1 zeroes those V rows in shared memory before it hands P over (generic-proxy
+        // stores, proxy fence, arrive: ordered before this tile's P.V).  The tile has landed: the issuer waited for
+        // it before it issued the S tile whose completion this thread has just seen.
+        // (The stores sit in a function of their own, not inlined: inlined, their mere presence cost the P loop 5 %
+        // on batches that hardly ever run them.)
+        if (grp == 1 && rem < kTileN)
+          zero_v_rows(sm_ring + ((ring_base + 2u * j + 1u) % C::kStages) * C::kTileBytes + rem * 128,
+                      (kTileN - rem) * 8, row, C::kHalves, C::kHalfBytes);
+        const BiasRow br{p.bias, bias_row, row_ok, bias_vec_ok != 0, p.maxk, it.s.lk};
+        if (kBias == 2 && fix_here) add_end_slice<T>(t_s + fix_col, fixv, fix_n);
+        if (full)
+          p_half<T, kBias, false>(t_s, grp, c0, br, rb, c_in, c_bias, p.scale, bar_p);
+        else
+          p_half<T, kBias, true>(t_s, grp, c0, br, rb, c_in, c_bias, p.scale, bar_p);
+        return true;
+      };
+      if constexpr (kRolled) {
+        // Round j serves step j of both Q tiles through ONE copy of the code (the loop over the tiles is not unrolled,
+        // the output store has one call site); a tile that has finished its last step - or visits nothing at all -
+        // stores its output in the round after it.
+        for (int j = 0; j <= it.nmax; ++j) {
+#pragma unroll 1
+          for (int t = 0; t < 2; ++t) {
+            const int nt = it.n(t);
+            const int tile_r0 = it.r0 + t * kTileM;
+            if (j == nt) store_o(t, OutTile{it.s.q0, it.s.lq, tile_r0, it.h, nt});
+            if (j >= nt) continue;
+            const int i_row = tile_r0 + row;
+            const bool row_ok = i_row < it.s.lq;
+            const RowBounds rb = row_bounds(it.s, row_ok ? i_row : it.s.lq - 1, p.mask_type, p.group);
+            const long long bias_row = kBias != 0 ? static_cast<long long>(it.b) * p.bias_bstride +
+                                                        (static_cast<long long>(it.h) * p.maxq + i_row) * p.maxk
+                                                  : 0;
+            if (!tile(t, j, row_ok, rb, bias_row)) break;
+          }
+          if (w.aborted()) break;
+        }
+      } else {
+        int i_row[2];
+        bool row_ok[2];
+        RowBounds rb[2];
+        long long bias_row[2];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          i_row[t] = it.r0 + t * kTileM + row;
+          row_ok[t] = i_row[t] < it.s.lq;
+          rb[t] = row_bounds(it.s, row_ok[t] ? i_row[t] : it.s.lq - 1, p.mask_type, p.group);
+          bias_row[t] = kBias != 0 ? static_cast<long long>(it.b) * p.bias_bstride +
+                                         (static_cast<long long>(it.h) * p.maxq + i_row[t]) * p.maxk
+                                   : 0;
+        }
+        // Tile 0 usually ends one K tile before tile 1: its output leaves while tile 1's last S tile is computed.
+        // (Keeping tile 1's output back until the next item's first score tile has been served was measured too:
+        // slower on every workload.)
+        const OutTile out0{it.s.q0, it.s.lq, it.r0, it.h, it.n0};
+        bool o0_stored = false;
+        for (int j = 0; j < it.nmax; ++j) {
+          if (!o0_stored && j >= it.n(0)) {
+            store_o(0, out0);
+            o0_stored = true;
+          }
+          bool ok = true;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (j >= it.n(t) || !ok) continue;
+            ok = tile(t, j, row_ok[t], rb[t], bias_row[t]);
+          }
+          if (!ok) break;
+        }
+        if (!o0_stored) store_o(0, out0);
+        store_o(1, OutTile{it.s.q0, it.s.lq, it.r0 + kTileM, it.h, it.n1});
       }
-      if (!o0_stored) store_o(0, out0);
-      store_o(1, OutTile{it.s.q0, it.s.lq, it.r0 + kTileM, it.h, it.n1});
       ring_base += 2u * it.nmax;
     }
     if (C::kOutBytes > 0 && lane == 0) ptx::bulk_wait<0>();  // this thread's TMA stores have completed
@@ -1028,11 +1067,11 @@ bool make_out_map(CUtensorMap* m, const KParams& p, int dtype) {
             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D, typename T, int kBias>
+template <int D, typename T, int kBias, bool kRolled>
 cudaError_t launch_inst(const KParams& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                         const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mc, int bias_vec_ok, int grid,
                         cudaStream_t stream) {
-  auto kern = hstu_tc_kernel<D, T, kBias>;
+  auto kern = hstu_tc_kernel<D, T, kBias, kRolled>;
   constexpr int smem = Cfg<D, kBias>::kSmemBytes;
   static_assert(smem <= 232448, "shared memory budget of one CTA exceeded");
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -1143,11 +1182,19 @@ cudaError_t launch_tc(const KParams& p_in, int dtype, int num_sms, cudaStream_t 
   // hstu_paged with direct page reads: the cache as one K / V tensor of num_pages * 2 * 128 rows
   CUtensorMap mc = mk;
   if (p.paged_direct && !make_map(&mc, p.kv_cache, p.num_pages * 2 * kTileN, p.hk, p.dqk, dtype)) return cudaErrorNotSupported;
-#define HSTU_TC_CASE(DD, TT)                                                                       \
-  return bias_mode == 3   ? launch_inst<DD, TT, 3>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream)  \
-         : bias_mode == 2 ? launch_inst<DD, TT, 2>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream)  \
-         : bias_mode == 1 ? launch_inst<DD, TT, 1>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream)  \
-                          : launch_inst<DD, TT, 0>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream)
+  // Which form of the P/O code (see the kernel): the rolled one for batches of short sequences, where every item
+  // walks through every path of that code, the unrolled one where long sequences keep it in one path.  Measured
+  // (B200, in-process A/B): mean length 270 with a bias - 21 % time rolled, without - 10 %; mean 640 with a bias - 4 %,
+  // without + 3 %; mean 2400 + 6 %.
+  const long long mean_len = p.batch > 0 ? p.total_q / p.batch : 0;
+  const bool rolled = mean_len < 512 || (bias_mode == 2 && mean_len < 1024);
+#define HSTU_TC_CASE(DD, TT)                                                                                       \
+  if (rolled && bias_mode == 2) return launch_inst<DD, TT, 2, true>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream);  \
+  if (rolled && bias_mode == 0) return launch_inst<DD, TT, 0, true>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream);  \
+  return bias_mode == 3   ? launch_inst<DD, TT, 3, false>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream)             \
+         : bias_mode == 2 ? launch_inst<DD, TT, 2, false>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream)             \
+         : bias_mode == 1 ? launch_inst<DD, TT, 1, false>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream)             \
+                          : launch_inst<DD, TT, 0, false>(p, mq, mk, mv, mb, mo, mc, vec_ok, g, stream)
   if (dtype == HSTU_DTYPE_BF16) {
     if (p.dqk == 128) { HSTU_TC_CASE(128, __nv_bfloat16); }
     HSTU_TC_CASE(64, __nv_bfloat16);
