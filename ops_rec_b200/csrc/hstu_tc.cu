@@ -114,6 +114,24 @@ struct Barriers {
 };
 static_assert(sizeof(Barriers) <= 2048, "barrier block too large");
 
+// The waiting loop of Waiter::wait, one copy for every wait of the kernel (the fast path - the phase is already
+// complete - stays inline): less code for the instruction caches, and the warps that spin all spin in the same lines.
+__device__ __noinline__ void wait_slow(int* abort_flag, uint32_t* status, uint32_t bar, uint32_t parity) {
+  if (*reinterpret_cast<volatile int*>(abort_flag)) return;
+  const long long t0 = clock64();
+  unsigned spins = 0;
+  while (!ptx::mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3ffu) == 0) {
+      if (*reinterpret_cast<volatile int*>(abort_flag)) return;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *reinterpret_cast<volatile int*>(abort_flag) = 1;
+        atomicOr(status, static_cast<uint32_t>(HSTU_ST_PIPE_TIMEOUT));
+        return;
+      }
+    }
+  }
+}
+
 struct Waiter {
   int* abort_flag;
   uint32_t* status;
@@ -125,19 +143,7 @@ struct Waiter {
   __device__ __forceinline__ bool aborted() const { return *reinterpret_cast<volatile int*>(abort_flag) != 0; }
   __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity) const {
     if (ptx::mbar_try_wait(bar, parity)) return;
-    if (*reinterpret_cast<volatile int*>(abort_flag)) return;
-    const long long t0 = clock64();
-    unsigned spins = 0;
-    while (!ptx::mbar_try_wait(bar, parity)) {
-      if ((++spins & 0x3ffu) == 0) {
-        if (*reinterpret_cast<volatile int*>(abort_flag)) return;
-        if (clock64() - t0 > kWaitLimitCycles) {
-          *reinterpret_cast<volatile int*>(abort_flag) = 1;
-          atomicOr(status, static_cast<uint32_t>(HSTU_ST_PIPE_TIMEOUT));
-          return;
-        }
-      }
-    }
+    wait_slow(abort_flag, status, bar, parity);
   }
 };
 

@@ -211,6 +211,17 @@ def test_medium_batches_take_the_limited_look_ahead(rab):
     assert torch.equal(out, again)
 
 
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("rab,lo,hi", [(None, 200, 420), (None, 1030, 1300), ("shared3", 600, 900), ("shared3", 1030, 1300)])
+def test_both_forms_of_the_score_stage(D, rab, lo, hi):
+    """The kernel exists with its P/O code rolled (short sequences) and unrolled (long ones); the launcher picks by
+    mean length and bias mode: below 512 / 1024 with a staged bias rolled, above unrolled."""
+    args = make_case(3, 2, 1, D, D, lo, hi, BF16, seed=lo + D, rab=rab, tgt=20, g=1)
+    out, status = run_cabi(args)
+    assert status == 0
+    assert_parity(out, args, label=f"D{D} rab={rab} lengths {lo}-{hi}")
+
+
 def test_results_are_bitwise_reproducible():
     args = make_case(8, 4, 4, 128, 128, 1, 900, BF16, seed=17, rab="batch")
     a, _ = run_cabi(args)
