@@ -32,52 +32,75 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
   // for this grid to complete before it reads the work list.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
+  // (this kernel's latency is part of every call: the attention kernel's first item waits for it.  Hence one
+  // read of the offsets for the first 1024 sequences, and a warp-wide scan instead of a serial walk over the buckets.)
   for (int i = tid; i < kBuckets; i += kPreThreads) {
     s_count[i] = 0;
     s_seen[i] = 0;
   }
+  for (int i = tid; i < 32 * kBuckets; i += kPreThreads) (&s_warp[0][0])[i] = 0;
   if (tid == 0) s_status = 0;
   __syncthreads();
 
   unsigned st = 0;
+  int key_first = 0;   // bucket of sequence `tid` (the first chunk of the second pass)
   for (int b = tid; b < p.batch; b += kPreThreads) {
     st |= check_seq(p, b) | check_pages(p, b);
     if (build_items) {
       const SeqInfo s = load_seq(p, b);
-      atomicAdd(&s_count[pairs_of(s.lq)], 1u);
+      const int key = pairs_of(s.lq);
+      if (b == tid) key_first = key;
+      atomicAdd(&s_count[key], 1u);
     }
   }
   if (st) atomicOr(&s_status, st);
   __syncthreads();
-  if (tid == 0) {
-    p.ws_header[0] = s_status;
-    p.ws_header[2] = 0;   // work counters (forward; backward dQ pass)
-    p.ws_header[3] = 0;   // (backward dK/dV pass)
-    unsigned run = 0;
-    for (int key = kMaxPairs; key >= 1; --key) {
-      s_start[key] = run;
-      run += s_count[key] * static_cast<unsigned>(key) * static_cast<unsigned>(p.hq);
+  if (warp == 0) {
+    // s_start[key] = items of all larger keys: an exclusive scan from the largest key down, three keys per lane
+    // (lane 0 holds the largest)
+    unsigned v[3], sum = 0;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const int key = kMaxPairs - (3 * lane + i);
+      v[i] = key >= 1 ? s_count[key] * static_cast<unsigned>(key) * static_cast<unsigned>(p.hq) : 0u;
+      sum += v[i];
     }
-    s_start[0] = run;
-    // never more than the list holds: offsets that are not monotone can describe more q-pairs than total_q has
-    // rows for (the host sizes the list from total_q); the surplus items are dropped, the status word says why
-    if (static_cast<long long>(run) > p.item_capacity) run = static_cast<unsigned>(p.item_capacity);
-    p.ws_header[1] = build_items ? run : 0u;
+    unsigned incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const unsigned o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    unsigned run = incl - sum;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const int key = kMaxPairs - (3 * lane + i);
+      if (key >= 0) s_start[key] = run;
+      run += v[i];
+    }
+    if (lane == 31) {
+      // never more than the list holds: offsets that are not monotone can describe more q-pairs than total_q has
+      // rows for (the host sizes the list from total_q); the surplus items are dropped, the status word says why
+      unsigned total = incl;
+      if (static_cast<long long>(total) > p.item_capacity) total = static_cast<unsigned>(p.item_capacity);
+      p.ws_header[0] = s_status;
+      p.ws_header[2] = 0;   // work counters (forward; backward dQ pass)
+      p.ws_header[3] = 0;   // (backward dK/dV pass)
+      p.ws_header[1] = build_items ? total : 0u;
+    }
   }
   if (!build_items) return;
   __syncthreads();
 
   for (int base = 0; base < p.batch; base += kPreThreads) {
-    for (int i = tid; i < 32 * kBuckets; i += kPreThreads) (&s_warp[0][0])[i] = 0;
-    __syncthreads();
+    if (base > 0) {
+      for (int i = tid; i < 32 * kBuckets; i += kPreThreads) (&s_warp[0][0])[i] = 0;
+      __syncthreads();
+    }
     const int b = base + tid;
     const bool live = b < p.batch;
     int key = 0;
-    SeqInfo s;
-    if (live) {
-      s = load_seq(p, b);
-      key = pairs_of(s.lq);
-    }
+    if (live) key = base == 0 ? key_first : pairs_of(load_seq(p, b).lq);
     // rank among the lanes of this warp that hold the same key (idle lanes use key -1 and are ignored)
     const unsigned same = __match_any_sync(0xffffffffu, live ? key : -1);
     const unsigned rank_in_warp = __popc(same & ((1u << lane) - 1u));
