@@ -15,6 +15,7 @@
 namespace hstu {
 cudaError_t launch_generic(const KParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_prepass(const KParams& p, bool build_items, cudaStream_t stream);
+cudaError_t launch_bwd_prepass(const KParams& p, cudaStream_t stream);
 long long plan_host(const KParams& p, uint32_t* items, long long capacity, uint32_t* status);
 bool tc_supported(const KParams& p, int dtype);
 cudaError_t launch_tc(const KParams& p, int dtype, int num_sms, cudaStream_t stream);
@@ -360,12 +361,25 @@ static int validate_bwd(const HstuJaggedBwdArgs* a) {
   return HSTU_OK;
 }
 
+// Upper bounds of the backward's two tile lists that need no device data: every sequence adds at most one partial
+// tile per head; with a grad_bias the dQ pass visits every q-tile slot (rows past a sequence's end must be zeroed).
+static void bwd_list_bounds(const HstuJaggedArgs* f, long long* cap_q, long long* cap_k) {
+  const long long slots_q = static_cast<long long>(f->batch) * ((f->max_seq_len_q + hstu::kTileM - 1) / hstu::kTileM);
+  *cap_q = static_cast<long long>(f->heads_q) * (f->attn_bias ? slots_q : f->total_q / hstu::kTileM + f->batch);
+  *cap_k = static_cast<long long>(f->heads_k) * (f->total_k / hstu::kTileN + f->batch);
+}
+static uint64_t bwd_workspace_bytes(const HstuJaggedArgs* f) {
+  long long cap_q, cap_k;
+  bwd_list_bounds(f, &cap_q, &cap_k);
+  return hstu::kWsHeaderBytes + 8ull * static_cast<uint64_t>(cap_q + cap_k);
+}
+
 int hstu_jagged_bwd_get_workspace_size(const HstuJaggedBwdArgs* args, uint64_t* workspace_bytes) {
   g_err[0] = 0;
   if (!workspace_bytes) return fail(HSTU_E_NULL, "workspace_bytes is null");
   int rc = validate_bwd(args);
   if (rc) return rc;
-  *workspace_bytes = hstu::kWsHeaderBytes;  // status word only
+  *workspace_bytes = bwd_workspace_bytes(&args->fwd);  // status word, work counters and the two tile lists
   return HSTU_OK;
 }
 
@@ -379,12 +393,12 @@ int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t wor
   if (f->total_k > 0 && (!f->k || !f->v || !args->grad_k || !args->grad_v))
     return fail(HSTU_E_NULL, "k / v / grad_k / grad_v is null");
   if (f->attn_bias && !args->grad_bias) return fail(HSTU_E_NULL, "grad_bias is null but attn_bias is given");
-  if (!workspace) return fail(HSTU_E_WORKSPACE, "workspace is null (%llu bytes needed)",
-                              (unsigned long long)hstu::kWsHeaderBytes);
+  const uint64_t ws_need = bwd_workspace_bytes(f);
+  if (!workspace) return fail(HSTU_E_WORKSPACE, "workspace is null (%llu bytes needed)", (unsigned long long)ws_need);
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(HSTU_E_WORKSPACE, "workspace must be 256-byte aligned");
-  if (workspace_bytes < hstu::kWsHeaderBytes)
+  if (workspace_bytes < ws_need)
     return fail(HSTU_E_WORKSPACE, "workspace has %llu bytes, %llu needed", (unsigned long long)workspace_bytes,
-                (unsigned long long)hstu::kWsHeaderBytes);
+                (unsigned long long)ws_need);
   DeviceInfo dev;
   rc = device_info(&dev);
   if (rc) return rc;
@@ -392,13 +406,19 @@ int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t wor
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   hstu::BwdParams bp;
-  bp.f = to_params(f, workspace, hstu::kWsHeaderBytes);
+  bp.f = to_params(f, workspace, ws_need);
   bp.dout = args->grad_out;
   bp.dq = args->grad_q;
   bp.dk = args->grad_k;
   bp.dv = args->grad_v;
   bp.dbias = f->attn_bias ? args->grad_bias : nullptr;
-  cudaError_t e = hstu::launch_prepass(bp.f, false, stream);  // input consistency -> status word
+  // input consistency -> status word; for the tensor-core kernels also their two tile lists
+  const bool tc = hstu::bwd_tc_supported(bp, f->dtype);
+  if (tc) {
+    bwd_list_bounds(f, &bp.f.bwd_cap_q, &bp.f.bwd_cap_k);
+    bp.f.bwd_all_q_tiles = bp.dbias ? 1 : 0;
+  }
+  cudaError_t e = tc ? hstu::launch_bwd_prepass(bp.f, stream) : hstu::launch_prepass(bp.f, false, stream);
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "pre-pass launch: %s", cudaGetErrorString(e));
   if (f->total_q == 0 && bp.dbias) {
     // no query rows: no kernel visits grad_bias, and every element of it is promised to be written
@@ -410,7 +430,7 @@ int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t wor
     bp.f.bias = nullptr;   // (nothing reads the bias either)
   }
   if (f->total_q == 0 && f->total_k == 0) return HSTU_OK;
-  if (hstu::bwd_tc_supported(bp, f->dtype)) {
+  if (tc) {
     e = hstu::launch_bwd_tc(bp, f->dtype, dev.sms, stream);
     if (e == cudaErrorNotSupported) return fail(HSTU_E_CUDA, "cuTensorMapEncodeTiled failed or is unavailable");
   } else {

@@ -75,7 +75,9 @@ struct BwdBars {
   uint64_t bias_full, bias_free;   // dK/dV pass with a staged bias tile: landed / read by all 256 element-wise threads
   uint32_t tmem_base;
   int abort_flag;
-  int item;                    // the tile every thread of the CTA works on next (-1: none left)
+  int item;                    // -1: no tile left; else the tile every thread of the CTA works on next:
+  int item_seq;                //   its sequence,
+  uint32_t item_head_tile;     //   head << 16 | tile index (the pre-pass's list entry)
 };
 
 struct BwdWaiter {
@@ -218,12 +220,12 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   ptx::tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
-  // Persistent CTAs take tiles from a counter in the workspace (zeroed by the pre-pass).  Tile order: all tiles of a
-  // (sequence, head) are neighbours, so the CTAs that run together stream the same K/V (Q/dO) rows out of L2, and
-  // the tiles with the most steps of a sequence come first (dQ pass: its last q-tile; dK/dV pass: its first keys).
+  // Persistent CTAs take tiles from the pre-pass's list of this pass through a counter in the workspace (zeroed by
+  // the pre-pass).  Order of the list: all tiles of a (sequence, head) are neighbours, so the CTAs that run together
+  // stream the same K/V (Q/dO) rows out of L2, and the tiles with the most steps of a sequence come first (dQ pass:
+  // its last q-tile; dK/dV pass: its first keys).
   const int heads = kDKV ? p.hk : p.hq;
-  const int ntiles = ((kDKV ? p.maxk : p.maxq) + kTileM - 1) / kTileM;
-  const unsigned total = static_cast<unsigned>(p.batch) * heads * ntiles;
+  const uint32_t* list = p.items + (kDKV ? 2 * p.bwd_cap_q : 0);
   uint32_t* counter = p.ws_header + (kDKV ? 3 : 2);
   uint32_t cnt = 0;          // steps so far (every role counts them alike): barrier phases run on across tiles
   uint32_t tiles_done = 0;   // tiles so far: phase of a_full / acc_full
@@ -231,28 +233,22 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   if (tid == 0) {
     int found = -1;
     if (!*reinterpret_cast<volatile int*>(&bars->abort_flag)) {
-      for (;;) {
-        const unsigned idx = atomicAdd(counter, 1u);
-        if (idx >= total) break;
-        const int bh = idx / ntiles, tpos = idx - bh * ntiles;
-        const int t0 = (kDKV ? tpos : ntiles - 1 - tpos) * kTileM;
-        const SeqInfo cs = load_seq(p, bh / heads);
-        // (a q-tile past the sequence end still has its d_bias rows to clear)
-        if (t0 < (kDKV ? cs.lk : cs.lq) || (!kDKV && bp.dbias && t0 < p.maxq)) {
-          found = static_cast<int>(idx);
-          break;
-        }
+      const unsigned idx = atomicAdd(counter, 1u);
+      if (idx < p.ws_header[kDKV ? 4 : 1]) {
+        const uint2 e = *reinterpret_cast<const uint2*>(list + 2ull * idx);
+        bars->item_seq = static_cast<int>(e.x);
+        bars->item_head_tile = e.y;
+        found = 0;
       }
     }
     bars->item = found;
   }
   __syncthreads();
-  const int item = *reinterpret_cast<volatile int*>(&bars->item);
-  if (item < 0) break;
-  const int bh = item / ntiles, tpos = item - bh * ntiles;
-  const int b = bh / heads;
-  const int head = bh - b * heads;                       // dQ pass: query head; dK/dV pass: kv head
-  const int tile0 = (kDKV ? tpos : ntiles - 1 - tpos) * kTileM;   // first query row (dQ) / first key (dK/dV)
+  if (*reinterpret_cast<volatile int*>(&bars->item) < 0) break;
+  const int b = *reinterpret_cast<volatile int*>(&bars->item_seq);
+  const uint32_t head_tile = *reinterpret_cast<volatile uint32_t*>(&bars->item_head_tile);
+  const int head = static_cast<int>(head_tile >> 16);    // dQ pass: query head; dK/dV pass: kv head
+  const int tile0 = static_cast<int>(head_tile & 0xffffu) * kTileM;   // first query row (dQ) / first key (dK/dV)
   const SeqInfo s = load_seq(p, b);
   const int len = kDKV ? s.lk : s.lq;
   const uint32_t first = cnt;

@@ -66,6 +66,11 @@ struct KParams {
   // rows - goes through the staging tensors
   const void* kv_cache;       // [num_pages, 2, page_size, hk, d]
   int paged_direct;
+  // backward on the tensor-core kernels only (0 otherwise): `items` holds two tile lists, bwd_cap_q entries for the
+  // dQ pass followed by bwd_cap_k for the dK/dV pass; bwd_all_q_tiles: the dQ pass also visits the q-tiles past a
+  // sequence's end (they hold rows of grad_bias that must be zeroed)
+  long long bwd_cap_q, bwd_cap_k;
+  int bwd_all_q_tiles;
 };
 
 // Backward call: the forward's parameters plus the gradient tensors.

@@ -134,6 +134,113 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
   }
 }
 
+// Pre-pass of the tensor-core backward: input check, and the two tile lists its persistent kernels draw from - the
+// (sequence, query head, 128-row q-tile) triples of the dQ pass and the (sequence, kv head, 128-key tile) triples of
+// the dK/dV pass, only tiles that exist (a batch of short sequences under a large max_seq_len has few of the
+// batch x heads x max_seq_len / 128 slots filled).  Order: sequences as they come, inside a sequence head-major, and
+// inside a head the tiles with the most steps first (dQ: the last q-tile; dK/dV: the first keys) - the CTAs that run
+// together then stream the same K/V (Q/dO) rows out of L2.  Entry: [sequence, head << 16 | tile].
+// header[1] / header[4] = entries of the dQ / dK/dV list, header[2] / header[3] = the two work counters.
+__global__ void __launch_bounds__(kPreThreads) hstu_bwd_prepass_kernel(const KParams p) {
+  __shared__ unsigned s_wq[32], s_wk[32];   // per-warp tile counts of the current chunk, then exclusive prefix
+  __shared__ unsigned s_carry_q, s_carry_k; // tiles of all earlier chunks
+  __shared__ unsigned s_status;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    s_carry_q = 0;
+    s_carry_k = 0;
+    s_status = 0;
+  }
+  __syncthreads();
+  const int all_q = (p.maxq + kTileM - 1) / kTileM;
+  uint32_t* list_q = p.items;
+  uint32_t* list_k = p.items + 2 * p.bwd_cap_q;
+  unsigned st = 0;
+  for (int base = 0; base < p.batch; base += kPreThreads) {
+    const int b = base + tid;
+    unsigned nq = 0, nk = 0;
+    if (b < p.batch) {
+      st |= check_seq(p, b) | check_pages(p, b);
+      const SeqInfo s = load_seq(p, b);
+      nq = p.bwd_all_q_tiles ? all_q : (s.lq + kTileM - 1) / kTileM;
+      nk = (s.lk + kTileN - 1) / kTileN;
+    }
+    // exclusive scan of (nq, nk) over the chunk
+    unsigned iq = nq, ik = nk;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const unsigned oq = __shfl_up_sync(0xffffffffu, iq, d), ok = __shfl_up_sync(0xffffffffu, ik, d);
+      if (lane >= d) {
+        iq += oq;
+        ik += ok;
+      }
+    }
+    if (lane == 31) {
+      s_wq[warp] = iq;
+      s_wk[warp] = ik;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      const unsigned vq = s_wq[lane], vk = s_wk[lane];
+      unsigned aq = vq, ak = vk;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const unsigned oq = __shfl_up_sync(0xffffffffu, aq, d), ok = __shfl_up_sync(0xffffffffu, ak, d);
+        if (lane >= d) {
+          aq += oq;
+          ak += ok;
+        }
+      }
+      s_wq[lane] = aq - vq;
+      s_wk[lane] = ak - vk;
+    }
+    __syncthreads();
+    const long long first_q = static_cast<long long>(s_carry_q + s_wq[warp] + (iq - nq)) * p.hq;
+    const long long first_k = static_cast<long long>(s_carry_k + s_wk[warp] + (ik - nk)) * p.hk;
+    for (int h = 0; h < p.hq; ++h)
+      for (unsigned t = 0; t < nq; ++t) {
+        const long long at = first_q + static_cast<long long>(h) * nq + t;
+        if (at < p.bwd_cap_q) {
+          list_q[2 * at] = static_cast<uint32_t>(b);
+          list_q[2 * at + 1] = (static_cast<uint32_t>(h) << 16) | (nq - 1u - t);
+        }
+      }
+    for (int h = 0; h < p.hk; ++h)
+      for (unsigned t = 0; t < nk; ++t) {
+        const long long at = first_k + static_cast<long long>(h) * nk + t;
+        if (at < p.bwd_cap_k) {
+          list_k[2 * at] = static_cast<uint32_t>(b);
+          list_k[2 * at + 1] = (static_cast<uint32_t>(h) << 16) | t;
+        }
+      }
+    __syncthreads();
+    if (tid == kPreThreads - 1) {   // (its inclusive sums are the chunk's totals)
+      s_carry_q += s_wq[warp] + iq;
+      s_carry_k += s_wk[warp] + ik;
+    }
+    __syncthreads();
+  }
+  if (st) atomicOr(&s_status, st);
+  __syncthreads();
+  if (tid == 0) {
+    // never more than the lists hold: offsets that are not monotone can describe more tiles than the tensors have
+    // rows for (the host sizes the lists from total_q / total_k); the surplus is dropped, the status word says why
+    long long tq = static_cast<long long>(s_carry_q) * p.hq, tk = static_cast<long long>(s_carry_k) * p.hk;
+    if (tq > p.bwd_cap_q) tq = p.bwd_cap_q;
+    if (tk > p.bwd_cap_k) tk = p.bwd_cap_k;
+    p.ws_header[0] = s_status;
+    p.ws_header[1] = static_cast<uint32_t>(tq);
+    p.ws_header[2] = 0;
+    p.ws_header[3] = 0;
+    p.ws_header[4] = static_cast<uint32_t>(tk);
+  }
+}
+
+cudaError_t launch_bwd_prepass(const KParams& p, cudaStream_t stream) {
+  hstu_bwd_prepass_kernel<<<1, kPreThreads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_prepass(const KParams& p, bool build_items, cudaStream_t stream) {
   hstu_prepass_kernel<<<1, kPreThreads, 0, stream>>>(p, build_items ? 1 : 0);
   return cudaGetLastError();

@@ -237,6 +237,21 @@ def test_padded_bias_stride_is_rejected():
     assert rc == -2 and b"bias_batch_stride" in cabi.load().hstu_last_error()
 
 
+@pytest.mark.parametrize("B,lo_hi,maxL,bias", [(40, (1, 300), 1500, False), (24, (1, 200), 700, True),
+                                               (1100, (1, 40), 64, True), (1300, (1, 30), 256, False)])
+def test_tile_lists_of_short_sequences_under_a_large_max_seq_len(B, lo_hi, maxL, bias):
+    """The tensor-core kernels draw their tiles from lists the pre-pass writes: only tiles that exist (most of the
+    batch x heads x max_seq_len / 128 slots are empty here), more than 1024 sequences (the pre-pass scans in chunks)."""
+    grad, args = make_bwd_case(B, 2, 1, 64, 64, lo_hi[1], BF16, seed=B, bias=False, alpha=1.0 / 64)
+    args["max_seq_len"] = args["max_seq_len_k"] = maxL
+    if bias:
+        gen = torch.Generator().manual_seed(B)
+        args["attn_bias"] = (torch.rand(B, 2, maxL, maxL, generator=gen) * 2 - 1).to(BF16)
+    got, status = run_bwd(grad, args)
+    assert status == 0
+    assert_bwd_parity(got, grad, args, label=f"B{B} maxL{maxL} bias={bias}")
+
+
 def test_no_query_rows_still_writes_every_element_of_grad_bias():
     # all sequences empty: no kernel visits grad_bias, which must come back as zeros, not as uninitialised memory
     B, H, S, D = 3, 2, 40, 64
