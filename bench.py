@@ -371,12 +371,14 @@ def run_also(ops_rec, W, dev, peaks, names=("cfg2", "cfg3", "cfg5"), reps=12):
         f()
     out["fixed_cost_us"] = time_cold(f, flush, reps) * 1e3
     del kw
-    # the backward of the operator (hstu_jagged_backward: 2.5 x the forward's FLOPs) on cfg4 and cfg3, and the
+    # the backward of the operator (hstu_jagged_backward: 2.5 x the forward's FLOPs) on cfg4, cfg3 and cfg5 (without rab), and the
     # operator that produces q / k / v (distance_in_linear_silu, m = 65536, k = 1024, n = 4096): device-resident,
     # a few back-to-back steps each, CUDA events
     hb = ops_rec.ascendc.attention.hstu_jagged_backward
-    for name, steps in (("cfg4", 5), ("cfg3", 12)):
+    for name, steps in (("cfg4", 5), ("cfg3", 12), ("cfg5", 8)):
         w = W.make_workload(name)
+        if name == "cfg5":
+            w.rab = None   # cfg5's rab is shared by the batch; the backward takes a per-sequence bias only
         kw = W.materialize(w, dev)
         grad = torch.randn_like(kw["q"]) * 0.1
         ctx = None if kw["num_target"] is None else torch.zeros_like(kw["num_target"])
@@ -397,6 +399,8 @@ def run_also(ops_rec, W, dev, peaks, names=("cfg2", "cfg3", "cfg5"), reps=12):
         out["backward_" + name] = {"value": tf, "unit": UNIT, "ms_per_step": ms, "steps": steps,
                                    "tensor_frac": tf / peaks["tflops_burst"], "l2": "warm (back to back)",
                                    "flops": "2.5 x forward (S, dP, dV, dK, dQ; recomputation not counted)"}
+        if name == "cfg5":
+            out["backward_" + name]["workload"] = "cfg5 without its rab (shared by the batch: no per-sequence gradient)"
         del kw, grad
         torch.cuda.empty_cache()
     m, k, n = 65536, 1024, 4096

@@ -22,6 +22,8 @@
 // Every mbarrier wait is bounded; a wait that gives up sets HSTU_ST_PIPE_TIMEOUT and a CTA-wide abort flag, the
 // kernel still drains its TMA loads, frees its tensor memory and returns.
 #include <cuda.h>
+
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -75,9 +77,11 @@ struct BwdBars {
   uint64_t bias_full, bias_free;   // dK/dV pass with a staged bias tile: landed / read by all 256 element-wise threads
   uint32_t tmem_base;
   int abort_flag;
-  int item;                    // -1: no tile left; else the tile every thread of the CTA works on next:
-  int item_seq;                //   its sequence,
-  uint32_t item_head_tile;     //   head << 16 | tile index (the pre-pass's list entry)
+  // the tiles this CTA has drawn, two slots used in turn:
+  int item[2];                 // -1: no tile left; else the tile every thread of the CTA works on:
+  int item_seq[2];             //   its sequence,
+  uint32_t item_head_tile[2];  //   head << 16 | tile index (the pre-pass's list entry)
+  uint32_t n_list;             // entries of this pass's tile list (read once, by thread 0)
 };
 
 struct BwdWaiter {
@@ -161,7 +165,7 @@ __device__ __forceinline__ void score_grad2(float2 s, float2 dp, float2 bias, fl
 
 // kStaged (dK/dV pass with a bias that TMA can tile): a kernel of its own - the same code merely present in the
 // bias-free kernel cost that one 4 %.
-template <int D, typename T, bool kDKV, bool kStaged = false>
+template <int D, typename T, bool kDKV, bool kStaged, bool kAhead>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1,
                    const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_b1,
@@ -229,24 +233,42 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   uint32_t* counter = p.ws_header + (kDKV ? 3 : 2);
   uint32_t cnt = 0;          // steps so far (every role counts them alike): barrier phases run on across tiles
   uint32_t tiles_done = 0;   // tiles so far: phase of a_full / acc_full
-  for (;;) {
-  if (tid == 0) {
+  // With many tiles per CTA the next tile is drawn while the current one runs (by a thread of the warp that has no
+  // role in a tile), so its atomic and the dependent load of the list entry cost nothing at the tile boundary.  With
+  // few, a tile drawn early is a tile that cannot go to a CTA that has run dry - measured: - 7 % on a batch with four
+  // tiles per CTA - and the tile is drawn when the last one is complete.  (kAhead, chosen by the launcher from the
+  // number of token rows: an instantiation of its own, because the code of the one form cost the other 3 %.)
+  auto draw = [&](const uint32_t slot) {   // (one thread)
     int found = -1;
     if (!*reinterpret_cast<volatile int*>(&bars->abort_flag)) {
       const unsigned idx = atomicAdd(counter, 1u);
-      if (idx < p.ws_header[kDKV ? 4 : 1]) {
+      if (idx < *reinterpret_cast<volatile uint32_t*>(&bars->n_list)) {
         const uint2 e = *reinterpret_cast<const uint2*>(list + 2ull * idx);
-        bars->item_seq = static_cast<int>(e.x);
-        bars->item_head_tile = e.y;
+        bars->item_seq[slot] = static_cast<int>(e.x);
+        bars->item_head_tile[slot] = e.y;
         found = 0;
       }
     }
-    bars->item = found;
+    bars->item[slot] = found;
+  };
+  if (tid == 0) {
+    bars->n_list = p.ws_header[kDKV ? 4 : 1];
+    draw(0);
   }
   __syncthreads();
-  if (*reinterpret_cast<volatile int*>(&bars->item) < 0) break;
-  const int b = *reinterpret_cast<volatile int*>(&bars->item_seq);
-  const uint32_t head_tile = *reinterpret_cast<volatile uint32_t*>(&bars->item_head_tile);
+  constexpr bool ahead = kAhead;
+  uint32_t draws = 0;        // tiles drawn and read so far by this CTA (every thread counts alike)
+  for (;;) {
+  if (!ahead && draws > 0) {
+    if (tid == 0) draw(draws & 1u);
+    __syncthreads();
+  }                          // (ahead: the end-of-tile barrier has published the next slot)
+  const uint32_t slot = draws & 1u;
+  if (*reinterpret_cast<volatile int*>(&bars->item[slot]) < 0) break;
+  const int b = *reinterpret_cast<volatile int*>(&bars->item_seq[slot]);
+  const uint32_t head_tile = *reinterpret_cast<volatile uint32_t*>(&bars->item_head_tile[slot]);
+  ++draws;
+  if (ahead && tid == 64) draw(draws & 1u);
   const int head = static_cast<int>(head_tile >> 16);    // dQ pass: query head; dK/dV pass: kv head
   const int tile0 = static_cast<int>(head_tile & 0xffffu) * kTileM;   // first query row (dQ) / first key (dK/dV)
   const SeqInfo s = load_seq(p, b);
@@ -672,30 +694,32 @@ cudaError_t launch_bwd_tc_t(const BwdParams& bp, int dtype, int num_sms, cudaStr
   const int bias_staged = p.bias && (p.maxk % 8 == 0) && (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0 &&
                           p.bias_bstride == static_cast<long long>(p.hq) * p.maxq * p.maxk &&
                           make_bias_tile_map(&mb, p, dtype);
-  auto kq = hstu_bwd_tc_kernel<D, T, false>;
-  auto kkv = hstu_bwd_tc_kernel<D, T, true>;
-  auto kkv_staged = hstu_bwd_tc_kernel<D, T, true, true>;
-  auto kq_staged = hstu_bwd_tc_kernel<D, T, false, true>;
-  cudaError_t e = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(kkv_staged, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_kv);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(kq_staged, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_kv);
+  // one pass: the instantiation for (staged bias, tile look-ahead), its shared-memory size set, launched
+  auto launch = [&](auto kdkv, long long tiles_bound, long long tiles_least, const CUtensorMap& a1,
+                    const CUtensorMap& a2, const CUtensorMap& b1, const CUtensorMap& b2) -> cudaError_t {
+    constexpr bool kDKV = decltype(kdkv)::value;
+    const unsigned grid = static_cast<unsigned>(tiles_bound < num_sms ? tiles_bound : num_sms);
+    // (the next tile is drawn ahead when every CTA has at least eight: see the kernel)
+    const bool ahead = tiles_least >= 8ll * grid;
+    auto go = [&](auto kern, int bytes) -> cudaError_t {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      if (e != cudaSuccess) return e;
+      kern<<<grid, kBwdThreads, bytes, stream>>>(bp, a1, a2, b1, b2, mb);
+      return cudaGetLastError();
+    };
+    if (bias_staged) return ahead ? go(hstu_bwd_tc_kernel<D, T, kDKV, true, true>, smem_kv)
+                                  : go(hstu_bwd_tc_kernel<D, T, kDKV, true, false>, smem_kv);
+    return ahead ? go(hstu_bwd_tc_kernel<D, T, kDKV, false, true>, smem)
+                 : go(hstu_bwd_tc_kernel<D, T, kDKV, false, false>, smem);
+  };
+  cudaError_t e = cudaSuccess;
+  if (p.total_q > 0)
+    e = launch(std::false_type{}, static_cast<long long>(p.batch) * p.hq * ((p.maxq + kTileM - 1) / kTileM),
+               static_cast<long long>(p.hq) * (p.total_q / kTileM), mq, mg, mk, mv);
   if (e != cudaSuccess) return e;
-  if (p.total_q > 0) {
-    const long long tiles = static_cast<long long>(p.batch) * p.hq * ((p.maxq + kTileM - 1) / kTileM);
-    const unsigned grid = static_cast<unsigned>(tiles < num_sms ? tiles : num_sms);
-    if (bias_staged) kq_staged<<<grid, kBwdThreads, smem_kv, stream>>>(bp, mq, mg, mk, mv, mb);
-    else kq<<<grid, kBwdThreads, smem, stream>>>(bp, mq, mg, mk, mv, mb);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-  }
-  if (p.total_k > 0) {
-    const long long tiles = static_cast<long long>(p.batch) * p.hk * ((p.maxk + kTileN - 1) / kTileN);
-    const unsigned grid = static_cast<unsigned>(tiles < num_sms ? tiles : num_sms);
-    if (bias_staged) kkv_staged<<<grid, kBwdThreads, smem_kv, stream>>>(bp, mk, mv, mq, mg, mb);
-    else kkv<<<grid, kBwdThreads, smem, stream>>>(bp, mk, mv, mq, mg, mb);
-    e = cudaGetLastError();
-  }
+  if (p.total_k > 0)
+    e = launch(std::true_type{}, static_cast<long long>(p.batch) * p.hk * ((p.maxk + kTileN - 1) / kTileN),
+               static_cast<long long>(p.hk) * (p.total_k / kTileN), mk, mv, mq, mg);
   return e;
 }
 
