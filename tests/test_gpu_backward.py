@@ -252,6 +252,17 @@ def test_tile_lists_of_short_sequences_under_a_large_max_seq_len(B, lo_hi, maxL,
     assert_bwd_parity(got, grad, args, label=f"B{B} maxL{maxL} bias={bias}")
 
 
+@pytest.mark.parametrize("bias", [False, True])
+def test_many_tiles_per_cta_draw_the_next_tile_ahead(bias):
+    """With at least eight tiles per CTA the kernels run in the form that draws the next tile while the current one
+    runs (with and without a staged bias): 310 sequences of 121 - 128 rows x 4 heads on 148 CTAs."""
+    grad, args = make_bwd_case(310, 4, 4, 64, 64, 128, BF16, seed=5, bias=bias, tgt=120, g=1, alpha=1.0 / 64)
+    assert int(args["seq_offset"][-1]) * 4 // 128 >= 8 * 148
+    got, status = run_bwd(grad, args)
+    assert status == 0
+    assert_bwd_parity(got, grad, args, label=f"310 x 4 tiles, bias={bias}")
+
+
 def test_no_query_rows_still_writes_every_element_of_grad_bias():
     # all sequences empty: no kernel visits grad_bias, which must come back as zeros, not as uninitialised memory
     B, H, S, D = 3, 2, 40, 64
