@@ -206,7 +206,8 @@ typedef struct HstuJaggedBwdArgs {
 } HstuJaggedBwdArgs;
 
 /* Phase 1 / phase 2 of the backward, same contract as the forward pair (workspace: device memory, 256-byte
- * aligned, alive until the work completes; asynchronous on `stream`). */
+ * aligned, alive until the work completes; asynchronous on `stream`).  The workspace holds the status word, the work
+ * counters and the tile lists of the two passes (8 bytes per 128-row tile and head). */
 HSTU_API int hstu_jagged_bwd_get_workspace_size(const HstuJaggedBwdArgs* args, uint64_t* workspace_bytes);
 HSTU_API int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t workspace_bytes, void* stream);
 
