@@ -26,6 +26,8 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
   __shared__ unsigned s_seen[kBuckets];         // sequences of the bucket placed by earlier chunks
   __shared__ unsigned s_warp[32][kBuckets];     // per-warp counts of the current chunk, then exclusive prefix
   __shared__ unsigned s_status;
+  __shared__ unsigned s_first[kPreThreads];     // first item of each sequence of the chunk
+  __shared__ unsigned short s_key[kPreThreads]; // its number of q-pairs (0: nothing to write)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   // Let the attention kernel (launched with programmatic stream serialization) begin its set-up now; it waits
@@ -116,17 +118,21 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
       s_seen[tid] = acc;
     }
     __syncthreads();
-    if (live && key > 0) {
-      const unsigned rank = s_warp[warp][key] + rank_in_warp;
-      const long long first = static_cast<long long>(s_start[key]) +
-                              static_cast<long long>(rank) * key * p.hq;
-      for (int h = 0; h < p.hq; ++h) {
-        for (int pr = key - 1; pr >= 0; --pr) {
-          const long long at = first + static_cast<long long>(h) * key + (key - 1 - pr);
-          if (at < p.item_capacity) {
-            p.items[2 * at] = static_cast<uint32_t>(b);
-            p.items[2 * at + 1] = (static_cast<uint32_t>(h) << 16) | static_cast<uint32_t>(pr);
-          }
+    s_key[tid] = static_cast<unsigned short>(live ? key : 0);
+    if (live && key > 0) s_first[tid] = s_start[key] + (s_warp[warp][key] + rank_in_warp) * key * p.hq;
+    __syncthreads();
+    // A chunk of few sequences: the items of a sequence are written by a whole warp (a long sequence has hundreds of
+    // them, and this kernel's latency is part of every call); a full chunk: every thread writes its own sequence's.
+    const int in_chunk = p.batch - base < kPreThreads ? p.batch - base : kPreThreads;
+    const bool by_warp = in_chunk <= 256;
+    for (int i = by_warp ? warp : tid; i < in_chunk; i += by_warp ? kPreThreads / 32 : kPreThreads) {
+      const unsigned wkey = s_key[i];
+      const long long first = s_first[i];
+      for (unsigned e = by_warp ? lane : 0; e < wkey * p.hq; e += by_warp ? 32 : 1) {   // e = h * key + (key - 1 - pr)
+        const long long at = first + e;
+        if (at < p.item_capacity) {
+          const unsigned h = e / wkey, pr = wkey - 1u - (e - h * wkey);
+          *reinterpret_cast<uint2*>(p.items + 2 * at) = make_uint2(static_cast<uint32_t>(base + i), (h << 16) | pr);
         }
       }
     }
@@ -145,6 +151,8 @@ __global__ void __launch_bounds__(kPreThreads) hstu_bwd_prepass_kernel(const KPa
   __shared__ unsigned s_wq[32], s_wk[32];   // per-warp tile counts of the current chunk, then exclusive prefix
   __shared__ unsigned s_carry_q, s_carry_k; // tiles of all earlier chunks
   __shared__ unsigned s_status;
+  __shared__ unsigned s_nq[kPreThreads], s_nk[kPreThreads];     // tiles of each sequence of the chunk
+  __shared__ unsigned s_fq[kPreThreads], s_fk[kPreThreads];     // tiles of all sequences before it
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) {
     s_carry_q = 0;
@@ -195,24 +203,34 @@ __global__ void __launch_bounds__(kPreThreads) hstu_bwd_prepass_kernel(const KPa
       s_wk[lane] = ak - vk;
     }
     __syncthreads();
-    const long long first_q = static_cast<long long>(s_carry_q + s_wq[warp] + (iq - nq)) * p.hq;
-    const long long first_k = static_cast<long long>(s_carry_k + s_wk[warp] + (ik - nk)) * p.hk;
-    for (int h = 0; h < p.hq; ++h)
-      for (unsigned t = 0; t < nq; ++t) {
-        const long long at = first_q + static_cast<long long>(h) * nq + t;
+    s_nq[tid] = nq;
+    s_nk[tid] = nk;
+    s_fq[tid] = s_carry_q + s_wq[warp] + (iq - nq);
+    s_fk[tid] = s_carry_k + s_wk[warp] + (ik - nk);
+    __syncthreads();
+    // (few sequences: a warp per sequence - a long one has hundreds of entries; a full chunk: a thread per sequence)
+    const int in_chunk = p.batch - base < kPreThreads ? p.batch - base : kPreThreads;
+    const bool by_warp = in_chunk <= 256;
+    const unsigned e0 = by_warp ? lane : 0, estep = by_warp ? 32 : 1;
+    for (int i = by_warp ? warp : tid; i < in_chunk; i += by_warp ? kPreThreads / 32 : kPreThreads) {
+      const unsigned wnq = s_nq[i], wnk = s_nk[i];
+      const long long first_q = static_cast<long long>(s_fq[i]) * p.hq;
+      const long long first_k = static_cast<long long>(s_fk[i]) * p.hk;
+      for (unsigned e = e0; e < wnq * p.hq; e += estep) {   // e = h * nq + t
+        const long long at = first_q + e;
         if (at < p.bwd_cap_q) {
-          list_q[2 * at] = static_cast<uint32_t>(b);
-          list_q[2 * at + 1] = (static_cast<uint32_t>(h) << 16) | (nq - 1u - t);
+          const unsigned h = e / wnq, t = e - h * wnq;
+          *reinterpret_cast<uint2*>(list_q + 2 * at) = make_uint2(static_cast<uint32_t>(base + i), (h << 16) | (wnq - 1u - t));
         }
       }
-    for (int h = 0; h < p.hk; ++h)
-      for (unsigned t = 0; t < nk; ++t) {
-        const long long at = first_k + static_cast<long long>(h) * nk + t;
+      for (unsigned e = e0; e < wnk * p.hk; e += estep) {
+        const long long at = first_k + e;
         if (at < p.bwd_cap_k) {
-          list_k[2 * at] = static_cast<uint32_t>(b);
-          list_k[2 * at + 1] = (static_cast<uint32_t>(h) << 16) | t;
+          const unsigned h = e / wnk, t = e - h * wnk;
+          *reinterpret_cast<uint2*>(list_k + 2 * at) = make_uint2(static_cast<uint32_t>(base + i), (h << 16) | t);
         }
       }
+    }
     __syncthreads();
     if (tid == kPreThreads - 1) {   // (its inclusive sums are the chunk's totals)
       s_carry_q += s_wq[warp] + iq;
