@@ -143,115 +143,131 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
 // Pre-pass of the tensor-core backward: input check, and the two tile lists its persistent kernels draw from - the
 // (sequence, query head, 128-row q-tile) triples of the dQ pass and the (sequence, kv head, 128-key tile) triples of
 // the dK/dV pass, only tiles that exist (a batch of short sequences under a large max_seq_len has few of the
-// batch x heads x max_seq_len / 128 slots filled).  Order: sequences as they come, inside a sequence head-major, and
-// inside a head the tiles with the most steps first (dQ: the last q-tile; dK/dV: the first keys) - the CTAs that run
-// together then stream the same K/V (Q/dO) rows out of L2.  Entry: [sequence, head << 16 | tile].
+// batch x heads x max_seq_len / 128 slots filled).  Order of a list, as in the forward's: sequences by their number of
+// tiles, most first (a counting sort, stable in the sequence index) - the tiles drawn last, when the other CTAs run
+// dry, are then the short ones of the shortest sequences; inside a sequence head-major, and inside a head the tiles
+// with the most steps first (dQ: the last q-tile; dK/dV: the first keys) - the CTAs that run together then stream the
+// same K/V (Q/dO) rows out of L2.  Entry: [sequence, head << 16 | tile].
 // header[1] / header[4] = entries of the dQ / dK/dV list, header[2] / header[3] = the two work counters.
+constexpr int kMaxTiles = 20480 / kTileM;   // 160
+constexpr int kTBuckets = kMaxTiles + 1;
+
 __global__ void __launch_bounds__(kPreThreads) hstu_bwd_prepass_kernel(const KParams p) {
-  __shared__ unsigned s_wq[32], s_wk[32];   // per-warp tile counts of the current chunk, then exclusive prefix
-  __shared__ unsigned s_carry_q, s_carry_k; // tiles of all earlier chunks
+  __shared__ unsigned s_count[kTBuckets];       // sequences per bucket (bucket = number of tiles)
+  __shared__ unsigned s_start[kTBuckets];       // first entry of the bucket
+  __shared__ unsigned s_seen[kTBuckets];        // sequences of the bucket placed by earlier chunks
+  __shared__ unsigned s_warp[32][kTBuckets];    // per-warp counts of the current chunk, then exclusive prefix
+  __shared__ unsigned s_first[kPreThreads];     // first entry of each sequence of the chunk
+  __shared__ unsigned short s_key[kPreThreads]; // its number of tiles
   __shared__ unsigned s_status;
-  __shared__ unsigned s_nq[kPreThreads], s_nk[kPreThreads];     // tiles of each sequence of the chunk
-  __shared__ unsigned s_fq[kPreThreads], s_fk[kPreThreads];     // tiles of all sequences before it
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) {
-    s_carry_q = 0;
-    s_carry_k = 0;
-    s_status = 0;
-  }
-  __syncthreads();
   const int all_q = (p.maxq + kTileM - 1) / kTileM;
-  uint32_t* list_q = p.items;
-  uint32_t* list_k = p.items + 2 * p.bwd_cap_q;
+  if (tid == 0) s_status = 0;
   unsigned st = 0;
-  for (int base = 0; base < p.batch; base += kPreThreads) {
-    const int b = base + tid;
-    unsigned nq = 0, nk = 0;
-    if (b < p.batch) {
-      st |= check_seq(p, b) | check_pages(p, b);
+#pragma unroll 1
+  for (int which = 0; which < 2; ++which) {   // 0: dQ list, 1: dK/dV list
+    const int heads = which ? p.hk : p.hq;
+    uint32_t* list = which ? p.items + 2 * p.bwd_cap_q : p.items;
+    const long long cap = which ? p.bwd_cap_k : p.bwd_cap_q;
+    auto tiles_of = [&](int b) -> int {
       const SeqInfo s = load_seq(p, b);
-      nq = p.bwd_all_q_tiles ? all_q : (s.lq + kTileM - 1) / kTileM;
-      nk = (s.lk + kTileN - 1) / kTileN;
+      int n = which ? (s.lk + kTileN - 1) / kTileN : (p.bwd_all_q_tiles ? all_q : (s.lq + kTileM - 1) / kTileM);
+      return n > kMaxTiles ? kMaxTiles : n;
+    };
+    for (int i = tid; i < kTBuckets; i += kPreThreads) {
+      s_count[i] = 0;
+      s_seen[i] = 0;
     }
-    // exclusive scan of (nq, nk) over the chunk
-    unsigned iq = nq, ik = nk;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const unsigned oq = __shfl_up_sync(0xffffffffu, iq, d), ok = __shfl_up_sync(0xffffffffu, ik, d);
-      if (lane >= d) {
-        iq += oq;
-        ik += ok;
-      }
-    }
-    if (lane == 31) {
-      s_wq[warp] = iq;
-      s_wk[warp] = ik;
+    for (int i = tid; i < 32 * kTBuckets; i += kPreThreads) (&s_warp[0][0])[i] = 0;
+    __syncthreads();
+    int key_first = 0;   // bucket of sequence `tid` (the first chunk of the second pass)
+    for (int b = tid; b < p.batch; b += kPreThreads) {
+      if (which == 0) st |= check_seq(p, b) | check_pages(p, b);
+      const int key = tiles_of(b);
+      if (b == tid) key_first = key;
+      atomicAdd(&s_count[key], 1u);
     }
     __syncthreads();
     if (warp == 0) {
-      const unsigned vq = s_wq[lane], vk = s_wk[lane];
-      unsigned aq = vq, ak = vk;
+      // s_start[key] = entries of all larger keys: an exclusive scan from the largest key down, six keys per lane
+      unsigned v[6], sum = 0;
+#pragma unroll
+      for (int i = 0; i < 6; ++i) {
+        const int key = kMaxTiles - (6 * lane + i);
+        v[i] = key >= 1 ? s_count[key] * static_cast<unsigned>(key) * static_cast<unsigned>(heads) : 0u;
+        sum += v[i];
+      }
+      unsigned incl = sum;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
-        const unsigned oq = __shfl_up_sync(0xffffffffu, aq, d), ok = __shfl_up_sync(0xffffffffu, ak, d);
-        if (lane >= d) {
-          aq += oq;
-          ak += ok;
-        }
+        const unsigned o = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += o;
       }
-      s_wq[lane] = aq - vq;
-      s_wk[lane] = ak - vk;
-    }
-    __syncthreads();
-    s_nq[tid] = nq;
-    s_nk[tid] = nk;
-    s_fq[tid] = s_carry_q + s_wq[warp] + (iq - nq);
-    s_fk[tid] = s_carry_k + s_wk[warp] + (ik - nk);
-    __syncthreads();
-    // (few sequences: a warp per sequence - a long one has hundreds of entries; a full chunk: a thread per sequence)
-    const int in_chunk = p.batch - base < kPreThreads ? p.batch - base : kPreThreads;
-    const bool by_warp = in_chunk <= 256;
-    const unsigned e0 = by_warp ? lane : 0, estep = by_warp ? 32 : 1;
-    for (int i = by_warp ? warp : tid; i < in_chunk; i += by_warp ? kPreThreads / 32 : kPreThreads) {
-      const unsigned wnq = s_nq[i], wnk = s_nk[i];
-      const long long first_q = static_cast<long long>(s_fq[i]) * p.hq;
-      const long long first_k = static_cast<long long>(s_fk[i]) * p.hk;
-      for (unsigned e = e0; e < wnq * p.hq; e += estep) {   // e = h * nq + t
-        const long long at = first_q + e;
-        if (at < p.bwd_cap_q) {
-          const unsigned h = e / wnq, t = e - h * wnq;
-          *reinterpret_cast<uint2*>(list_q + 2 * at) = make_uint2(static_cast<uint32_t>(base + i), (h << 16) | (wnq - 1u - t));
-        }
+      unsigned run = incl - sum;
+#pragma unroll
+      for (int i = 0; i < 6; ++i) {
+        const int key = kMaxTiles - (6 * lane + i);
+        if (key >= 0) s_start[key] = run;
+        run += v[i];
       }
-      for (unsigned e = e0; e < wnk * p.hk; e += estep) {
-        const long long at = first_k + e;
-        if (at < p.bwd_cap_k) {
-          const unsigned h = e / wnk, t = e - h * wnk;
-          *reinterpret_cast<uint2*>(list_k + 2 * at) = make_uint2(static_cast<uint32_t>(base + i), (h << 16) | t);
-        }
+      if (lane == 31) {
+        // never more than the list holds: offsets that are not monotone can describe more tiles than the tensors have
+        // rows for (the host sizes the lists from total_q / total_k); the surplus is dropped, the status word says why
+        unsigned total = incl;
+        if (static_cast<long long>(total) > cap) total = static_cast<unsigned>(cap);
+        p.ws_header[which ? 4 : 1] = total;
+        p.ws_header[2 + which] = 0;   // the pass's work counter
       }
     }
     __syncthreads();
-    if (tid == kPreThreads - 1) {   // (its inclusive sums are the chunk's totals)
-      s_carry_q += s_wq[warp] + iq;
-      s_carry_k += s_wk[warp] + ik;
+    for (int base = 0; base < p.batch; base += kPreThreads) {
+      if (base > 0) {
+        for (int i = tid; i < 32 * kTBuckets; i += kPreThreads) (&s_warp[0][0])[i] = 0;
+        __syncthreads();
+      }
+      const int b = base + tid;
+      const bool live = b < p.batch;
+      int key = 0;
+      if (live) key = base == 0 ? key_first : tiles_of(b);
+      // rank among the lanes of this warp that hold the same key (idle lanes use key -1 and are ignored)
+      const unsigned same = __match_any_sync(0xffffffffu, live ? key : -1);
+      const unsigned rank_in_warp = __popc(same & ((1u << lane) - 1u));
+      if (live && rank_in_warp == 0) s_warp[warp][key] = __popc(same);
+      __syncthreads();
+      if (tid < kTBuckets) {
+        unsigned acc = s_seen[tid];
+        for (int w = 0; w < 32; ++w) {
+          const unsigned c = s_warp[w][tid];
+          s_warp[w][tid] = acc;
+          acc += c;
+        }
+        s_seen[tid] = acc;
+      }
+      __syncthreads();
+      s_key[tid] = static_cast<unsigned short>(live ? key : 0);
+      if (live && key > 0) s_first[tid] = s_start[key] + (s_warp[warp][key] + rank_in_warp) * key * heads;
+      __syncthreads();
+      // (few sequences: a warp per sequence - a long one has hundreds of entries; a full chunk: a thread per sequence)
+      const int in_chunk = p.batch - base < kPreThreads ? p.batch - base : kPreThreads;
+      const bool by_warp = in_chunk <= 256;
+      for (int i = by_warp ? warp : tid; i < in_chunk; i += by_warp ? kPreThreads / 32 : kPreThreads) {
+        const unsigned wkey = s_key[i];
+        const long long first = s_first[i];
+        for (unsigned e = by_warp ? lane : 0; e < wkey * heads; e += by_warp ? 32 : 1) {   // e = h * key + t
+          const long long at = first + e;
+          if (at < cap) {
+            const unsigned h = e / wkey, t = e - h * wkey;
+            *reinterpret_cast<uint2*>(list + 2 * at) =
+                make_uint2(static_cast<uint32_t>(base + i), (h << 16) | (which ? t : wkey - 1u - t));
+          }
+        }
+      }
+      __syncthreads();
     }
-    __syncthreads();
   }
   if (st) atomicOr(&s_status, st);
   __syncthreads();
-  if (tid == 0) {
-    // never more than the lists hold: offsets that are not monotone can describe more tiles than the tensors have
-    // rows for (the host sizes the lists from total_q / total_k); the surplus is dropped, the status word says why
-    long long tq = static_cast<long long>(s_carry_q) * p.hq, tk = static_cast<long long>(s_carry_k) * p.hk;
-    if (tq > p.bwd_cap_q) tq = p.bwd_cap_q;
-    if (tk > p.bwd_cap_k) tk = p.bwd_cap_k;
-    p.ws_header[0] = s_status;
-    p.ws_header[1] = static_cast<uint32_t>(tq);
-    p.ws_header[2] = 0;
-    p.ws_header[3] = 0;
-    p.ws_header[4] = static_cast<uint32_t>(tk);
-  }
+  if (tid == 0) p.ws_header[0] = s_status;
 }
 
 cudaError_t launch_bwd_prepass(const KParams& p, cudaStream_t stream) {
