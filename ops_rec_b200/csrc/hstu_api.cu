@@ -417,6 +417,8 @@ int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t wor
   if (tc) {
     bwd_list_bounds(f, &bp.f.bwd_cap_q, &bp.f.bwd_cap_k);
     bp.f.bwd_all_q_tiles = bp.dbias ? 1 : 0;
+    // few tiles per CTA: the lists are ordered by step count (longest first); many: sequence by sequence (L2 reuse)
+    bp.f.bwd_by_steps = static_cast<long long>(f->heads_q) * (f->total_q / hstu::kTileM) < 8ll * dev.sms ? 1 : 0;
   }
   cudaError_t e = tc ? hstu::launch_bwd_prepass(bp.f, stream) : hstu::launch_prepass(bp.f, false, stream);
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "pre-pass launch: %s", cudaGetErrorString(e));

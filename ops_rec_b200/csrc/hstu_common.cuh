@@ -71,6 +71,7 @@ struct KParams {
   // sequence's end (they hold rows of grad_bias that must be zeroed)
   long long bwd_cap_q, bwd_cap_k;
   int bwd_all_q_tiles;
+  int bwd_by_steps;   // order the lists by the tiles' step counts (few tiles per CTA) instead of sequence by sequence
 };
 
 // Backward call: the forward's parameters plus the gradient tensors.

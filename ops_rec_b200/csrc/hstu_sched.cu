@@ -155,6 +155,8 @@ constexpr int kTBuckets = kMaxTiles + 1;
 __global__ void __launch_bounds__(kPreThreads) hstu_bwd_prepass_kernel(const KParams p) {
   __shared__ unsigned s_count[kTBuckets];       // sequences per bucket (bucket = number of tiles)
   __shared__ unsigned s_start[kTBuckets];       // first entry of the bucket
+  __shared__ unsigned s_before[kTBuckets];      // by steps: sequences with more tiles than the bucket's
+  __shared__ unsigned s_class[kTBuckets];       // by steps: first entry of the tiles with `index` steps
   __shared__ unsigned s_seen[kTBuckets];        // sequences of the bucket placed by earlier chunks
   __shared__ unsigned s_warp[32][kTBuckets];    // per-warp counts of the current chunk, then exclusive prefix
   __shared__ unsigned s_first[kPreThreads];     // first entry of each sequence of the chunk
@@ -210,6 +212,49 @@ __global__ void __launch_bounds__(kPreThreads) hstu_bwd_prepass_kernel(const KPa
         if (key >= 0) s_start[key] = run;
         run += v[i];
       }
+      // Ordered by steps (p.bwd_by_steps): the tiles of all sequences with the most steps first - with a few tiles per
+      // CTA that is longest-first list scheduling.  A tile with s steps exists once per head in every sequence of at
+      // least s tiles, and these sequences are a prefix of the sorted order: entry = s_class[s] + (rank of the
+      // sequence in the sorted order) * heads + head.
+      {
+        unsigned c[6], csum = 0;
+#pragma unroll
+        for (int i = 0; i < 6; ++i) {
+          const int key = kMaxTiles - (6 * lane + i);
+          c[i] = key >= 1 ? s_count[key] : 0u;
+          csum += c[i];
+        }
+        unsigned cincl = csum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const unsigned o = __shfl_up_sync(0xffffffffu, cincl, d);
+          if (lane >= d) cincl += o;
+        }
+        // before[key] = sequences with more tiles; ge = sequences with at least `key` tiles = tiles per head in class
+        // `key`; class start = entries of all classes with more steps
+        unsigned before = cincl - csum, g[6], gsum = 0;
+#pragma unroll
+        for (int i = 0; i < 6; ++i) {
+          const int key = kMaxTiles - (6 * lane + i);
+          if (key >= 0) s_before[key] = before;
+          before += c[i];
+          g[i] = key >= 1 ? before * static_cast<unsigned>(heads) : 0u;
+          gsum += g[i];
+        }
+        unsigned gincl = gsum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const unsigned o = __shfl_up_sync(0xffffffffu, gincl, d);
+          if (lane >= d) gincl += o;
+        }
+        unsigned gstart = gincl - gsum;
+#pragma unroll
+        for (int i = 0; i < 6; ++i) {
+          const int key = kMaxTiles - (6 * lane + i);
+          if (key >= 0) s_class[key] = gstart;
+          gstart += g[i];
+        }
+      }
       if (lane == 31) {
         // never more than the list holds: offsets that are not monotone can describe more tiles than the tensors have
         // rows for (the host sizes the lists from total_q / total_k); the surplus is dropped, the status word says why
@@ -245,7 +290,9 @@ __global__ void __launch_bounds__(kPreThreads) hstu_bwd_prepass_kernel(const KPa
       }
       __syncthreads();
       s_key[tid] = static_cast<unsigned short>(live ? key : 0);
-      if (live && key > 0) s_first[tid] = s_start[key] + (s_warp[warp][key] + rank_in_warp) * key * heads;
+      if (live && key > 0)
+        s_first[tid] = p.bwd_by_steps ? (s_before[key] + s_warp[warp][key] + rank_in_warp) * heads   // rank * heads
+                                      : s_start[key] + (s_warp[warp][key] + rank_in_warp) * key * heads;
       __syncthreads();
       // (few sequences: a warp per sequence - a long one has hundreds of entries; a full chunk: a thread per sequence)
       const int in_chunk = p.batch - base < kPreThreads ? p.batch - base : kPreThreads;
@@ -254,9 +301,9 @@ __global__ void __launch_bounds__(kPreThreads) hstu_bwd_prepass_kernel(const KPa
         const unsigned wkey = s_key[i];
         const long long first = s_first[i];
         for (unsigned e = by_warp ? lane : 0; e < wkey * heads; e += by_warp ? 32 : 1) {   // e = h * key + t
-          const long long at = first + e;
+          const unsigned h = e / wkey, t = e - h * wkey;   // t-th heaviest tile of the head: key - t steps
+          const long long at = p.bwd_by_steps ? static_cast<long long>(s_class[wkey - t]) + first + h : first + e;
           if (at < cap) {
-            const unsigned h = e / wkey, t = e - h * wkey;
             *reinterpret_cast<uint2*>(list + 2 * at) =
                 make_uint2(static_cast<uint32_t>(base + i), (h << 16) | (which ? t : wkey - 1u - t));
           }
