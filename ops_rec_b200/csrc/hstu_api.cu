@@ -121,6 +121,7 @@ hstu::KParams to_params(const HstuJaggedArgs* a, void* workspace, uint64_t works
   p.scale = a->silu_scale == 0.0f ? 1.0f / static_cast<float>(a->max_seq_len_q) : a->silu_scale;
   p.alpha = a->alpha;
   p.flags = a->flags;
+  p.fwd_by_steps = static_cast<long long>(a->heads_q) * (a->total_q / hstu::kPairM) < hstu::kFewItems ? 1 : 0;
   if (workspace) {
     p.ws_header = static_cast<uint32_t*>(workspace);
     p.items = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + hstu::kWsHeaderBytes);
@@ -418,7 +419,7 @@ int hstu_jagged_bwd(const HstuJaggedBwdArgs* args, void* workspace, uint64_t wor
     bwd_list_bounds(f, &bp.f.bwd_cap_q, &bp.f.bwd_cap_k);
     bp.f.bwd_all_q_tiles = bp.dbias ? 1 : 0;
     // few tiles per CTA: the lists are ordered by step count (longest first); many: sequence by sequence (L2 reuse)
-    bp.f.bwd_by_steps = static_cast<long long>(f->heads_q) * (f->total_q / hstu::kTileM) < 8ll * dev.sms ? 1 : 0;
+    bp.f.bwd_by_steps = static_cast<long long>(f->heads_q) * (f->total_q / hstu::kTileM) < hstu::kFewItems ? 1 : 0;
   }
   cudaError_t e = tc ? hstu::launch_bwd_prepass(bp.f, stream) : hstu::launch_prepass(bp.f, false, stream);
   if (e != cudaSuccess) return fail(HSTU_E_CUDA, "pre-pass launch: %s", cudaGetErrorString(e));

@@ -27,6 +27,10 @@ constexpr int kTileN = 128;
 //   [12]  uint32 work counter (backward dK/dV pass)
 //   [256] uint32 items[2 * capacity]   {sequence, head << 16 | q_pair}
 constexpr uint64_t kWsHeaderBytes = 256;
+// Below this many work items (tiles) in a call - eight per SM of a B200 - a list is ordered by the items' step counts,
+// longest first: with a few items per CTA the balance at the end of the kernel is what counts.  Above it the items of
+// one (sequence, head) stay neighbours, so the CTAs that run together share K/V in L2.
+constexpr long long kFewItems = 8 * 148;
 
 struct KParams {
   const void* q;
@@ -72,6 +76,7 @@ struct KParams {
   long long bwd_cap_q, bwd_cap_k;
   int bwd_all_q_tiles;
   int bwd_by_steps;   // order the lists by the tiles' step counts (few tiles per CTA) instead of sequence by sequence
+  int fwd_by_steps;   // the same for the forward's work list: all sequences' last q-pairs first, then the ones before
 };
 
 // Backward call: the forward's parameters plus the gradient tensors.

@@ -28,6 +28,8 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
   __shared__ unsigned s_status;
   __shared__ unsigned s_first[kPreThreads];     // first item of each sequence of the chunk
   __shared__ unsigned short s_key[kPreThreads]; // its number of q-pairs (0: nothing to write)
+  __shared__ unsigned s_before[kBuckets];       // by steps: sequences with more q-pairs than the bucket's
+  __shared__ unsigned s_class[kBuckets];        // by steps: first item of the class "q-pair number `index` - 1"
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   // Let the attention kernel (launched with programmatic stream serialization) begin its set-up now; it waits
@@ -80,6 +82,47 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
       if (key >= 0) s_start[key] = run;
       run += v[i];
     }
+    // Ordered by steps (p.fwd_by_steps, calls with few items): the last q-pairs of all sequences first, then the ones
+    // before them - a q-pair's cost grows with its number, so this is longest-first list scheduling.  Q-pair number
+    // s - 1 exists once per head in every sequence of at least s pairs, and these sequences are a prefix of the sorted
+    // order: item = s_class[s] + (rank of the sequence in the sorted order) * heads + head.
+    {
+      unsigned c[3], csum = 0;
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int key = kMaxPairs - (3 * lane + i);
+        c[i] = key >= 1 ? s_count[key] : 0u;
+        csum += c[i];
+      }
+      unsigned cincl = csum;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const unsigned o = __shfl_up_sync(0xffffffffu, cincl, d);
+        if (lane >= d) cincl += o;
+      }
+      unsigned before = cincl - csum, g[3], gsum = 0;
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int key = kMaxPairs - (3 * lane + i);
+        if (key >= 0) s_before[key] = before;
+        before += c[i];
+        g[i] = key >= 1 ? before * static_cast<unsigned>(p.hq) : 0u;
+        gsum += g[i];
+      }
+      unsigned gincl = gsum;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const unsigned o = __shfl_up_sync(0xffffffffu, gincl, d);
+        if (lane >= d) gincl += o;
+      }
+      unsigned gstart = gincl - gsum;
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int key = kMaxPairs - (3 * lane + i);
+        if (key >= 0) s_class[key] = gstart;
+        gstart += g[i];
+      }
+    }
     if (lane == 31) {
       // never more than the list holds: offsets that are not monotone can describe more q-pairs than total_q has
       // rows for (the host sizes the list from total_q); the surplus items are dropped, the status word says why
@@ -119,7 +162,9 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
     }
     __syncthreads();
     s_key[tid] = static_cast<unsigned short>(live ? key : 0);
-    if (live && key > 0) s_first[tid] = s_start[key] + (s_warp[warp][key] + rank_in_warp) * key * p.hq;
+    if (live && key > 0)
+      s_first[tid] = p.fwd_by_steps ? (s_before[key] + s_warp[warp][key] + rank_in_warp) * p.hq   // rank * heads
+                                    : s_start[key] + (s_warp[warp][key] + rank_in_warp) * key * p.hq;
     __syncthreads();
     // A chunk of few sequences: the items of a sequence are written by a whole warp (a long sequence has hundreds of
     // them, and this kernel's latency is part of every call); a full chunk: every thread writes its own sequence's.
@@ -129,9 +174,9 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
       const unsigned wkey = s_key[i];
       const long long first = s_first[i];
       for (unsigned e = by_warp ? lane : 0; e < wkey * p.hq; e += by_warp ? 32 : 1) {   // e = h * key + (key - 1 - pr)
-        const long long at = first + e;
+        const unsigned h = e / wkey, pr = wkey - 1u - (e - h * wkey);
+        const long long at = p.fwd_by_steps ? static_cast<long long>(s_class[pr + 1u]) + first + h : first + e;
         if (at < p.item_capacity) {
-          const unsigned h = e / wkey, pr = wkey - 1u - (e - h * wkey);
           *reinterpret_cast<uint2*>(p.items + 2 * at) = make_uint2(static_cast<uint32_t>(base + i), (h << 16) | pr);
         }
       }
@@ -332,6 +377,24 @@ long long plan_host(const KParams& p, uint32_t* items, long long capacity, uint3
   unsigned st = 0;
   long long n = 0;
   for (int b = 0; b < p.batch; ++b) st |= check_seq(p, b) | check_pages(p, b);
+  if (p.fwd_by_steps) {
+    // q-pair number descending over all sequences; inside a number the sequences in the sorted order (most pairs
+    // first, stable in the index), heads inside a sequence
+    for (int pr = kMaxPairs - 1; pr >= 0; --pr)
+      for (int key = kMaxPairs; key > pr; --key)
+        for (int b = 0; b < p.batch; ++b) {
+          if (pairs_of(load_seq(p, b).lq) != key) continue;
+          for (int h = 0; h < p.hq; ++h) {
+            if (n < capacity && items) {
+              items[2 * n] = static_cast<uint32_t>(b);
+              items[2 * n + 1] = (static_cast<uint32_t>(h) << 16) | static_cast<uint32_t>(pr);
+            }
+            ++n;
+          }
+        }
+    if (status) *status = st;
+    return n;
+  }
   for (int key = kMaxPairs; key >= 1; --key) {
     for (int b = 0; b < p.batch; ++b) {
       const SeqInfo s = load_seq(p, b);
