@@ -12,6 +12,9 @@
 // first.  Persistent CTAs draw items from a global atomic counter, so the order of the list is greedy
 // longest-first scheduling, and the CTAs that run at the same time work on neighbouring q-pairs of the same few
 // (sequence, head) - their K/V stays in L2.
+// A call with few items (fewer than eight per SM) orders them by steps instead: q-pair number descending over all
+// sequences - a q-pair's cost grows with its number, and with two or three items per CTA the balance at the end of
+// the kernel counts for more than L2 reuse (such a call's K/V fits the L2 anyway).
 #include "hstu_common.cuh"
 
 namespace hstu {
