@@ -81,7 +81,8 @@ struct BwdBars {
   int item[2];                 // -1: no tile left; else the tile every thread of the CTA works on:
   int item_seq[2];             //   its sequence,
   uint32_t item_head_tile[2];  //   head << 16 | tile index (the pre-pass's list entry)
-  uint32_t n_list;             // entries of this pass's tile list (read once, by thread 0)
+  uint64_t item_full[2];       // slot written by the producer thread / read by every other warp (11 arrivals)
+  uint64_t item_free[2];
 };
 
 struct BwdWaiter {
@@ -211,6 +212,10 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
     ptx::mbar_init(ptx::smem_u32(&bars->acc_full), 1);
     ptx::mbar_init(ptx::smem_u32(&bars->bias_full), 1);
     ptx::mbar_init(ptx::smem_u32(&bars->bias_free), 2 * kTileM);
+    for (int sl = 0; sl < 2; ++sl) {
+      ptx::mbar_init(ptx::smem_u32(&bars->item_full[sl]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->item_free[sl]), 11);
+    }
     if (staged) ptx::prefetch_tensormap(&tm_bias);
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
@@ -233,42 +238,110 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   uint32_t* counter = p.ws_header + (kDKV ? 3 : 2);
   uint32_t cnt = 0;          // steps so far (every role counts them alike): barrier phases run on across tiles
   uint32_t tiles_done = 0;   // tiles so far: phase of a_full / acc_full
-  // With many tiles per CTA the next tile is drawn while the current one runs (by a thread of the warp that has no
-  // role in a tile), so its atomic and the dependent load of the list entry cost nothing at the tile boundary.  With
-  // few, a tile drawn early is a tile that cannot go to a CTA that has run dry - measured: - 7 % on a batch with four
-  // tiles per CTA - and the tile is drawn when the last one is complete.  (kAhead, chosen by the launcher from the
-  // number of token rows: an instantiation of its own, because the code of the one form cost the other 3 %.)
-  auto draw = [&](const uint32_t slot) {   // (one thread)
-    int found = -1;
-    if (!*reinterpret_cast<volatile int*>(&bars->abort_flag)) {
-      const unsigned idx = atomicAdd(counter, 1u);
-      if (idx < *reinterpret_cast<volatile uint32_t*>(&bars->n_list)) {
-        const uint2 e = *reinterpret_cast<const uint2*>(list + 2ull * idx);
-        bars->item_seq[slot] = static_cast<int>(e.x);
-        bars->item_head_tile[slot] = e.y;
-        found = 0;
+  // Tiles are drawn by the producer thread, which runs ahead of the other warps across tile boundaries: when it has
+  // requested the last loads of a tile it draws the next one, publishes it in one of two slots (item_full / item_free)
+  // and - once the MMAs of the current tile are complete (acc_full: the resident pair's buffer is free) - requests
+  // the next tile's loads, so that the draw (an atomic and a dependent load of the list entry) and the first loads
+  // overlap the current tile's epilogue.  With many tiles per CTA (kAhead, chosen by the launcher from the number
+  // of token rows) the draw does not wait for anything; with few, a tile drawn early is a tile that cannot go to a
+  // CTA that has run dry (measured: - 7 % on a batch with four tiles per CTA), and it waits for acc_full too.
+  // The other warps meet at a named barrier at the end of a tile (the producer warp takes no part in it).
+  constexpr int kConsumers = kBwdThreads - 32;
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- TMA producer (and tile drawer)
+      const unsigned n_list = p.ws_header[kDKV ? 4 : 1];
+      uint32_t draws = 0;
+      for (;;) {
+        const uint32_t slot = draws & 1u;
+        // the slot's last tile (two draws ago) has been read by every warp
+        if (draws >= 2) w.wait(ptx::smem_u32(&bars->item_free[slot]), ((draws >> 1) - 1u) & 1u);
+        if (!kAhead && tiles_done > 0) w.wait(ptx::smem_u32(&bars->acc_full), (tiles_done - 1u) & 1u);
+        int found = -1, b = 0;
+        uint32_t head_tile = 0;
+        if (!*reinterpret_cast<volatile int*>(&bars->abort_flag)) {
+          const unsigned idx = atomicAdd(counter, 1u);
+          if (idx < n_list) {
+            const uint2 e = *reinterpret_cast<const uint2*>(list + 2ull * idx);
+            b = static_cast<int>(e.x);
+            head_tile = e.y;
+            found = 0;
+          }
+        }
+        bars->item_seq[slot] = b;
+        bars->item_head_tile[slot] = head_tile;
+        bars->item[slot] = found;
+        ptx::mbar_arrive(ptx::smem_u32(&bars->item_full[slot]));
+        ++draws;
+        if (found < 0) break;
+        const int head = static_cast<int>(head_tile >> 16);
+        const int tile0 = static_cast<int>(head_tile & 0xffffu) * kTileM;
+        const SeqInfo s = load_seq(p, b);
+        if (tile0 >= (kDKV ? s.lk : s.lq)) continue;   // (a q-tile past the sequence end: nothing to load)
+        const long long a_row = (kDKV ? s.k0 : s.q0) + tile0;
+        const long long b_row0 = kDKV ? s.q0 : s.k0;
+        const int a_head = head;
+        // the resident pair's buffer is free once the MMAs of the tile before are complete
+        if (tiles_done > 0) w.wait(ptx::smem_u32(&bars->acc_full), (tiles_done - 1u) & 1u);
+        if (*reinterpret_cast<volatile int*>(&bars->abort_flag)) break;
+        const uint32_t afull = ptx::smem_u32(&bars->a_full);
+        ptx::mbar_expect_tx(afull, 2 * kTileBytes);
+#pragma unroll
+        for (int hf = 0; hf < kHalves; ++hf) {
+          ptx::tma_load_3d(sm_a + hf * kHalfBytes, &tm_a1, afull, hf * 64, a_head, static_cast<int>(a_row));
+          ptx::tma_load_3d(sm_a + kTileBytes + hf * kHalfBytes, &tm_a2, afull, hf * 64, a_head, static_cast<int>(a_row));
+        }
+        for_each_step<kDKV>(p, s, tile0, head, [&](int sh, int srow0, int qh) {
+          const uint32_t stage = cnt & 1u;
+          const uint32_t full = ptx::smem_u32(&bars->b_full[stage]);
+          if (staged) {
+            // the bias tile of this step, once every element-wise thread has read the last one
+            w.wait(ptx::smem_u32(&bars->bias_free), (cnt & 1u) ^ 1u);
+            const uint32_t bfull = ptx::smem_u32(&bars->bias_full);
+            ptx::mbar_expect_tx(bfull, 2 * kTileM * 128);
+            // rows = queries, columns = keys: the streamed rows are queries in the dK/dV pass and keys in the dQ pass
+            const int brow = (b * p.hq + qh) * p.maxq + (kDKV ? srow0 : tile0);
+            const int bcol0 = kDKV ? tile0 : srow0;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf)
+              ptx::tma_load_2d(sm_bias + hf * (kTileM * 128), &tm_bias, bfull, bcol0 + hf * 64, brow);
+          }
+          w.wait(ptx::smem_u32(&bars->b_free[stage]), ((cnt >> 1) & 1u) ^ 1u);
+          ptx::mbar_expect_tx(full, 2 * kTileBytes);
+          const int row = static_cast<int>(b_row0) + srow0;
+#pragma unroll
+          for (int hf = 0; hf < kHalves; ++hf) {
+            ptx::tma_load_3d(sm_b + stage * 2 * kTileBytes + hf * kHalfBytes, &tm_b1, full, hf * 64, sh, row);
+            ptx::tma_load_3d(sm_b + stage * 2 * kTileBytes + kTileBytes + hf * kHalfBytes, &tm_b2, full, hf * 64, sh, row);
+          }
+          ++cnt;
+        });
+        ++tiles_done;
+      }
+      if (tiles_done > 0) {
+        // drain (matters only after an abort: otherwise the consumers have waited for every load)
+        for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(ptx::smem_u32(&bars->a_full), (tiles_done - 1) & 1u); ++spin) {}
+        for (uint32_t back = 0; back < 2 && back < cnt; ++back) {
+          const uint32_t c = cnt - 1 - back;
+          const uint32_t bar = ptx::smem_u32(&bars->b_full[c & 1u]);
+          for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (c >> 1) & 1u); ++spin) {}
+        }
+        if (staged && cnt > 0)
+          for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(ptx::smem_u32(&bars->bias_full), (cnt - 1) & 1u); ++spin) {}
       }
     }
-    bars->item[slot] = found;
-  };
-  if (tid == 0) {
-    bars->n_list = p.ws_header[kDKV ? 4 : 1];
-    draw(0);
-  }
-  __syncthreads();
-  constexpr bool ahead = kAhead;
-  uint32_t draws = 0;        // tiles drawn and read so far by this CTA (every thread counts alike)
+  } else {
+  uint32_t draws = 0;        // tiles read so far (every thread of these warps counts alike)
   for (;;) {
-  if (!ahead && draws > 0) {
-    if (tid == 0) draw(draws & 1u);
-    __syncthreads();
-  }                          // (ahead: the end-of-tile barrier has published the next slot)
   const uint32_t slot = draws & 1u;
-  if (*reinterpret_cast<volatile int*>(&bars->item[slot]) < 0) break;
+  w.wait(ptx::smem_u32(&bars->item_full[slot]), (draws >> 1) & 1u);
+  const int found = *reinterpret_cast<volatile int*>(&bars->item[slot]);
   const int b = *reinterpret_cast<volatile int*>(&bars->item_seq[slot]);
   const uint32_t head_tile = *reinterpret_cast<volatile uint32_t*>(&bars->item_head_tile[slot]);
+  __syncwarp();
+  if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->item_free[slot]));
   ++draws;
-  if (ahead && tid == 64) draw(draws & 1u);
+  if (found < 0 || *reinterpret_cast<volatile int*>(&bars->abort_flag)) break;
   const int head = static_cast<int>(head_tile >> 16);    // dQ pass: query head; dK/dV pass: kv head
   const int tile0 = static_cast<int>(head_tile & 0xffffu) * kTileM;   // first query row (dQ) / first key (dK/dV)
   const SeqInfo s = load_seq(p, b);
@@ -285,21 +358,21 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
       if (p.maxk % 8 == 0 && (reinterpret_cast<uintptr_t>(bp.dbias) & 15u) == 0) {
         // 16-byte stores: first_col is a multiple of 128, so every row piece starts on a 16-byte boundary
         const int pieces = width / 8;
-        for (int idx = tid; idx < kTileM * pieces; idx += kBwdThreads) {
+        for (int idx = tid - 32; idx < kTileM * pieces; idx += kConsumers) {
           const int r = idx / pieces, c = idx - r * pieces;
           if (tile0 + r < p.maxq)
             *reinterpret_cast<uint4*>(dbias + (brow0 + tile0 + r) * p.maxk + first_col + 8 * c) = make_uint4(0, 0, 0, 0);
         }
       } else {
-        for (int idx = tid; idx < kTileM * width; idx += kBwdThreads) {
+        for (int idx = tid - 32; idx < kTileM * width; idx += kConsumers) {
           const int r = idx / width, c = idx - r * width;
           if (tile0 + r < p.maxq) dbias[(brow0 + tile0 + r) * p.maxk + first_col + c] = T(0.f);
         }
       }
     }
   }
-  if (tile0 >= len) {   // uniform over the CTA
-    __syncthreads();
+  if (tile0 >= len) {   // uniform over these warps
+    ptx::named_bar_sync(1, kConsumers);
     continue;
   }
 
@@ -308,43 +381,7 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   const long long b_row0 = kDKV ? s.q0 : s.k0;
   const int a_head = head;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      const uint32_t afull = ptx::smem_u32(&bars->a_full);
-      ptx::mbar_expect_tx(afull, 2 * kTileBytes);
-#pragma unroll
-      for (int hf = 0; hf < kHalves; ++hf) {
-        ptx::tma_load_3d(sm_a + hf * kHalfBytes, &tm_a1, afull, hf * 64, a_head, static_cast<int>(a_row));
-        ptx::tma_load_3d(sm_a + kTileBytes + hf * kHalfBytes, &tm_a2, afull, hf * 64, a_head, static_cast<int>(a_row));
-      }
-      for_each_step<kDKV>(p, s, tile0, head, [&](int sh, int srow0, int qh) {
-        const uint32_t stage = cnt & 1u;
-        const uint32_t full = ptx::smem_u32(&bars->b_full[stage]);
-        if (staged) {
-          // the bias tile of this step, once every element-wise thread has read the last one
-          w.wait(ptx::smem_u32(&bars->bias_free), (cnt & 1u) ^ 1u);
-          const uint32_t bfull = ptx::smem_u32(&bars->bias_full);
-          ptx::mbar_expect_tx(bfull, 2 * kTileM * 128);
-          // rows = queries, columns = keys: the streamed rows are queries in the dK/dV pass and keys in the dQ pass
-          const int brow = (b * p.hq + qh) * p.maxq + (kDKV ? srow0 : tile0);
-          const int bcol0 = kDKV ? tile0 : srow0;
-#pragma unroll
-          for (int hf = 0; hf < 2; ++hf)
-            ptx::tma_load_2d(sm_bias + hf * (kTileM * 128), &tm_bias, bfull, bcol0 + hf * 64, brow);
-        }
-        w.wait(ptx::smem_u32(&bars->b_free[stage]), ((cnt >> 1) & 1u) ^ 1u);
-        ptx::mbar_expect_tx(full, 2 * kTileBytes);
-        const int row = static_cast<int>(b_row0) + srow0;
-#pragma unroll
-        for (int hf = 0; hf < kHalves; ++hf) {
-          ptx::tma_load_3d(sm_b + stage * 2 * kTileBytes + hf * kHalfBytes, &tm_b1, full, hf * 64, sh, row);
-          ptx::tma_load_3d(sm_b + stage * 2 * kTileBytes + kTileBytes + hf * kHalfBytes, &tm_b2, full, hf * 64, sh, row);
-        }
-        ++cnt;
-      });
-    }
-  } else if (warp == 1) {
+  if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     // (an elected thread, not `lane == 0`: the compiler then keeps descriptors and barrier addresses in uniform registers)
     if (ptx::elect_one()) {
@@ -651,24 +688,14 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
     }
   }
 
-  // everything of this tile is complete (MMAs, TMEM reads, loads) before the next one reuses the buffers
+  // everything of this tile is complete (MMAs, TMEM reads) before the next one reuses the tensor memory
   ++tiles_done;
   ptx::tc_fence_before();
-  __syncthreads();
+  ptx::named_bar_sync(1, kConsumers);
   ptx::tc_fence_after();
   }  // tiles
+  }  // warps 1 .. 11
 
-  if (warp == 0 && lane == 0 && tiles_done > 0) {
-    // drain (matters only after an abort: otherwise the consumers have waited for every load)
-    for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(ptx::smem_u32(&bars->a_full), (tiles_done - 1) & 1u); ++spin) {}
-    for (uint32_t back = 0; back < 2 && back < cnt; ++back) {
-      const uint32_t c = cnt - 1 - back;
-      const uint32_t bar = ptx::smem_u32(&bars->b_full[c & 1u]);
-      for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(bar, (c >> 1) & 1u); ++spin) {}
-    }
-    if (staged && cnt > 0)
-      for (int spin = 0; spin < (1 << 22) && !ptx::mbar_try_wait(ptx::smem_u32(&bars->bias_full), (cnt - 1) & 1u); ++spin) {}
-  }
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 2) {
