@@ -166,7 +166,7 @@ __device__ __forceinline__ void score_grad2(float2 s, float2 dp, float2 bias, fl
 
 // kStaged (dK/dV pass with a bias that TMA can tile): a kernel of its own - the same code merely present in the
 // bias-free kernel cost that one 4 %.
-template <int D, typename T, bool kDKV, bool kStaged, bool kAhead>
+template <int D, typename T, bool kDKV, bool kStaged>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1,
                    const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_b1,
@@ -242,9 +242,10 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   // requested the last loads of a tile it draws the next one, publishes it in one of two slots (item_full / item_free)
   // and - once the MMAs of the current tile are complete (acc_full: the resident pair's buffer is free) - requests
   // the next tile's loads, so that the draw (an atomic and a dependent load of the list entry) and the first loads
-  // overlap the current tile's epilogue.  With many tiles per CTA (kAhead, chosen by the launcher from the number
-  // of token rows) the draw does not wait for anything; with few, a tile drawn early is a tile that cannot go to a
-  // CTA that has run dry (measured: - 7 % on a batch with four tiles per CTA), and it waits for acc_full too.
+  // overlap the current tile's epilogue.  The draw comes a step or two before the current tile's end (the ring of
+  // streamed tiles has two stages), which costs no balance worth the name; drawing at the START of the current tile
+  // did (a tile drawn early is a tile that cannot go to a CTA that has run dry: - 7 % on a batch with four tiles per
+  // CTA).
   // The other warps meet at a named barrier at the end of a tile (the producer warp takes no part in it).
   constexpr int kConsumers = kBwdThreads - 32;
   if (warp == 0) {
@@ -256,7 +257,6 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
         const uint32_t slot = draws & 1u;
         // the slot's last tile (two draws ago) has been read by every warp
         if (draws >= 2) w.wait(ptx::smem_u32(&bars->item_free[slot]), ((draws >> 1) - 1u) & 1u);
-        if (!kAhead && tiles_done > 0) w.wait(ptx::smem_u32(&bars->acc_full), (tiles_done - 1u) & 1u);
         int found = -1, b = 0;
         uint32_t head_tile = 0;
         if (!*reinterpret_cast<volatile int*>(&bars->abort_flag)) {
@@ -722,31 +722,27 @@ cudaError_t launch_bwd_tc_t(const BwdParams& bp, int dtype, int num_sms, cudaStr
                           p.bias_bstride == static_cast<long long>(p.hq) * p.maxq * p.maxk &&
                           make_bias_tile_map(&mb, p, dtype);
   // one pass: the instantiation for (staged bias, tile look-ahead), its shared-memory size set, launched
-  auto launch = [&](auto kdkv, long long tiles_bound, long long tiles_least, const CUtensorMap& a1,
-                    const CUtensorMap& a2, const CUtensorMap& b1, const CUtensorMap& b2) -> cudaError_t {
+  // one pass: the instantiation with or without a staged bias, its shared-memory size set, launched
+  auto launch = [&](auto kdkv, long long tiles_bound, const CUtensorMap& a1, const CUtensorMap& a2,
+                    const CUtensorMap& b1, const CUtensorMap& b2) -> cudaError_t {
     constexpr bool kDKV = decltype(kdkv)::value;
     const unsigned grid = static_cast<unsigned>(tiles_bound < num_sms ? tiles_bound : num_sms);
-    // (the next tile is drawn ahead when every CTA has at least eight: see the kernel)
-    const bool ahead = tiles_least >= 8ll * grid;
     auto go = [&](auto kern, int bytes) -> cudaError_t {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
       if (e != cudaSuccess) return e;
       kern<<<grid, kBwdThreads, bytes, stream>>>(bp, a1, a2, b1, b2, mb);
       return cudaGetLastError();
     };
-    if (bias_staged) return ahead ? go(hstu_bwd_tc_kernel<D, T, kDKV, true, true>, smem_kv)
-                                  : go(hstu_bwd_tc_kernel<D, T, kDKV, true, false>, smem_kv);
-    return ahead ? go(hstu_bwd_tc_kernel<D, T, kDKV, false, true>, smem)
-                 : go(hstu_bwd_tc_kernel<D, T, kDKV, false, false>, smem);
+    return bias_staged ? go(hstu_bwd_tc_kernel<D, T, kDKV, true>, smem_kv) : go(hstu_bwd_tc_kernel<D, T, kDKV, false>, smem);
   };
   cudaError_t e = cudaSuccess;
   if (p.total_q > 0)
-    e = launch(std::false_type{}, static_cast<long long>(p.batch) * p.hq * ((p.maxq + kTileM - 1) / kTileM),
-               static_cast<long long>(p.hq) * (p.total_q / kTileM), mq, mg, mk, mv);
+    e = launch(std::false_type{}, static_cast<long long>(p.batch) * p.hq * ((p.maxq + kTileM - 1) / kTileM), mq, mg,
+               mk, mv);
   if (e != cudaSuccess) return e;
   if (p.total_k > 0)
-    e = launch(std::true_type{}, static_cast<long long>(p.batch) * p.hk * ((p.maxk + kTileN - 1) / kTileN),
-               static_cast<long long>(p.hk) * (p.total_k / kTileN), mk, mv, mq, mg);
+    e = launch(std::true_type{}, static_cast<long long>(p.batch) * p.hk * ((p.maxk + kTileN - 1) / kTileN), mk, mv,
+               mq, mg);
   return e;
 }
 

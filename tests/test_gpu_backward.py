@@ -253,9 +253,9 @@ def test_tile_lists_of_short_sequences_under_a_large_max_seq_len(B, lo_hi, maxL,
 
 
 @pytest.mark.parametrize("bias", [False, True])
-def test_many_tiles_per_cta_draw_the_next_tile_ahead(bias):
-    """With at least eight tiles per CTA the kernels run in the form that draws the next tile while the current one
-    runs (with and without a staged bias): 310 sequences of 121 - 128 rows x 4 heads on 148 CTAs."""
+def test_many_single_step_tiles_per_cta(bias):
+    """Eight one-step tiles per CTA (with and without a staged bias): the producer thread, which draws the tiles and
+    runs ahead of the other warps, is a whole tile ahead all the time.  310 sequences of 121 - 128 rows x 4 heads."""
     grad, args = make_bwd_case(310, 4, 4, 64, 64, 128, BF16, seed=5, bias=bias, tgt=120, g=1, alpha=1.0 / 64)
     assert int(args["seq_offset"][-1]) * 4 // 128 >= 8 * 148
     got, status = run_bwd(grad, args)
