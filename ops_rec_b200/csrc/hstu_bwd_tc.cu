@@ -196,6 +196,12 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   BwdBars* bars = reinterpret_cast<BwdBars*>(base_ptr + 6 * kTileBytes + (staged ? 2 * kTileM * 128 : 0));
   const BwdWaiter w{&bars->abort_flag, p.ws_header};
 
+  // The two passes do not depend on each other, only on the pre-pass before them.  The dK/dV pass is launched with
+  // programmatic stream serialization behind the dQ pass, which lets it go at once: its CTAs take the SMs as the dQ
+  // pass's CTAs leave them, so the end of the one pass (CTAs running dry) overlaps the start of the other.  The dK/dV
+  // pass waits for the dQ pass's completion only at its very end, so that whatever follows in the stream finds both
+  // complete.  (The dQ pass itself started after the pre-pass had completed, so the lists are there for both.)
+  if (!kDKV) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (tid == 0) {
     ptx::prefetch_tensormap(&tm_a1);
     ptx::prefetch_tensormap(&tm_a2);
@@ -696,6 +702,7 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   }  // tiles
   }  // warps 1 .. 11
 
+  if (kDKV && tid == 0) asm volatile("griddepcontrol.wait;" ::: "memory");   // (no-op when launched the plain way)
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 2) {
@@ -722,6 +729,7 @@ cudaError_t launch_bwd_tc_t(const BwdParams& bp, int dtype, int num_sms, cudaStr
                           p.bias_bstride == static_cast<long long>(p.hq) * p.maxq * p.maxk &&
                           make_bias_tile_map(&mb, p, dtype);
   // one pass: the instantiation for (staged bias, tile look-ahead), its shared-memory size set, launched
+  bool overlap = false;
   // one pass: the instantiation with or without a staged bias, its shared-memory size set, launched
   auto launch = [&](auto kdkv, long long tiles_bound, const CUtensorMap& a1, const CUtensorMap& a2,
                     const CUtensorMap& b1, const CUtensorMap& b2) -> cudaError_t {
@@ -730,12 +738,22 @@ cudaError_t launch_bwd_tc_t(const BwdParams& bp, int dtype, int num_sms, cudaStr
     auto go = [&](auto kern, int bytes) -> cudaError_t {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
       if (e != cudaSuccess) return e;
-      kern<<<grid, kBwdThreads, bytes, stream>>>(bp, a1, a2, b1, b2, mb);
-      return cudaGetLastError();
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(grid);
+      cfg.blockDim = dim3(kBwdThreads);
+      cfg.dynamicSmemBytes = bytes;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = (kDKV && overlap) ? 1 : 0;   // the dK/dV pass may start while the dQ pass is still running
+      return cudaLaunchKernelEx(&cfg, kern, bp, a1, a2, b1, b2, mb);
     };
     return bias_staged ? go(hstu_bwd_tc_kernel<D, T, kDKV, true>, smem_kv) : go(hstu_bwd_tc_kernel<D, T, kDKV, false>, smem);
   };
   cudaError_t e = cudaSuccess;
+  overlap = p.total_q > 0;   // (a dQ pass is launched in front of the dK/dV pass)
   if (p.total_q > 0)
     e = launch(std::false_type{}, static_cast<long long>(p.batch) * p.hq * ((p.maxq + kTileM - 1) / kTileM), mq, mg,
                mk, mv);
