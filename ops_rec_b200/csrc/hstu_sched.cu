@@ -156,7 +156,8 @@ __global__ void __launch_bounds__(kPreThreads) hstu_prepass_kernel(const KParams
     __syncthreads();
     if (tid < kBuckets) {
       unsigned acc = s_seen[tid];
-      for (int w = 0; w < 32; ++w) {
+      const int live_warps = p.batch - base >= kPreThreads ? 32 : (p.batch - base + 31) / 32;   // (the others hold zeros)
+      for (int w = 0; w < live_warps; ++w) {
         const unsigned c = s_warp[w][tid];
         s_warp[w][tid] = acc;
         acc += c;
@@ -329,7 +330,8 @@ __global__ void __launch_bounds__(kPreThreads) hstu_bwd_prepass_kernel(const KPa
       __syncthreads();
       if (tid < kTBuckets) {
         unsigned acc = s_seen[tid];
-        for (int w = 0; w < 32; ++w) {
+        const int live_warps = p.batch - base >= kPreThreads ? 32 : (p.batch - base + 31) / 32;   // (the others hold zeros)
+        for (int w = 0; w < live_warps; ++w) {
           const unsigned c = s_warp[w][tid];
           s_warp[w][tid] = acc;
           acc += c;
