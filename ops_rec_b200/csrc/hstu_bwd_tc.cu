@@ -200,8 +200,9 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
   // programmatic stream serialization behind the dQ pass, which lets it go at once: its CTAs take the SMs as the dQ
   // pass's CTAs leave them, so the end of the one pass (CTAs running dry) overlaps the start of the other.  The dK/dV
   // pass waits for the dQ pass's completion only at its very end, so that whatever follows in the stream finds both
-  // complete.  (The dQ pass itself started after the pre-pass had completed, so the lists are there for both.)
-  if (!kDKV) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // complete.  The dQ pass itself is launched the same way behind the pre-pass (its set-up overlaps it): one thread
+  // waits for the pre-pass to complete before the barrier that ends the set-up, and only behind that barrier do the
+  // threads release the dK/dV pass - so the tile lists are complete before either pass reads them.
   if (tid == 0) {
     ptx::prefetch_tensormap(&tm_a1);
     ptx::prefetch_tensormap(&tm_a2);
@@ -230,9 +231,11 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
     ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), 512);
     ptx::tmem_relinquish();
   }
+  if (!kDKV && tid == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
+  if (!kDKV) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
   // Persistent CTAs take tiles from the pre-pass's list of this pass through a counter in the workspace (zeroed by
@@ -747,7 +750,9 @@ cudaError_t launch_bwd_tc_t(const BwdParams& bp, int dtype, int num_sms, cudaStr
       attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
       attr[0].val.programmaticStreamSerializationAllowed = 1;
       cfg.attrs = attr;
-      cfg.numAttrs = (kDKV && overlap) ? 1 : 0;   // the dK/dV pass may start while the dQ pass is still running
+      // the dQ pass sets itself up while the pre-pass runs; the dK/dV pass may start while the dQ pass is still
+      // running (when there is no dQ pass it follows the pre-pass in plain stream order)
+      cfg.numAttrs = (!kDKV || overlap) ? 1 : 0;
       return cudaLaunchKernelEx(&cfg, kern, bp, a1, a2, b1, b2, mb);
     };
     return bias_staged ? go(hstu_bwd_tc_kernel<D, T, kDKV, true>, smem_kv) : go(hstu_bwd_tc_kernel<D, T, kDKV, false>, smem);

@@ -212,6 +212,9 @@ __global__ void __launch_bounds__(kPreThreads) hstu_bwd_prepass_kernel(const KPa
   __shared__ unsigned short s_key[kPreThreads]; // its number of tiles
   __shared__ unsigned s_status;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // (the dQ pass, launched with programmatic stream serialization, may begin its set-up now; it waits for this grid
+  // to complete before it reads the lists)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int all_q = (p.maxq + kTileM - 1) / kTileM;
   if (tid == 0) s_status = 0;
   unsigned st = 0;
