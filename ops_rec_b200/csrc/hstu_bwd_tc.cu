@@ -1,8 +1,9 @@
 // HSTU jagged backward on Blackwell tensor cores (tcgen05 + TMEM + TMA), bf16 / fp16, Dqk = Dv in {64, 128},
 // mask tril / none, the reference's order x = alpha (S + bias).  Everything else runs on hstu_bwd_generic.cu.
 //
-// One kernel template, launched twice with one persistent CTA per SM (tiles are handed out by a counter in the
-// workspace), no atomics on the data (bitwise reproducible):
+// One kernel template, launched twice with one persistent CTA per SM (the tiles of a pass come from a list the
+// pre-pass wrote - only tiles that exist - through a counter in the workspace; the producer thread draws them and
+// runs ahead of the other warps across tile boundaries), no atomics on the data (bitwise reproducible):
 //
 //   dQ pass   (kDKV = false)  one tile of work per (sequence, query head, 128-row q-tile).  Resident: Q tile, dO tile.
 //             Streamed over the visible K tiles j: K_j, V_j.   S = Q.K_j^T, dP = dO.V_j^T  ->  dS  ->  dQ += dS.K_j.
@@ -384,11 +385,6 @@ hstu_bwd_tc_kernel(const BwdParams bp, const __grid_constant__ CUtensorMap tm_a1
     ptx::named_bar_sync(1, kConsumers);
     continue;
   }
-
-  // token row of the resident tiles and of the streamed ones, heads of both
-  const long long a_row = (kDKV ? s.k0 : s.q0) + tile0;
-  const long long b_row0 = kDKV ? s.q0 : s.k0;
-  const int a_head = head;
 
   if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
