@@ -207,6 +207,49 @@ def test_autograd_through_the_forward_operator():
     assert_bwd_parity([g.cpu() for g in got] + [None], grad, dict(args, attn_bias=None), label="delta")
 
 
+def test_forward_and_backward_replay_from_a_cuda_graph():
+    """The operators enqueue on the current stream without any host synchronisation or host read of device data, so a
+    step (forward, then the backward of its output's gradient) can be captured in a CUDA graph and replayed on new
+    inputs - including the kernels launched with programmatic stream serialization."""
+    grad, args = make_bwd_case(5, 4, 2, 64, 64, 300, BF16, seed=31, tgt=11, g=1, alpha=1.0 / 64)
+    grad2, args2 = make_bwd_case(5, 4, 2, 64, 64, 300, BF16, seed=31, tgt=11, g=1, alpha=1.0 / 64)
+    gen = torch.Generator().manual_seed(77)
+    for name in ("q", "k", "v", "attn_bias"):   # same lengths, other values
+        args2[name] = (torch.rand(args[name].shape, generator=gen) * 2 - 1).to(BF16)
+    grad2 = (torch.rand(grad.shape, generator=gen) * 2 - 1).to(BF16)
+    ca = to_cuda(args)
+    fwd = ops_rec_b200.ascendc.attention.hstu_jagged
+    bwd = ops_rec_b200.ascendc.attention.hstu_jagged_backward
+    g_in = grad.cuda()
+
+    def step():
+        out = fwd(ca["q"], ca["k"], ca["v"], None, ca["attn_bias"], 0, args["max_seq_len"], 0.0, ca["seq_offset"],
+                  ca["num_context"], ca["num_target"], 1, args["alpha"])
+        grads = bwd(g_in, ca["q"], ca["k"], ca["v"], None, ca["attn_bias"], 0, args["max_seq_len"], 0.0,
+                    ca["seq_offset"], ca["num_context"], ca["num_target"], 1, args["alpha"])
+        return out, grads
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out, grads = step()
+    for a, g in ((args, grad), (args2, grad2)):
+        for name in ("q", "k", "v", "attn_bias"):
+            ca[name].copy_(a[name])
+        g_in.copy_(g)
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = O.hstu_jagged_forward(**a)
+        assert (out.float().cpu() - ref.float()).abs().max() <= 2e-2 * max(1.0, float(ref.float().abs().max()))
+        got = [t.cpu() if t is not None else None for t in grads[:4]]
+        assert_bwd_parity(got, g, a, label="graph replay")
+
+
 def test_errors():
     grad, args = make_bwd_case(2, 2, 2, 16, 16, 20, BF16, seed=1)
     shared = dict(args, attn_bias=args["attn_bias"][:1])
