@@ -320,6 +320,9 @@ def time_cold(step, flush, reps):
     import torch
     ts = []
     for _ in range(reps):
+        # (twice: ~160 us of device work, so that the host has enqueued the whole call - validation, tensor maps and
+        # two launches take it some tens of microseconds - before the device gets to the first event)
+        flush.zero_()
         flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
