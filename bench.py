@@ -565,7 +565,7 @@ def run_backward(args, ops_rec, W, full, mine, kw, dev, rank, world, local_rank,
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="cfg4", choices=sorted(WORKLOAD_DESC))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
